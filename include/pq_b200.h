@@ -1,0 +1,152 @@
+/* pq_b200.h -- C ABI of libpq_b200.so: the INT8 deployment hot path of PyraQuant
+ * (deploy/int8_exec.py and the token gather/scatter of flux/routing.py) as hand-written
+ * sm_100a CUDA.
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless stated;
+ *   - the return value is a pq_status (0 = PQ_OK); nothing throws, nothing prints;
+ *   - no allocation, no implicit synchronisation: kernels are enqueued on `stream`
+ *     (a cudaStream_t passed as void*; NULL = the legacy default stream) and the call
+ *     returns at once; outputs are caller-allocated;
+ *   - argument checks (null / shape / alignment / dtype) run on the host before any launch:
+ *     a non-zero status means nothing was enqueued;
+ *   - safe to call from any host thread; the only process-wide state is the tuning knobs of
+ *     pq_set_option and a small cache of weight tensor maps guarded by a mutex.
+ *
+ * dtype codes: 0 = bfloat16, 1 = float16 (activations, low-rank factors, outputs).
+ */
+#ifndef PQ_B200_H_
+#define PQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pq_status {
+  PQ_OK = 0,
+  PQ_ERR_NULL = 1,        /* a required pointer is NULL */
+  PQ_ERR_SHAPE = 2,       /* a size is negative, zero where it may not be, or too large */
+  PQ_ERR_ALIGN = 3,       /* a pointer or leading dimension breaks the stated alignment */
+  PQ_ERR_DTYPE = 4,       /* unknown dtype code */
+  PQ_ERR_CUDA = 5,        /* a CUDA runtime/driver call failed (see pq_last_cuda_error) */
+  PQ_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up (read from a status word) */
+  PQ_ERR_UNSUPPORTED = 7, /* valid arguments, but a combination this build does not implement */
+  PQ_ERR_WORKSPACE = 8    /* workspace missing or too small */
+} pq_status;
+
+#define PQ_DTYPE_BF16 0
+#define PQ_DTYPE_FP16 1
+
+/* Library version (major*10000 + minor*100 + patch). */
+int pq_version(void);
+/* Static, human-readable text for a status code. */
+const char* pq_status_str(int status);
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling thread. */
+int pq_last_cuda_error(void);
+
+/* Internal tuning / test knobs ("gemm_epilogue", "gemm_stages", "gemm_block_n", "gemm_group_m",
+ * "gemm_max_ctas").  Unknown keys return PQ_ERR_UNSUPPORTED.  Not part of the reference API. */
+int pq_set_option(const char* key, int value);
+int pq_get_option(const char* key, int* value);
+
+/* Per-token symmetric INT8 quantisation:  s[m] = max(max_k |x[m,k]|, 1e-8) / 127,
+ * q[m,k] = clamp(round_half_even(x[m,k] / s[m]), -127, 127), IEEE fp32 division.
+ * Replaces quant_rows + _quant_rows_kernel (deploy/int8_exec.py:216-230, :78-101).
+ * x [M,K] with row stride ldx (elements), last dim contiguous; q [M,K] contiguous; s [M].
+ * Needs K % 8 == 0, ldx % 8 == 0, x and q 16-byte aligned.  M == 0 is a no-op. */
+int pq_quant_rows(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                  int8_t* q, float* s, void* stream);
+
+/* Same quantisation applied to gathered rows: row m of the output is row row_idx[m] of the
+ * canvas (the active-leaf + halo token rows of build_patch_buckets, flux/routing.py:253-315,
+ * fused with the quantisation of deploy/int8_exec.py:216-230).  row_idx[m] < 0 marks a padding
+ * row: it is written as zeros with the scale of an all-zero row.  0 <= row_idx[m] < rows. */
+int pq_gather_quant_rows(const void* canvas, int dtype, int64_t rows, int64_t K, int64_t ld,
+                         const int32_t* row_idx, int64_t M, int8_t* q, float* s, void* stream);
+
+/* Plain gather without quantisation (the copy of flux/routing.py:288-311): out[m,:] =
+ * canvas[row_idx[m],:], zeros for row_idx[m] < 0.  K % 8 == 0, 16-byte aligned rows. */
+int pq_gather_rows(const void* canvas, int dtype, int64_t rows, int64_t K, int64_t ld,
+                   const int32_t* row_idx, int64_t M, void* out, int64_t ldo, void* stream);
+
+/* Group-32 variant: one scale per 32 consecutive input channels,
+ * s[m,g] = max(max_{k in g} |x|, 1e-8) / 127  (ExtActQuant "dyn_group",
+ * pyraquant/external_quant.py:104-109 with group 32, 8 bits, signed).  s is [M, K/32]. K % 32 == 0. */
+int pq_quant_rows_g32(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                      int8_t* q, float* s, void* stream);
+
+/* Dequantisation of materialised accumulators: out[m,n] = float(acc[m,n]) * (s_row[m] * s_col[n])
+ * (+ bias[n]) rounded to out_dtype.  Replaces dequant_epilogue / _dequant_epilogue_kernel
+ * (deploy/int8_exec.py:233-243, :104-127); kept for API parity, the fused GEMM never needs it.
+ * acc int32 [M,N] contiguous, out [M,N] contiguous. */
+int pq_dequant_epilogue(const int32_t* acc, const float* s_row, const float* s_col, const float* bias,
+                        void* out, int out_dtype, int64_t M, int64_t N, void* stream);
+
+/* Fused INT8 GEMM:  out[m,n] = float(sum_k xq[m,k] * w[n,k]) * (s_row[m] * s_col[n])
+ *                              (+ sum_r t[m,r] * lb[r,n])  (+ bias[n]),  rounded to out_dtype.
+ * Replaces int8_gemm_fused / _int8_gemm_fused_kernel_impl (deploy/int8_exec.py:202-212, :144-183)
+ * and, with t/lb given, int8_gemm_lr / _int8_gemm_lr_impl (:327-336, :272-314); same operation
+ * order as :303-309.  tcgen05 kind::i8 with int32 accumulators in tensor memory.
+ *   xq [M,K] int8 row stride ldx;  w [N,K] int8 row stride ldw;  both K-contiguous, 16-byte aligned
+ *   bases, ldx % 16 == 0, ldw % 16 == 0, K % 16 == 0;
+ *   s_row [M], s_col [N], bias [N] or NULL: fp32;
+ *   t [M,R] (row stride ldt) and lb [R,N] (row stride ldb) in lr_dtype, both NULL or both set,
+ *   R == 32 (the reference's rank) when set;
+ *   out [M,N] row stride ldo in out_dtype;
+ *   dbg_acc: NULL, or int32 [M,N] contiguous that receives the raw accumulators (tests);
+ *   workspace: NULL or >= PQ_GEMM_WORKSPACE_BYTES device bytes; word 0 is a status word that the
+ *   kernel sets non-zero if a bounded wait gave up (read it with pq_read_status_word).
+ * M == 0 is a no-op. */
+#define PQ_GEMM_WORKSPACE_BYTES 256
+int pq_int8_gemm(const int8_t* xq, int64_t ldx, const float* s_row,
+                 const int8_t* w, int64_t ldw, const float* s_col, const float* bias,
+                 const void* t, int64_t ldt, const void* lb, int64_t ldb, int R, int lr_dtype,
+                 void* out, int out_dtype, int64_t ldo,
+                 int64_t M, int64_t N, int64_t K,
+                 void* workspace, size_t ws_bytes, int32_t* dbg_acc, void* stream);
+
+/* Routed two-tier GEMM (the per-leaf precision routing of flux/run_flux.py:117-123 collapsed to a
+ * hard choice at the Linear): rows [0, M_hi) use weight set 0 (the INT8 codes), rows [M_hi, M)
+ * use weight set 1 (the codes re-rounded to the nested 4-bit grid,
+ * pyraquant/quantizers_weight.py:182-199, still stored as int8).  Everything else as pq_int8_gemm;
+ * low-rank factors and bias are shared by both tiers. */
+int pq_int8_gemm_grouped(const int8_t* xq, int64_t ldx, const float* s_row,
+                         const int8_t* w_hi, const float* s_col_hi,
+                         const int8_t* w_lo, const float* s_col_lo, int64_t ldw,
+                         const float* bias,
+                         const void* t, int64_t ldt, const void* lb, int64_t ldb, int R, int lr_dtype,
+                         void* out, int out_dtype, int64_t ldo,
+                         int64_t M_hi, int64_t M, int64_t N, int64_t K,
+                         void* workspace, size_t ws_bytes, void* stream);
+
+/* Feathered scatter of routed rows back over the cached canvas, in place: the pull form of
+ * fuse_patch_predictions (flux/routing.py:328-379).  For canvas token j with contributor list
+ * e in [ptr[j], ptr[j+1]):  local = sum_e beta[e] * y[src[e], :], bsum = sum_e beta[e] (both
+ * accumulated in the canvas dtype, in list order, like the reference's bf16 accumulators), then
+ *   canvas[j] = (1 - clamp(bsum,0,1)) * canvas[j] + clamp(bsum,0,1) * (local / max(bsum, 1e-8)).
+ * Tokens without contributors are left untouched.  `tokens` is the list of canvas rows that have
+ * at least one contributor (n_tokens of them); ptr has n_tokens + 1 entries and indexes src/beta.
+ * y [M_act, C] row stride ldy; canvas [rows, C] row stride ldc.  C % 8 == 0, 16-byte aligned. */
+int pq_scatter_rows(const void* y, int64_t ldy, int64_t M_act,
+                    const int32_t* tokens, const int32_t* ptr, const int32_t* src, const float* beta,
+                    int64_t n_tokens, void* canvas, int64_t ldc, int64_t rows, int64_t C,
+                    int dtype, void* stream);
+
+/* Copies the workspace status word to the host after synchronising `stream` and maps it to a
+ * pq_status (PQ_OK or PQ_ERR_TIMEOUT); *raw receives the word itself (role and barrier that gave
+ * up) when raw != NULL.  The word is cleared when `clear` is non-zero. */
+int pq_read_status_word(void* workspace, int32_t* raw, int clear, void* stream);
+
+/* Tensor-pipe ceiling probe: every CTA issues `iters` tcgen05.mma kind::i8 128x256x32 instructions
+ * on shared-memory operands with no global traffic and writes elapsed clock cycles per CTA to
+ * cycles[ctas] (int64).  Used by the benchmark for the measured INT8 ceiling. */
+int pq_i8_mma_issue_loop(int ctas, int iters, long long* cycles, void* workspace, size_t ws_bytes,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PQ_B200_H_ */

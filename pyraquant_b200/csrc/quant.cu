@@ -1,0 +1,347 @@
+// Memory-bound kernels of the hot path: per-token INT8 quantisation (plain, gathered, group-32) and
+// the plain row gather.  One HBM pass: each thread keeps its 16-byte chunks of the row in registers
+// between the absmax reduction and the quantisation, loads are 128-bit and coalesced, the per-token
+// absmax is a warp-shuffle reduction (plus one shared-memory hop when a row spans several warps).
+//
+// Arithmetic contract (bit-exact with torch on CPU; deploy/int8_exec.py:508-509 and :83-101):
+//   scale = max(absmax, 1e-8) / 127        IEEE fp32 division
+//   q     = round_half_even(x / scale)     IEEE fp32 division, clamp to [-127, 127]
+// The division per element is replaced by a multiplication with 1/scale plus a distance-to-tie test;
+// only elements whose product lands within 2^-13 of a rounding boundary take the IEEE division.
+#include "common.cuh"
+
+namespace pq {
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename T> __device__ __forceinline__ uint32_t abs2_max(uint32_t acc, uint32_t w);
+template <> __device__ __forceinline__ uint32_t abs2_max<__nv_bfloat16>(uint32_t acc, uint32_t w) {
+  __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&acc);
+  __nv_bfloat162 b = __habs2(*reinterpret_cast<__nv_bfloat162*>(&w));
+  __nv_bfloat162 r = __hmax2(a, b);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t abs2_max<__half>(uint32_t acc, uint32_t w) {
+  __half2 a = *reinterpret_cast<__half2*>(&acc);
+  __half2 b = __habs2(*reinterpret_cast<__half2*>(&w));
+  __half2 r = __hmax2(a, b);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// One element: returns the int8 code in the low byte (two's complement).
+__device__ __forceinline__ uint32_t quant1(float x, float scale, float inv) {
+  const float kMagic = 12582912.0f;                 // 1.5 * 2^23: adding it rounds to nearest-even integer
+  float r = x * inv;
+  float m = r + kMagic;
+  float qf = m - kMagic;
+  float d = fabsf(r - qf);
+  if (d > 0.5f - 1.220703125e-4f) {                 // within 2^-13 of a tie: decide with the exact quotient
+    qf = rintf(__fdiv_rn(x, scale));
+  }
+  qf = fminf(fmaxf(qf, -127.0f), 127.0f);
+  return static_cast<uint32_t>(__float2int_rn(qf)) & 0xFFu;
+}
+
+template <typename T>
+__device__ __forceinline__ void quant_chunk(const uint4& v, float scale, float inv, uint32_t& lo, uint32_t& hi) {
+  T tag{};
+  lo = quant1(lo_f32(v.x, tag), scale, inv) | (quant1(hi_f32(v.x, tag), scale, inv) << 8) |
+       (quant1(lo_f32(v.y, tag), scale, inv) << 16) | (quant1(hi_f32(v.y, tag), scale, inv) << 24);
+  hi = quant1(lo_f32(v.z, tag), scale, inv) | (quant1(hi_f32(v.z, tag), scale, inv) << 8) |
+       (quant1(lo_f32(v.w, tag), scale, inv) << 16) | (quant1(hi_f32(v.w, tag), scale, inv) << 24);
+}
+
+template <typename T>
+__device__ __forceinline__ float amax_of_packed(uint32_t acc) {
+  T tag{};
+  return fmaxf(lo_f32(acc, tag), hi_f32(acc, tag));
+}
+
+// TPR threads cooperate on one row, each holding CPT chunks of 8 elements (chunk c of the row is owned
+// by thread c % TPR).  GROUP32: one scale per 32 elements (4 neighbouring threads) instead of per row.
+template <typename T, int TPR, int CPT, bool GATHER, bool GROUP32>
+__global__ void __launch_bounds__(kThreads)
+pq_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, const int32_t* __restrict__ row_idx, int64_t src_rows,
+                     int8_t* __restrict__ q, float* __restrict__ s, int64_t M, int K) {
+  constexpr int RPB = kThreads / TPR;                  // rows per block
+  constexpr int WPR = (TPR + 31) / 32;                 // warps per row
+  __shared__ float s_part[kThreads / 32];
+  const int tid = threadIdx.x;
+  const int r_in_blk = tid / TPR;
+  const int lane_in_row = tid % TPR;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * RPB + r_in_blk;
+  const bool row_ok = row < M;
+  const int nchunk = K >> 3;
+
+  int64_t src = row;
+  if (GATHER && row_ok) src = row_idx[row];
+  const bool have_src = row_ok && src >= 0 && (!GATHER || src < src_rows);   // out-of-range indices read nothing
+  const uint4* xrow = reinterpret_cast<const uint4*>(x + (have_src ? src : 0) * ldx);
+
+  uint4 v[CPT];
+#pragma unroll
+  for (int j = 0; j < CPT; ++j) {
+    const int c = lane_in_row + j * TPR;
+    if (have_src && c < nchunk) v[j] = ld_stream_v4(xrow + c);
+    else v[j] = make_uint4(0u, 0u, 0u, 0u);
+  }
+
+  if constexpr (!GROUP32) {
+    uint32_t acc = 0u;
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) {
+      acc = abs2_max<T>(acc, v[j].x); acc = abs2_max<T>(acc, v[j].y);
+      acc = abs2_max<T>(acc, v[j].z); acc = abs2_max<T>(acc, v[j].w);
+    }
+    float amax = amax_of_packed<T>(acc);
+    constexpr int W = TPR < 32 ? TPR : 32;
+#pragma unroll
+    for (int o = W / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if constexpr (WPR > 1) {
+      const int warp = tid >> 5;
+      if ((tid & 31) == 0) s_part[warp] = amax;
+      __syncthreads();
+      const int w0 = r_in_blk * WPR;
+      amax = s_part[w0];
+#pragma unroll
+      for (int w = 1; w < WPR; ++w) amax = fmaxf(amax, s_part[w0 + w]);
+    }
+    const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (row_ok) {
+      if (lane_in_row == 0) s[row] = scale;
+      int8_t* qrow = q + row * static_cast<int64_t>(K);
+#pragma unroll
+      for (int j = 0; j < CPT; ++j) {
+        const int c = lane_in_row + j * TPR;
+        if (c < nchunk) {
+          uint32_t lo, hi;
+          quant_chunk<T>(v[j], scale, inv, lo, hi);
+          st_v2(qrow + (static_cast<int64_t>(c) << 3), lo, hi);
+        }
+      }
+    }
+  } else {
+    // group of 32 elements = chunks 4i..4i+3 = four neighbouring threads of the row (TPR % 4 == 0)
+    const int ngroup = K >> 5;
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) {
+      uint32_t acc = 0u;
+      acc = abs2_max<T>(acc, v[j].x); acc = abs2_max<T>(acc, v[j].y);
+      acc = abs2_max<T>(acc, v[j].z); acc = abs2_max<T>(acc, v[j].w);
+      float amax = amax_of_packed<T>(acc);
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+      const float inv = __fdiv_rn(1.0f, scale);
+      const int c = lane_in_row + j * TPR;
+      if (row_ok && c < nchunk) {
+        if ((c & 3) == 0) s[row * static_cast<int64_t>(ngroup) + (c >> 2)] = scale;
+        uint32_t lo, hi;
+        quant_chunk<T>(v[j], scale, inv, lo, hi);
+        st_v2(q + row * static_cast<int64_t>(K) + (static_cast<int64_t>(c) << 3), lo, hi);
+      }
+    }
+  }
+}
+
+// Rows too long for the register-resident kernel: one block per row, two sweeps (the second one is
+// served by L2 for any row that fits there).
+template <typename T, bool GATHER>
+__global__ void __launch_bounds__(kThreads)
+pq_quant_rows_kernel_long(const T* __restrict__ x, int64_t ldx, const int32_t* __restrict__ row_idx, int64_t src_rows,
+                          int8_t* __restrict__ q, float* __restrict__ s, int64_t M, int K) {
+  __shared__ float s_part[kThreads / 32];
+  const int64_t row = blockIdx.x;
+  int64_t src = row;
+  if (GATHER) src = row_idx[row];
+  const bool have_src = src >= 0 && (!GATHER || src < src_rows);
+  const uint4* xrow = reinterpret_cast<const uint4*>(x + (have_src ? src : 0) * ldx);
+  const int nchunk = K >> 3;
+  uint32_t acc = 0u;
+  if (have_src) {
+    for (int c = threadIdx.x; c < nchunk; c += kThreads) {
+      uint4 v = xrow[c];
+      acc = abs2_max<T>(acc, v.x); acc = abs2_max<T>(acc, v.y);
+      acc = abs2_max<T>(acc, v.z); acc = abs2_max<T>(acc, v.w);
+    }
+  }
+  float amax = amax_of_packed<T>(acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = s_part[0];
+#pragma unroll
+  for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, s_part[w]);
+  const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+  const float inv = __fdiv_rn(1.0f, scale);
+  if (threadIdx.x == 0) s[row] = scale;
+  int8_t* qrow = q + row * static_cast<int64_t>(K);
+  for (int c = threadIdx.x; c < nchunk; c += kThreads) {
+    uint4 v = have_src ? xrow[c] : make_uint4(0u, 0u, 0u, 0u);
+    uint32_t lo, hi;
+    quant_chunk<T>(v, scale, inv, lo, hi);
+    st_v2(qrow + (static_cast<int64_t>(c) << 3), lo, hi);
+  }
+}
+
+// Plain gather: out[m,:] = canvas[row_idx[m],:] (zeros for negative indices), 16-byte chunks.
+__global__ void __launch_bounds__(kThreads)
+pq_gather_rows_kernel(const uint4* __restrict__ x, int64_t ld16, const int32_t* __restrict__ row_idx, int64_t src_rows,
+                      uint4* __restrict__ out, int64_t ldo16, int64_t M, int nchunk) {
+  const int64_t total = M * static_cast<int64_t>(nchunk);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t m = i / nchunk;
+    const int c = static_cast<int>(i - m * nchunk);
+    const int64_t src = row_idx[m];
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (src >= 0 && src < src_rows) v = ld_stream_v4(x + src * ld16 + c);
+    st_v4(out + m * ldo16 + c, v);
+  }
+}
+
+
+// int32 accumulators -> scaled 16-bit output, one read and one write per element.
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads)
+pq_dequant_epilogue_kernel(const int32_t* __restrict__ acc, const float* __restrict__ s_row,
+                           const float* __restrict__ s_col, const float* __restrict__ bias, OutT* __restrict__ out,
+                           int64_t M, int64_t N) {
+  const int64_t total = M * N;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    const int64_t m = i / N;
+    const int64_t n = i - m * N;
+    float yv = static_cast<float>(acc[i]) * (s_row[m] * s_col[n]);
+    if (bias != nullptr) yv += bias[n];
+    if constexpr (sizeof(OutT) == 2 && __is_same(OutT, __nv_bfloat16)) out[i] = __float2bfloat16_rn(yv);
+    else out[i] = __float2half_rn(yv);
+  }
+}
+
+template <typename T, bool GATHER, bool GROUP32, int TPR, int CPT>
+int launch_one(const void* x, int64_t ldx, const int32_t* row_idx, int64_t src_rows, int8_t* q, float* s, int64_t M,
+               int K, cudaStream_t st) {
+  constexpr int RPB = kThreads / TPR;
+  const int64_t blocks = (M + RPB - 1) / RPB;
+  if (blocks > 0x7fffffffLL) return PQ_ERR_SHAPE;
+  pq_quant_rows_kernel<T, TPR, CPT, GATHER, GROUP32>
+      <<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(static_cast<const T*>(x), ldx, row_idx, src_rows, q, s, M, K);
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
+
+template <typename T, bool GATHER, bool GROUP32>
+int dispatch(const void* x, int64_t ldx, const int32_t* row_idx, int64_t src_rows, int8_t* q, float* s, int64_t M,
+             int K, cudaStream_t st) {
+  const int nchunk = K >> 3;
+  // pick the smallest team whose registers hold the row with <= 8 chunks per thread
+  if (nchunk <= 32 * 2) return launch_one<T, GATHER, GROUP32, 32, 2>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (nchunk <= 32 * 4) return launch_one<T, GATHER, GROUP32, 32, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (nchunk <= 64 * 4) return launch_one<T, GATHER, GROUP32, 64, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (nchunk <= 128 * 3) return launch_one<T, GATHER, GROUP32, 128, 3>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (nchunk <= 256 * 4) return launch_one<T, GATHER, GROUP32, 256, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (nchunk <= 256 * 6) return launch_one<T, GATHER, GROUP32, 256, 6>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (nchunk <= 256 * 8) return launch_one<T, GATHER, GROUP32, 256, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if constexpr (GROUP32) {
+    return PQ_ERR_UNSUPPORTED;   // K > 16384 with group scales: not a shape of the path
+  } else {
+    if (M > 0x7fffffffLL) return PQ_ERR_SHAPE;
+    pq_quant_rows_kernel_long<T, GATHER>
+        <<<static_cast<unsigned>(M), kThreads, 0, st>>>(static_cast<const T*>(x), ldx, row_idx, src_rows, q, s, M, K);
+    PQ_CUDA_TRY(cudaGetLastError());
+    return PQ_OK;
+  }
+}
+
+int check_common(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, const void* q, const void* s,
+                 int kmult) {
+  if (M < 0 || K <= 0 || K > 0x7fffffffLL || ldx < K) return PQ_ERR_SHAPE;
+  if (dtype != PQ_DTYPE_BF16 && dtype != PQ_DTYPE_FP16) return PQ_ERR_DTYPE;
+  if (M == 0) return PQ_OK;
+  if (x == nullptr || q == nullptr || s == nullptr) return PQ_ERR_NULL;
+  if (K % kmult != 0 || ldx % 8 != 0) return PQ_ERR_ALIGN;
+  if (!aligned_to(x, 16) || !aligned_to(q, 8) || !aligned_to(s, 4)) return PQ_ERR_ALIGN;
+  return PQ_OK;
+}
+
+}  // namespace
+}  // namespace pq
+
+using namespace pq;
+
+extern "C" int pq_quant_rows(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, int8_t* q, float* s,
+                             void* stream) {
+  int rc = check_common(x, dtype, M, K, ldx, q, s, 8);
+  if (rc != PQ_OK || M == 0) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == PQ_DTYPE_BF16)
+    return dispatch<__nv_bfloat16, false, false>(x, ldx, nullptr, M, q, s, M, static_cast<int>(K), st);
+  return dispatch<__half, false, false>(x, ldx, nullptr, M, q, s, M, static_cast<int>(K), st);
+}
+
+extern "C" int pq_gather_quant_rows(const void* canvas, int dtype, int64_t rows, int64_t K, int64_t ld,
+                                    const int32_t* row_idx, int64_t M, int8_t* q, float* s, void* stream) {
+  if (rows < 0) return PQ_ERR_SHAPE;
+  int rc = check_common(canvas, dtype, M, K, ld, q, s, 8);
+  if (rc != PQ_OK || M == 0) return rc;
+  if (row_idx == nullptr) return PQ_ERR_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == PQ_DTYPE_BF16)
+    return dispatch<__nv_bfloat16, true, false>(canvas, ld, row_idx, rows, q, s, M, static_cast<int>(K), st);
+  return dispatch<__half, true, false>(canvas, ld, row_idx, rows, q, s, M, static_cast<int>(K), st);
+}
+
+extern "C" int pq_quant_rows_g32(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, int8_t* q, float* s,
+                                 void* stream) {
+  int rc = check_common(x, dtype, M, K, ldx, q, s, 32);
+  if (rc != PQ_OK || M == 0) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == PQ_DTYPE_BF16)
+    return dispatch<__nv_bfloat16, false, true>(x, ldx, nullptr, M, q, s, M, static_cast<int>(K), st);
+  return dispatch<__half, false, true>(x, ldx, nullptr, M, q, s, M, static_cast<int>(K), st);
+}
+
+extern "C" int pq_gather_rows(const void* canvas, int dtype, int64_t rows, int64_t K, int64_t ld,
+                              const int32_t* row_idx, int64_t M, void* out, int64_t ldo, void* stream) {
+  if (M < 0 || rows < 0 || K <= 0 || K > 0x7fffffffLL || ld < K || ldo < K) return PQ_ERR_SHAPE;
+  if (dtype != PQ_DTYPE_BF16 && dtype != PQ_DTYPE_FP16) return PQ_ERR_DTYPE;
+  if (M == 0) return PQ_OK;
+  if (canvas == nullptr || row_idx == nullptr || out == nullptr) return PQ_ERR_NULL;
+  if (K % 8 != 0 || ld % 8 != 0 || ldo % 8 != 0 || !aligned_to(canvas, 16) || !aligned_to(out, 16))
+    return PQ_ERR_ALIGN;
+  const int nchunk = static_cast<int>(K >> 3);
+  const int64_t total = M * nchunk;
+  int64_t blocks = (total + kThreads - 1) / kThreads;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  pq_gather_rows_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(canvas), ld >> 3, row_idx, rows, static_cast<uint4*>(out), ldo >> 3, M, nchunk);
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
+
+extern "C" int pq_dequant_epilogue(const int32_t* acc, const float* s_row, const float* s_col, const float* bias,
+                                   void* out, int out_dtype, int64_t M, int64_t N, void* stream) {
+  if (M < 0 || N <= 0) return PQ_ERR_SHAPE;
+  if (out_dtype != PQ_DTYPE_BF16 && out_dtype != PQ_DTYPE_FP16) return PQ_ERR_DTYPE;
+  if (M == 0) return PQ_OK;
+  if (acc == nullptr || s_row == nullptr || s_col == nullptr || out == nullptr) return PQ_ERR_NULL;
+  const int64_t total = M * N;
+  int64_t blocks = (total + kThreads - 1) / kThreads;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == PQ_DTYPE_BF16)
+    pq_dequant_epilogue_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(
+        acc, s_row, s_col, bias, static_cast<__nv_bfloat16*>(out), M, N);
+  else
+    pq_dequant_epilogue_kernel<__half><<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(
+        acc, s_row, s_col, bias, static_cast<__half*>(out), M, N);
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}

@@ -1,0 +1,390 @@
+"""Drop-in for PyraQuant's ``deploy/int8_exec.py``: same public names, argument meaning and error
+behaviour, executed by libpq_b200.so (hand-written sm_100a CUDA) through torch custom ops.
+
+What stays the same for a caller of the reference module
+  * ``Int8Linear(lin, device=None, lowrank=None)`` with buffers ``weight_int8``, ``w_scale``, ``bias``,
+    ``lr_A``, ``lr_B`` and attributes ``in_features`` / ``out_features`` (reference :345-411);
+  * ``quant_rows``, ``int8_gemm_fused``, ``int8_gemm_lr``, ``int8_linear_2d``, ``dequant_epilogue``
+    (reference :202-261, :327-336) -- outputs freshly allocated, inputs never modified, launched on
+    torch's current stream without synchronising;
+  * ``set_backend`` / ``get_backend`` / ``BACKENDS`` / ``DEFAULT_BACKEND`` / ``BACKEND`` (reference :58-74):
+    both names are accepted because drivers pass them, and both select the one native backend;
+  * ``convert_linears_to_int8``, ``is_bf16_whitelisted``, ``warm_kernels``, ``FLUX_TOKEN_SHAPES``,
+    ``LOWRANK_A_ATTR`` / ``LOWRANK_B_ATTR``, ``selftest_and_bench`` and the module CLI (reference :415-588).
+What differs: no Triton, no cuBLAS ``_int_mm`` path, no CPU path (CPU tensors raise AssertionError exactly
+as the reference's ``quant_rows`` does, :221), and the shape rules are wider (K % 16 == 0, any N that is a
+multiple of 8, instead of K % 64 == 0 and N % 256 == 0).
+
+Added entry points (not in the reference module): ``quant_rows_g32``, ``gather_quant_rows``,
+``int8_gemm_grouped``, ``nested4_codes``, ``Int8LinearRouted``.
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+
+# --------------------------------------------------------------------------- backend names (API parity only)
+BACKENDS = ("triton", "cublas")
+DEFAULT_BACKEND = "triton"
+BACKEND = DEFAULT_BACKEND
+
+
+def set_backend(name: str) -> str:
+    """Accepted for compatibility with drivers that pass ``--int8-backend``; every name maps to the
+    sm_100a library.  Unknown names raise ValueError like the reference (:67-68)."""
+    global BACKEND
+    if name not in BACKENDS:
+        raise ValueError(f"unknown INT8 backend {name!r} (expected one of {BACKENDS})")
+    BACKEND = name
+    return BACKEND
+
+
+def get_backend() -> str:
+    return BACKEND
+
+
+def _m_bucket(M: int) -> int:
+    """Reference autotune bucket of M (:198-199); kept because drivers import it."""
+    return 0 if M < 8192 else (1 if M < 32768 else 2)
+
+
+# --------------------------------------------------------------------------- operator wrappers
+def quant_rows(x2: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """[M,K] bf16/fp16 -> (int8 codes [M,K], fp32 scale [M]); rows may be strided (no copy)."""
+    assert x2.dim() == 2 and x2.is_cuda
+    return torch.ops.pq_b200.quant_rows(x2)
+
+
+def quant_rows_g32(x2: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-token, per-32-channel scales: (int8 [M,K], fp32 [M, K/32])."""
+    assert x2.dim() == 2 and x2.is_cuda
+    return torch.ops.pq_b200.quant_rows_g32(x2)
+
+
+def gather_quant_rows(canvas: torch.Tensor, row_idx: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Rows ``row_idx`` (int32, -1 = zero padding row) of ``canvas`` [rows,K], quantised per token."""
+    assert canvas.dim() == 2 and canvas.is_cuda
+    return torch.ops.pq_b200.gather_quant_rows(canvas, row_idx)
+
+
+def int8_gemm_fused(xq: torch.Tensor, s_row: torch.Tensor, w_int8: torch.Tensor, w_scale: torch.Tensor,
+                    bias: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    assert xq.is_cuda
+    return torch.ops.pq_b200.int8_gemm(xq, s_row, w_int8, w_scale, bias, None, None, ops.dtype_code(out_dtype))
+
+
+def int8_gemm_lr(xq, s_row, w_i8, w_scale, bias, t, lb, out_dtype):
+    """Fused GEMM with the low-rank up-projection ``t @ lb`` added before the bias (reference :303-309)."""
+    assert xq.is_cuda
+    return torch.ops.pq_b200.int8_gemm(xq, s_row, w_i8, w_scale, bias, t, lb, ops.dtype_code(out_dtype))
+
+
+def int8_gemm_grouped(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, m_hi: int, out_dtype):
+    """Rows [0, m_hi) against (w_hi, s_hi), rows [m_hi, M) against (w_lo, s_lo), one launch."""
+    assert xq.is_cuda
+    return torch.ops.pq_b200.int8_gemm_grouped(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, int(m_hi),
+                                               ops.dtype_code(out_dtype))
+
+
+def dequant_epilogue(acc: torch.Tensor, s_row: torch.Tensor, s_col: torch.Tensor,
+                     bias: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    assert acc.dtype == torch.int32 and acc.is_contiguous()
+    return torch.ops.pq_b200.dequant_epilogue(acc, s_row, s_col, bias, ops.dtype_code(out_dtype))
+
+
+def int8_linear_2d(x2: torch.Tensor, w_int8: torch.Tensor, w_scale: torch.Tensor,
+                   bias: Optional[torch.Tensor], backend: Optional[str] = None) -> torch.Tensor:
+    """x2 [M,K] -> [M,N] in x2's dtype.  ``backend`` is validated and otherwise ignored."""
+    if backend is not None and backend not in BACKENDS:
+        raise ValueError(f"unknown INT8 backend {backend!r} (expected one of {BACKENDS})")
+    xq, sx = quant_rows(x2)
+    return int8_gemm_fused(xq, sx, w_int8, w_scale, bias, x2.dtype)
+
+
+# --------------------------------------------------------------------------- module
+LOWRANK_A_ATTR = "_lowrank_A"
+LOWRANK_B_ATTR = "_lowrank_B"
+
+
+def _quantize_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-output-channel symmetric absmax INT8 (reference :355-357): fp32 math, round-half-even."""
+    wf = w.float()
+    scale = wf.abs().amax(dim=1).clamp_min(1e-8) / 127.0
+    codes = torch.round(wf / scale[:, None]).clamp_(-127, 127).to(torch.int8)
+    return codes.contiguous(), scale.contiguous()
+
+
+def nested4_codes(weight_int8: torch.Tensor, w_scale: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """INT8 codes re-rounded to the nested 4-bit grid (pyraquant/quantizers_weight.py:182-199):
+    c = round(q8 * 7/127) in [-7, 7], dequantised as c * (127/7) * s8.  Returned as int8 codes plus the
+    matching per-channel scale so that the same INT8 kernel executes the low tier."""
+    c = torch.round(weight_int8.float() * (7.0 / 127.0)).clamp_(-7, 7).to(torch.int8)
+    return c.contiguous(), (w_scale.float() * (127.0 / 7.0)).contiguous()
+
+
+class Int8Linear(nn.Module):
+    """INT8 stand-in for ``nn.Linear``: per-channel INT8 weights held as buffers, per-token dynamic INT8
+    activations, optional rank-r low-rank branch executed for real (down-projection as a small GEMM,
+    up-projection inside the INT8 GEMM epilogue)."""
+
+    def __init__(self, lin: nn.Linear, device: Optional[torch.device] = None,
+                 lowrank: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+        super().__init__()
+        w = lin.weight.detach()
+        if device is not None:
+            w = w.to(device, non_blocking=False)
+        codes, scale = _quantize_weight(w)
+        self.register_buffer("weight_int8", codes)
+        self.register_buffer("w_scale", scale)
+        if lin.bias is not None:
+            b = lin.bias.detach().float()
+            if device is not None:
+                b = b.to(device)
+            self.register_buffer("bias", b.contiguous())
+        else:
+            self.bias = None
+        self.in_features = int(lin.in_features)
+        self.out_features = int(lin.out_features)
+        if lowrank is not None:
+            A, B = lowrank
+        else:
+            A, B = getattr(lin, LOWRANK_A_ATTR, None), getattr(lin, LOWRANK_B_ATTR, None)
+        if A is not None and B is not None:
+            if device is not None:
+                A, B = A.to(device), B.to(device)
+            self.register_buffer("lr_A", A.contiguous())
+            self.register_buffer("lr_B", B.contiguous())
+        else:
+            self.lr_A = None
+            self.lr_B = None
+
+    def _fusable_lowrank(self, x2: torch.Tensor) -> bool:
+        return (self.lr_A is not None and self.lr_A.shape[1] == 32 and x2.shape[1] % 32 == 0
+                and self.lr_A.dtype == x2.dtype and self.out_features % 8 == 0)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        if self._fusable_lowrank(x2):
+            t = x2.to(self.lr_A.dtype) @ self.lr_A                 # [M, r], rounded to the activation dtype
+            xq, sx = quant_rows(x2)
+            y = int8_gemm_lr(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B, x2.dtype)
+            return y.reshape(*shape[:-1], self.out_features)
+        y = int8_linear_2d(x2, self.weight_int8, self.w_scale, self.bias)
+        if self.lr_A is not None:                                  # shapes the fused epilogue does not take
+            xa = x2.to(self.lr_A.dtype) @ self.lr_A
+            if y.dtype == self.lr_B.dtype and y.is_contiguous():
+                y.addmm_(xa, self.lr_B)
+            else:
+                y = torch.addmm(y, xa.to(y.dtype), self.lr_B.to(y.dtype))
+        return y.reshape(*shape[:-1], self.out_features)
+
+    def extra_repr(self) -> str:
+        return (f"in={self.in_features}, out={self.out_features}, int8 per-channel W / per-token A, "
+                f"sm_100a tcgen05 kernel")
+
+
+class Int8LinearRouted(Int8Linear):
+    """Two-tier routed Linear: rows gathered from a token canvas, the first ``m_hi`` rows run against
+    the INT8 codes, the rest against the nested 4-bit grid derived from them (``nested4_codes``)."""
+
+    def __init__(self, lin: nn.Linear, device: Optional[torch.device] = None,
+                 lowrank: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+        super().__init__(lin, device=device, lowrank=lowrank)
+        c4, s4 = nested4_codes(self.weight_int8, self.w_scale)
+        self.register_buffer("weight_lo", c4)
+        self.register_buffer("w_scale_lo", s4)
+
+    def forward_rows(self, x2: torch.Tensor, m_hi: int) -> torch.Tensor:
+        """x2 [M,K] already gathered and ordered hi-tier rows first."""
+        t = lb = None
+        if self._fusable_lowrank(x2):
+            t = x2.to(self.lr_A.dtype) @ self.lr_A
+            lb = self.lr_B
+        xq, sx = quant_rows(x2)
+        return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self.weight_lo, self.w_scale_lo,
+                                 self.bias, t, lb, m_hi, x2.dtype)
+
+    def forward_gathered(self, canvas: torch.Tensor, row_idx: torch.Tensor, m_hi: int) -> torch.Tensor:
+        """Gather + quantise in one kernel straight from the canvas, then the two-tier GEMM."""
+        t = lb = None
+        xq, sx = gather_quant_rows(canvas, row_idx)
+        if self.lr_A is not None and self.lr_A.shape[1] == 32 and self.lr_A.dtype == canvas.dtype:
+            xg = torch.ops.pq_b200.gather_rows(canvas, row_idx)
+            t = xg @ self.lr_A
+            lb = self.lr_B
+        return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self.weight_lo, self.w_scale_lo,
+                                 self.bias, t, lb, m_hi, canvas.dtype)
+
+
+# --------------------------------------------------------------------------- model conversion
+def is_bf16_whitelisted(name: str) -> bool:
+    """Layers that stay in 16 bit: embedders, the output projection, time/text embedding, the final norm
+    and every adaLN modulation projection ``*.norm*.linear`` (reference :415-421)."""
+    parts = name.split(".")
+    if parts[0] in ("x_embedder", "context_embedder", "proj_out", "time_text_embed", "norm_out"):
+        return True
+    return len(parts) >= 2 and parts[-1] == "linear" and parts[-2].startswith("norm")
+
+
+def convert_linears_to_int8(model: nn.Module, device: Optional[str] = "cuda",
+                            whitelist: Callable[[str], bool] = is_bf16_whitelisted) -> Dict[str, object]:
+    """Swaps every non-whitelisted ``nn.Linear`` for ``Int8Linear`` in place and returns the same
+    statistics dictionary as the reference (:444-445)."""
+    dev = torch.device(device) if device is not None else None
+    stats = {"n_int8_linear": 0, "n_bf16_linear_kept": 0, "params_int8": 0, "params_bf16_linear_kept": 0,
+             "bf16_kept_names": []}
+    for name, lin in [(n, m) for n, m in model.named_modules() if isinstance(m, nn.Linear)]:
+        if whitelist(name):
+            stats["n_bf16_linear_kept"] += 1
+            stats["params_bf16_linear_kept"] += lin.weight.numel()
+            stats["bf16_kept_names"].append(name)
+            continue
+        parent_name, _, attr = name.rpartition(".")
+        parent = model.get_submodule(parent_name) if parent_name else model
+        setattr(parent, attr, Int8Linear(lin, device=dev))
+        stats["n_int8_linear"] += 1
+        stats["params_int8"] += lin.weight.numel()
+    if dev is not None and dev.type == "cuda":
+        torch.cuda.synchronize()
+    stats["int8_weight_gib"] = stats["params_int8"] / 2**30
+    stats["bf16_equiv_gib"] = stats["params_int8"] * 2 / 2**30
+    return stats
+
+
+FLUX_TOKEN_SHAPES = {   # (K, N): number of such token-level Linears in FLUX.1-schnell (reference :478-483)
+    (3072, 3072): 19 * 8 + 38 * 3,
+    (3072, 12288): 19 * 2 + 38,
+    (12288, 3072): 19 * 2,
+    (15360, 3072): 38,
+}
+
+
+def warm_kernels(Ms=(4352, 16640, 65792), device="cuda", lowrank_R=32, warm_lowrank: bool = True):
+    """Nothing is compiled at run time; this loads the library, creates the per-device status word and
+    runs each FLUX shape once so that first-call costs (module load, tensor-map cache) stay outside
+    timed regions.  Signature as the reference (:448-474)."""
+    t0 = time.perf_counter()
+    for (K, N) in FLUX_TOKEN_SHAPES:
+        w = torch.randint(-127, 127, (N, K), device=device, dtype=torch.int8)
+        s = torch.rand(N, device=device); b = torch.rand(N, device=device)
+        lb = torch.randn(lowrank_R, N, device=device, dtype=torch.bfloat16)
+        x = torch.randn(min(Ms), K, device=device, dtype=torch.bfloat16)
+        int8_linear_2d(x, w, s, b)
+        if warm_lowrank:
+            xq, sx = quant_rows(x)
+            t = torch.randn(x.shape[0], lowrank_R, device=device, dtype=torch.bfloat16)
+            int8_gemm_lr(xq, sx, w, s, b, t, lb, torch.bfloat16)
+        del w, s, b, lb, x
+    torch.cuda.synchronize(); torch.cuda.empty_cache()
+    ops.check_device_status(device)
+    print(f"[int8_exec] kernels warmed (backend={BACKEND} -> sm_100a native, lowrank r={lowrank_R}) "
+          f"in {time.perf_counter() - t0:.1f}s", flush=True)
+
+
+# --------------------------------------------------------------------------- self-test / micro-benchmark
+def _bench(fn, iters=20, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize(); t = time.perf_counter()
+    for _ in range(iters):
+        fn()
+    torch.cuda.synchronize(); return (time.perf_counter() - t) / iters * 1e3
+
+
+def selftest_and_bench(Ms=(4352, 16640, 33744, 65792), iters=10):
+    """The reference's numerical self-test (:498-536), asserted with its thresholds, followed by its
+    per-M micro-benchmark over the FLUX token-level shapes (:541-570)."""
+    dev = "cuda"
+    torch.manual_seed(0)
+    lin = nn.Linear(3072, 12288, bias=True).to(dev, torch.bfloat16)
+    x = (torch.randn(4352, 3072, device=dev) * 2).to(torch.bfloat16)
+    x[:, 5] *= 30.0
+    ref_bf16 = F.linear(x, lin.weight, lin.bias).float()
+    q = Int8Linear(lin, device=torch.device(dev))
+    y = q(x).float()
+    xq, sx = quant_rows(x)
+    acc = torch._int_mm(xq, q.weight_int8.t()).float() if xq.shape[0] > 16 else xq.float() @ q.weight_int8.float().t()
+    ref_int8 = (acc * sx[:, None] * q.w_scale[None, :] + q.bias[None, :]).to(torch.bfloat16).float()
+    xf = x.float(); sc = xf.abs().amax(1, keepdim=True).clamp_min(1e-8) / 127
+    xq_ref = torch.round(xf / sc).clamp(-127, 127).to(torch.int8)
+    x_plain = torch.randn(4352, 3072, device=dev).to(torch.bfloat16)
+    y_plain = q(x_plain).float(); ref_plain = F.linear(x_plain, lin.weight, lin.bias).float()
+    xs = x[:8]
+    ys = q(xs).float()
+    xqs, sxs = quant_rows(xs)
+    rs = ((xqs.float() @ q.weight_int8.float().t()) * sxs[:, None] * q.w_scale[None, :] + q.bias[None, :]
+          ).to(torch.bfloat16).float()
+    x3 = x[:2048].reshape(8, 256, 3072)
+    rep = {
+        "act_quant_mismatch_elems": int((xq != xq_ref).sum().item()),
+        "act_scale_max_rel_err": float(((sx - sc[:, 0]).abs() / sc[:, 0]).max().item()),
+        "fused_vs_unfused_int8_max_abs": float((y - ref_int8).abs().max().item()),
+        "fused_vs_unfused_int8_rel": float(((y - ref_int8).norm() / ref_int8.norm()).item()),
+        "int8_vs_bf16_rel_outlier30x": float(((y - ref_bf16).norm() / ref_bf16.norm()).item()),
+        "int8_vs_bf16_rel_plain": float(((y_plain - ref_plain).norm() / ref_plain.norm()).item()),
+        "smallM_fused_vs_unfused_rel": float(((ys - rs).norm() / rs.norm()).item()),
+        "3d_input_ok": bool(torch.equal(q(x3).reshape(2048, -1), q(x[:2048]))),
+    }
+    rep["act_quant_mismatch_frac"] = rep["act_quant_mismatch_elems"] / x.numel()
+    print("[int8_exec] selftest:", rep, flush=True)
+    assert rep["act_quant_mismatch_frac"] <= 1e-4, rep
+    assert rep["fused_vs_unfused_int8_rel"] < 1e-3 and rep["int8_vs_bf16_rel_plain"] < 2e-2, rep
+    assert rep["smallM_fused_vs_unfused_rel"] < 1e-3 and rep["3d_input_ok"], rep
+    ops.check_device_status(dev)
+    del lin, q, x, ref_bf16, ref_int8, y, x_plain, y_plain, ref_plain
+    torch.cuda.empty_cache()
+    out = {"selftest": rep, "gpu": torch.cuda.get_device_name(), "per_M": {}}
+    for M in Ms:
+        tot = {"bf16_ms": 0.0, "int8_fused_ms": 0.0, "quant_ms": 0.0, "gemm_fused_ms": 0.0}
+        per_shape = {}
+        for (K, N), cnt in FLUX_TOKEN_SHAPES.items():
+            lin = nn.Linear(K, N, bias=True).to(dev, torch.bfloat16)
+            x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            q = Int8Linear(lin, device=torch.device(dev))
+            b = _bench(lambda: F.linear(x, lin.weight, lin.bias), iters)
+            f = _bench(lambda: q(x), iters)
+            xq, sx = quant_rows(x)
+            qq = _bench(lambda: quant_rows(x), iters)
+            tg = _bench(lambda: int8_gemm_fused(xq, sx, q.weight_int8, q.w_scale, q.bias, torch.bfloat16), iters)
+            per_shape[f"{K}x{N}"] = {"count": cnt, "bf16_ms": round(b, 3), "int8_fused_ms": round(f, 3),
+                                     "quant_ms": round(qq, 3), "gemm_fused_ms": round(tg, 3),
+                                     "speedup": round(b / f, 3),
+                                     "gemm_tops": round(2.0 * M * N * K / (tg * 1e-3) / 1e12, 1)}
+            tot["bf16_ms"] += b * cnt; tot["int8_fused_ms"] += f * cnt
+            tot["quant_ms"] += qq * cnt; tot["gemm_fused_ms"] += tg * cnt
+            del lin, x, q, xq, sx
+            torch.cuda.empty_cache()
+        tot = {k: round(v, 2) for k, v in tot.items()}
+        tot["speedup_fused_vs_bf16"] = round(tot["bf16_ms"] / tot["int8_fused_ms"], 3)
+        tot["per_shape"] = per_shape
+        out["per_M"][str(M)] = tot
+        print(f"[int8_exec] M={M}: bf16 {tot['bf16_ms']} ms | int8 {tot['int8_fused_ms']} ms "
+              f"(quant {tot['quant_ms']}, gemm {tot['gemm_fused_ms']}) -> x{tot['speedup_fused_vs_bf16']}", flush=True)
+    return out
+
+
+if __name__ == "__main__":
+    import argparse
+    import json
+    ap = argparse.ArgumentParser(description="INT8 kernel self-test and micro-benchmark on the FLUX token-level "
+                                             "Linear shapes (needs a B200).")
+    ap.add_argument("out", nargs="?", default=None, help="optional JSON path for the results")
+    ap.add_argument("--int8-backend", choices=BACKENDS, default=DEFAULT_BACKEND,
+                    help="accepted for compatibility; both names run the sm_100a library")
+    args = ap.parse_args()
+    set_backend(args.int8_backend)
+    res = selftest_and_bench()
+    res["int8_backend"] = BACKEND
+    if args.out:
+        with open(args.out, "w") as fh:
+            json.dump(res, fh, indent=1)
+        print(f"[int8_exec] saved {args.out}")

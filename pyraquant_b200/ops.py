@@ -1,0 +1,300 @@
+"""Torch-facing operators over the C ABI: each one allocates its outputs with torch, passes raw device
+pointers and torch's current CUDA stream to libpq_b200.so, and is registered as a torch custom op
+(namespace ``pq_b200``) with a fake implementation for shape propagation.
+
+CUDA tensors only: a CPU tensor raises AssertionError, as the reference's ``quant_rows`` does
+(deploy/int8_exec.py:221).  There is no fallback implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+Tensor = torch.Tensor
+
+_DT = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16}
+_status_words: Dict[int, Tensor] = {}
+
+
+def _dt(dtype: torch.dtype) -> int:
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise TypeError(f"pq_b200 supports bfloat16 and float16, got {dtype}") from None
+
+
+def _stream(t: Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t: Optional[Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def status_word(device: torch.device) -> Tensor:
+    """Per-device workspace whose word 0 the GEMM kernels set when a bounded wait gives up."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(_lib.GEMM_WORKSPACE_BYTES // 4, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = w
+    return w
+
+
+def check_device_status(device=None, clear: bool = True) -> None:
+    """Synchronises and raises RuntimeError if any GEMM launched so far on `device` gave up a wait."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = status_word(dev)
+    raw = ctypes.c_int32(0)
+    with torch.cuda.device(dev):
+        rc = _lib.load().pq_read_status_word(w.data_ptr(), ctypes.byref(raw), int(clear),
+                                             torch.cuda.current_stream(dev).cuda_stream)
+    if rc == _lib.PQ_ERR_TIMEOUT:
+        raise RuntimeError(f"pq_b200: a device-side wait gave up (status word 0x{raw.value & 0xffffffff:08x})")
+    _lib.check(rc, "pq_read_status_word")
+
+
+def _rows_ok(x2: Tensor) -> Tensor:
+    """Row-strided views are consumed in place; anything the kernels cannot address is made contiguous."""
+    assert x2.dim() == 2 and x2.is_cuda
+    if x2.stride(1) != 1 or (x2.shape[0] > 1 and x2.stride(0) % 8 != 0) or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    return x2
+
+
+# ------------------------------------------------------------------------------------------------ quantisation
+def _quant_rows_impl(x2: Tensor) -> Tuple[Tensor, Tensor]:
+    x2 = _rows_ok(x2)
+    M, K = x2.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=x2.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x2.device)
+    ld = x2.stride(0) if M > 1 else max(K, x2.stride(0))
+    with torch.cuda.device(x2.device):
+        rc = _lib.load().pq_quant_rows(x2.data_ptr(), _dt(x2.dtype), M, K, ld, q.data_ptr(), s.data_ptr(), _stream(x2))
+    _lib.check(rc, f"pq_quant_rows(M={M}, K={K})")
+    return q, s
+
+
+def _quant_rows_g32_impl(x2: Tensor) -> Tuple[Tensor, Tensor]:
+    x2 = _rows_ok(x2)
+    M, K = x2.shape
+    assert K % 32 == 0, K
+    q = torch.empty((M, K), dtype=torch.int8, device=x2.device)
+    s = torch.empty((M, K // 32), dtype=torch.float32, device=x2.device)
+    ld = x2.stride(0) if M > 1 else max(K, x2.stride(0))
+    with torch.cuda.device(x2.device):
+        rc = _lib.load().pq_quant_rows_g32(x2.data_ptr(), _dt(x2.dtype), M, K, ld, q.data_ptr(), s.data_ptr(),
+                                           _stream(x2))
+    _lib.check(rc, f"pq_quant_rows_g32(M={M}, K={K})")
+    return q, s
+
+
+def _gather_quant_rows_impl(canvas: Tensor, row_idx: Tensor) -> Tuple[Tensor, Tensor]:
+    canvas = _rows_ok(canvas)
+    assert row_idx.is_cuda and row_idx.dtype == torch.int32 and row_idx.dim() == 1 and row_idx.is_contiguous()
+    rows, K = canvas.shape
+    M = row_idx.numel()
+    q = torch.empty((M, K), dtype=torch.int8, device=canvas.device)
+    s = torch.empty((M,), dtype=torch.float32, device=canvas.device)
+    with torch.cuda.device(canvas.device):
+        rc = _lib.load().pq_gather_quant_rows(canvas.data_ptr(), _dt(canvas.dtype), rows, K, max(K, canvas.stride(0)),
+                                              row_idx.data_ptr(), M, q.data_ptr(), s.data_ptr(), _stream(canvas))
+    _lib.check(rc, f"pq_gather_quant_rows(M={M}, K={K})")
+    return q, s
+
+
+def _gather_rows_impl(canvas: Tensor, row_idx: Tensor) -> Tensor:
+    canvas = _rows_ok(canvas)
+    assert row_idx.is_cuda and row_idx.dtype == torch.int32 and row_idx.dim() == 1 and row_idx.is_contiguous()
+    rows, K = canvas.shape
+    M = row_idx.numel()
+    out = torch.empty((M, K), dtype=canvas.dtype, device=canvas.device)
+    with torch.cuda.device(canvas.device):
+        rc = _lib.load().pq_gather_rows(canvas.data_ptr(), _dt(canvas.dtype), rows, K, max(K, canvas.stride(0)),
+                                        row_idx.data_ptr(), M, out.data_ptr(), K, _stream(canvas))
+    _lib.check(rc, f"pq_gather_rows(M={M}, K={K})")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias: Optional[Tensor],
+               t: Optional[Tensor], lb: Optional[Tensor], out_dtype: torch.dtype,
+               dbg_acc: Optional[Tensor] = None, w_lo: Optional[Tensor] = None, s_lo: Optional[Tensor] = None,
+               m_hi: Optional[int] = None) -> Tensor:
+    assert xq.is_cuda and xq.dtype == torch.int8 and xq.dim() == 2 and xq.stride(1) == 1
+    assert w_int8.dtype == torch.int8 and w_int8.dim() == 2 and w_int8.stride(1) == 1
+    M, K = xq.shape
+    N = w_int8.shape[0]
+    assert w_int8.shape[1] == K, (w_int8.shape, K)
+    assert K % 16 == 0, f"K={K} must be a multiple of 16"
+    assert s_row.dtype == torch.float32 and w_scale.dtype == torch.float32
+    s_row = s_row.contiguous(); w_scale = w_scale.contiguous()
+    if bias is not None:
+        assert bias.dtype == torch.float32
+        bias = bias.contiguous()
+    if xq.stride(0) % 16 != 0 or xq.data_ptr() % 16 != 0:
+        xq = xq.contiguous()
+    if w_int8.stride(0) % 16 != 0 or w_int8.data_ptr() % 16 != 0:
+        w_int8 = w_int8.contiguous()
+    out = torch.empty((M, N), dtype=out_dtype, device=xq.device)
+    R = 0
+    ldt = ldb = 0
+    if t is not None:
+        assert lb is not None and t.dtype == out_dtype and lb.dtype == out_dtype, (t.dtype, lb.dtype, out_dtype)
+        if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+            t = t.contiguous()
+        if lb.stride(1) != 1 or lb.stride(0) % 8 != 0 or lb.data_ptr() % 16 != 0:
+            lb = lb.contiguous()
+        R = t.shape[1]
+        ldt, ldb = t.stride(0), lb.stride(0)
+        if M == 1:
+            ldt = max(ldt, R)
+    ws = status_word(xq.device)
+    lib = _lib.load()
+    ldx = xq.stride(0) if M > 1 else max(K, xq.stride(0))
+    with torch.cuda.device(xq.device):
+        if w_lo is None:
+            rc = lib.pq_int8_gemm(xq.data_ptr(), ldx, s_row.data_ptr(), w_int8.data_ptr(), w_int8.stride(0),
+                                  w_scale.data_ptr(), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, R, _dt(out_dtype),
+                                  out.data_ptr(), _dt(out_dtype), N, M, N, K, ws.data_ptr(), ws.numel() * 4,
+                                  _ptr(dbg_acc), _stream(xq))
+        else:
+            assert w_lo.shape == w_int8.shape and w_lo.stride() == w_int8.stride() and s_lo is not None
+            rc = lib.pq_int8_gemm_grouped(xq.data_ptr(), ldx, s_row.data_ptr(), w_int8.data_ptr(),
+                                          w_scale.data_ptr(), w_lo.data_ptr(), s_lo.contiguous().data_ptr(),
+                                          w_int8.stride(0), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, R,
+                                          _dt(out_dtype), out.data_ptr(), _dt(out_dtype), N, int(m_hi), M, N, K,
+                                          ws.data_ptr(), ws.numel() * 4, _stream(xq))
+    _lib.check(rc, f"pq_int8_gemm(M={M}, N={N}, K={K})")
+    return out
+
+
+def _dequant_epilogue_impl(acc: Tensor, s_row: Tensor, s_col: Tensor, bias: Optional[Tensor],
+                           out_dtype: torch.dtype) -> Tensor:
+    assert acc.is_cuda and acc.dtype == torch.int32 and acc.is_contiguous()
+    M, N = acc.shape
+    out = torch.empty((M, N), dtype=out_dtype, device=acc.device)
+    with torch.cuda.device(acc.device):
+        rc = _lib.load().pq_dequant_epilogue(acc.data_ptr(), s_row.contiguous().data_ptr(),
+                                             s_col.contiguous().data_ptr(), _ptr(bias), out.data_ptr(),
+                                             _dt(out_dtype), M, N, _stream(acc))
+    _lib.check(rc, "pq_dequant_epilogue")
+    return out
+
+
+def _scatter_rows_impl(y: Tensor, tokens: Tensor, ptr: Tensor, src: Tensor, beta: Tensor, canvas: Tensor) -> None:
+    assert y.is_cuda and canvas.is_cuda and y.dtype == canvas.dtype and y.dim() == 2 and canvas.dim() == 2
+    assert y.stride(1) == 1 and canvas.stride(1) == 1 and y.shape[1] == canvas.shape[1]
+    for v in (tokens, ptr, src):
+        assert v.is_cuda and v.dtype == torch.int32 and v.is_contiguous()
+    assert beta.is_cuda and beta.dtype == torch.float32 and beta.is_contiguous()
+    n_tokens = tokens.numel()
+    assert ptr.numel() == n_tokens + 1 and src.numel() == beta.numel()
+    with torch.cuda.device(canvas.device):
+        rc = _lib.load().pq_scatter_rows(y.data_ptr(), max(y.stride(0), y.shape[1]), y.shape[0], tokens.data_ptr(),
+                                         ptr.data_ptr(), src.data_ptr(), beta.data_ptr(), n_tokens,
+                                         canvas.data_ptr(), max(canvas.stride(0), canvas.shape[1]), canvas.shape[0],
+                                         canvas.shape[1], _dt(canvas.dtype), _stream(canvas))
+    _lib.check(rc, "pq_scatter_rows")
+
+
+# ------------------------------------------------------------------------------------------------ custom ops
+# torch.library schemas cannot carry torch.dtype arguments portably, so out_dtype travels as the dtype code.
+_CODE2DT = {_lib.DTYPE_BF16: torch.bfloat16, _lib.DTYPE_FP16: torch.float16}
+
+
+@torch.library.custom_op("pq_b200::quant_rows", mutates_args=(), device_types="cuda")
+def quant_rows_op(x2: Tensor) -> Tuple[Tensor, Tensor]:
+    return _quant_rows_impl(x2)
+
+
+@quant_rows_op.register_fake
+def _(x2):
+    return x2.new_empty(x2.shape, dtype=torch.int8), x2.new_empty((x2.shape[0],), dtype=torch.float32)
+
+
+@torch.library.custom_op("pq_b200::quant_rows_g32", mutates_args=(), device_types="cuda")
+def quant_rows_g32_op(x2: Tensor) -> Tuple[Tensor, Tensor]:
+    return _quant_rows_g32_impl(x2)
+
+
+@quant_rows_g32_op.register_fake
+def _(x2):
+    return (x2.new_empty(x2.shape, dtype=torch.int8),
+            x2.new_empty((x2.shape[0], x2.shape[1] // 32), dtype=torch.float32))
+
+
+@torch.library.custom_op("pq_b200::gather_quant_rows", mutates_args=(), device_types="cuda")
+def gather_quant_rows_op(canvas: Tensor, row_idx: Tensor) -> Tuple[Tensor, Tensor]:
+    return _gather_quant_rows_impl(canvas, row_idx)
+
+
+@gather_quant_rows_op.register_fake
+def _(canvas, row_idx):
+    M = row_idx.shape[0]
+    return canvas.new_empty((M, canvas.shape[1]), dtype=torch.int8), canvas.new_empty((M,), dtype=torch.float32)
+
+
+@torch.library.custom_op("pq_b200::gather_rows", mutates_args=(), device_types="cuda")
+def gather_rows_op(canvas: Tensor, row_idx: Tensor) -> Tensor:
+    return _gather_rows_impl(canvas, row_idx)
+
+
+@gather_rows_op.register_fake
+def _(canvas, row_idx):
+    return canvas.new_empty((row_idx.shape[0], canvas.shape[1]))
+
+
+@torch.library.custom_op("pq_b200::int8_gemm", mutates_args=(), device_types="cuda")
+def int8_gemm_op(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias: Optional[Tensor],
+                 t: Optional[Tensor], lb: Optional[Tensor], out_dtype_code: int) -> Tensor:
+    return _gemm_impl(xq, s_row, w_int8, w_scale, bias, t, lb, _CODE2DT[out_dtype_code])
+
+
+@int8_gemm_op.register_fake
+def _(xq, s_row, w_int8, w_scale, bias, t, lb, out_dtype_code):
+    return xq.new_empty((xq.shape[0], w_int8.shape[0]), dtype=_CODE2DT[out_dtype_code])
+
+
+@torch.library.custom_op("pq_b200::int8_gemm_grouped", mutates_args=(), device_types="cuda")
+def int8_gemm_grouped_op(xq: Tensor, s_row: Tensor, w_hi: Tensor, s_hi: Tensor, w_lo: Tensor, s_lo: Tensor,
+                         bias: Optional[Tensor], t: Optional[Tensor], lb: Optional[Tensor], m_hi: int,
+                         out_dtype_code: int) -> Tensor:
+    return _gemm_impl(xq, s_row, w_hi, s_hi, bias, t, lb, _CODE2DT[out_dtype_code], None, w_lo, s_lo, m_hi)
+
+
+@int8_gemm_grouped_op.register_fake
+def _(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, m_hi, out_dtype_code):
+    return xq.new_empty((xq.shape[0], w_hi.shape[0]), dtype=_CODE2DT[out_dtype_code])
+
+
+@torch.library.custom_op("pq_b200::dequant_epilogue", mutates_args=(), device_types="cuda")
+def dequant_epilogue_op(acc: Tensor, s_row: Tensor, s_col: Tensor, bias: Optional[Tensor],
+                        out_dtype_code: int) -> Tensor:
+    return _dequant_epilogue_impl(acc, s_row, s_col, bias, _CODE2DT[out_dtype_code])
+
+
+@dequant_epilogue_op.register_fake
+def _(acc, s_row, s_col, bias, out_dtype_code):
+    return acc.new_empty(acc.shape, dtype=_CODE2DT[out_dtype_code])
+
+
+@torch.library.custom_op("pq_b200::scatter_rows_", mutates_args=("canvas",), device_types="cuda")
+def scatter_rows_op(y: Tensor, tokens: Tensor, ptr: Tensor, src: Tensor, beta: Tensor, canvas: Tensor) -> None:
+    _scatter_rows_impl(y, tokens, ptr, src, beta, canvas)
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    return _dt(dtype)
+
+
+def int8_gemm_debug(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias: Optional[Tensor],
+                    t: Optional[Tensor], lb: Optional[Tensor], out_dtype: torch.dtype) -> Tuple[Tensor, Tensor]:
+    """GEMM that also returns the raw int32 accumulators (parity tests)."""
+    acc = torch.full((xq.shape[0], w_int8.shape[0]), -2**31, dtype=torch.int32, device=xq.device)
+    out = _gemm_impl(xq, s_row, w_int8, w_scale, bias, t, lb, out_dtype, dbg_acc=acc)
+    return out, acc

@@ -1,0 +1,93 @@
+"""The C-ABI shared library: it loads, exports every symbol include/pq_b200.h declares, and its
+host-side argument checks reject bad calls before anything is launched (no GPU needed)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from pyraquant_b200 import _lib
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "pq_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported_and_bound():
+    lib = _lib.load()
+    names = declared_symbols()
+    assert "pq_int8_gemm" in names and "pq_quant_rows" in names
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in pq_b200.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes prototype"
+    assert set(_lib.SIGNATURES) == set(names)
+
+
+def test_version_and_status_strings():
+    lib = _lib.load()
+    assert lib.pq_version() >= 100
+    assert _lib.status_str(0) == "ok"
+    assert "NULL" in _lib.status_str(1)
+    assert "unknown" in _lib.status_str(999)
+
+
+def test_options_roundtrip():
+    old = _lib.get_option("gemm_group_m")
+    _lib.set_option("gemm_group_m", 4)
+    assert _lib.get_option("gemm_group_m") == 4
+    _lib.set_option("gemm_group_m", old)
+    with pytest.raises(RuntimeError):
+        _lib.set_option("no_such_knob", 1)
+
+
+def test_quant_rows_argument_checks():
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf)
+    p16 = (p + 15) & ~15
+    assert lib.pq_quant_rows(None, 0, 0, 64, 64, None, None, None) == 0            # M == 0: no-op
+    assert lib.pq_quant_rows(None, 0, 4, 64, 64, p16, p16, None) == 1              # null x
+    assert lib.pq_quant_rows(p16, 7, 4, 64, 64, p16, p16, None) == 4               # bad dtype
+    assert lib.pq_quant_rows(p16, 0, 4, 60, 64, p16, p16, None) == 3               # K % 8
+    assert lib.pq_quant_rows(p16, 0, 4, 64, 32, p16, p16, None) == 2               # ldx < K
+    assert lib.pq_quant_rows(p16 + 2, 0, 4, 64, 64, p16, p16, None) == 3           # misaligned x
+    assert lib.pq_quant_rows(p16, 0, -1, 64, 64, p16, p16, None) == 2              # negative M
+    assert lib.pq_quant_rows_g32(p16, 0, 4, 72, 72, p16, p16, None) == 3           # K % 32
+
+
+def test_gemm_argument_checks():
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(4096)
+    p16 = (ctypes.addressof(buf) + 15) & ~15
+
+    def gemm(xq=p16, ldx=64, s_row=p16, w=p16, ldw=64, s_col=p16, bias=None, t=None, ldt=0, lb=None, ldb=0, R=0,
+             lr_dtype=0, out=p16, out_dtype=0, ldo=64, M=8, N=64, K=64, ws=None, ws_bytes=0):
+        return lib.pq_int8_gemm(xq, ldx, s_row, w, ldw, s_col, bias, t, ldt, lb, ldb, R, lr_dtype, out, out_dtype,
+                                ldo, M, N, K, ws, ws_bytes, None, None)
+
+    assert gemm(M=0) == 0
+    assert gemm(xq=None) == 1
+    assert gemm(K=40, ldx=48, ldw=48) == 3          # K % 16
+    assert gemm(ldx=72) == 3                         # ldx % 16
+    assert gemm(out_dtype=5) == 4
+    assert gemm(ldo=32) == 2                         # ldo < N
+    assert gemm(t=p16, ldt=32) == 1                  # t without lb
+    assert gemm(t=p16, ldt=16, lb=p16, ldb=64, R=16) == 7    # rank other than 32
+    assert gemm(ws=p16, ws_bytes=8) == 8             # workspace too small
+    assert gemm(N=0) == 2
+
+
+def test_scatter_and_gather_argument_checks():
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(4096)
+    p16 = (ctypes.addressof(buf) + 15) & ~15
+    assert lib.pq_scatter_rows(p16, 64, 4, p16, p16, p16, p16, 0, p16, 64, 16, 64, 0, None) == 0   # nothing to do
+    assert lib.pq_scatter_rows(p16, 64, 4, p16, p16, p16, p16, 2, p16, 64, 16, 60, 0, None) == 3   # C % 8
+    assert lib.pq_scatter_rows(p16, 64, 4, None, p16, p16, p16, 2, p16, 64, 16, 64, 0, None) == 1
+    assert lib.pq_gather_rows(p16, 0, 16, 64, 64, None, 4, p16, 64, None) == 1
+    assert lib.pq_gather_quant_rows(p16, 0, 16, 64, 64, None, 4, p16, p16, None) == 1
+    assert lib.pq_i8_mma_issue_loop(0, 10, p16, None, 0, None) == 2

@@ -1,0 +1,387 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on identical seeded inputs.
+
+Bars: int8 codes, fp32 scales, int32 accumulators and all index work bit-exact; 16-bit outputs within
+max-rel-err 1e-2 of the exact dequantised math (fp64), where
+    rel = |y - ref| / max(|ref|, 1e-3 * max|ref|).
+"""
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from conftest import from_bf16_bits
+from oracle import oracle
+from pyraquant_b200 import _lib, int8_exec, ops, routing
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def max_rel_err(y: torch.Tensor, ref64: torch.Tensor) -> float:
+    ref = ref64.double()
+    denom = torch.maximum(ref.abs(), 1e-3 * ref.abs().max())
+    return float(((y.double() - ref).abs() / denom).max())
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(cuda_dev):
+    yield
+    ops.check_device_status(cuda_dev)
+
+
+def rand_act(M, K, dtype, seed, outliers=True):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    if outliers and K >= 16:
+        x[:, torch.randperm(K, generator=g)[: max(1, K // 200)]] *= 20.0
+    return x.to(dtype)
+
+
+# ------------------------------------------------------------------------------------------------ quantisation
+@pytest.mark.parametrize("M,K", [(1, 64), (8, 64), (17, 640), (154, 1280), (513, 2048), (4350, 3072),
+                                 (300, 5120), (200, 10240), (130, 12288), (96, 15360), (5, 20480), (33, 8)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_quant_rows_bit_exact(cuda_dev, M, K, dtype):
+    x = rand_act(M, K, dtype, 100 + M + K)
+    if M > 3:
+        x[2].zero_()                          # all-zero token -> 1e-8 floor
+        x[3] = x[3].abs().max()               # constant row: every code is 127
+    q, s = int8_exec.quant_rows(x.to(cuda_dev))
+    qo, so = oracle.quant_rows(x)
+    assert q.dtype == torch.int8 and s.dtype == torch.float32 and q.shape == (M, K) and s.shape == (M,)
+    assert torch.equal(s.cpu(), so)
+    assert torch.equal(q.cpu(), qo)
+
+
+def test_quant_rows_cfg0_full(cuda_dev):
+    L = oracle.make_layer(0, 4608, 3072, 8, lowrank=False, bias=False)
+    q, s = int8_exec.quant_rows(L["x"].to(cuda_dev))
+    qo, so = oracle.quant_rows(L["x"])
+    assert torch.equal(s.cpu(), so) and torch.equal(q.cpu(), qo)
+
+
+def test_quant_rows_strided_rows_and_views(cuda_dev):
+    x = rand_act(64, 3072 + 1024, torch.bfloat16, 7).to(cuda_dev)
+    view = x[:, 1024:]                                    # row stride 4096, offset 2048 bytes
+    q, s = int8_exec.quant_rows(view)
+    qo, so = oracle.quant_rows(view.cpu())
+    assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+    odd = x[:, 3:3 + 64]                                  # misaligned start: falls back to a copy, same result
+    q2, s2 = int8_exec.quant_rows(odd)
+    qo2, so2 = oracle.quant_rows(odd.cpu())
+    assert torch.equal(q2.cpu(), qo2) and torch.equal(s2.cpu(), so2)
+    tr = x[:32, :32].t()                                  # last dim not contiguous
+    q3, _ = int8_exec.quant_rows(tr)
+    assert torch.equal(q3.cpu(), oracle.quant_rows(tr.cpu())[0])
+
+
+def test_quant_rows_empty(cuda_dev):
+    q, s = int8_exec.quant_rows(torch.empty(0, 64, dtype=torch.bfloat16, device=cuda_dev))
+    assert q.shape == (0, 64) and s.shape == (0,)
+
+
+def test_quant_rows_ties_exact(cuda_dev):
+    # rows built so that many quotients land exactly on or next to .5: amax = 127 * 2^e makes scale a power of two
+    base = torch.arange(-254, 255, dtype=torch.float32) * 0.5            # includes every k + 0.5
+    rows = []
+    for e in (-3, 0, 2):
+        r = base * 2.0 ** e
+        r = torch.cat([r, torch.tensor([127.0 * 2.0 ** e])])
+        rows.append(torch.nn.functional.pad(r, (0, 512 - r.numel())))
+    x = torch.stack(rows).to(torch.bfloat16)
+    q, s = int8_exec.quant_rows(x.to(cuda_dev))
+    qo, so = oracle.quant_rows(x)
+    assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+
+
+@pytest.mark.parametrize("M,K", [(9, 64), (300, 640), (257, 1280), (64, 5120), (31, 2560)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_quant_rows_g32_bit_exact(cuda_dev, M, K, dtype):
+    x = rand_act(M, K, dtype, 200 + M + K)
+    x[0, :32] = 0
+    q, s = int8_exec.quant_rows_g32(x.to(cuda_dev))
+    qo, so = oracle.quant_rows_g32(x)
+    assert s.shape == (M, K // 32)
+    assert torch.equal(s.cpu(), so) and torch.equal(q.cpu(), qo)
+
+
+def test_gather_quant_rows_bit_exact(cuda_dev):
+    canvas = rand_act(1024, 3072, torch.bfloat16, 11)
+    g = torch.Generator().manual_seed(5)
+    idx = torch.randint(0, 1024, (777,), generator=g, dtype=torch.int32)
+    idx[5] = -1; idx[100] = -1; idx[776] = 1023; idx[0] = 0
+    q, s = int8_exec.gather_quant_rows(canvas.to(cuda_dev), idx.to(cuda_dev))
+    src = canvas[idx.clamp_min(0).long()].clone()
+    src[idx < 0] = 0
+    qo, so = oracle.quant_rows(src)
+    assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+    plain = torch.ops.pq_b200.gather_rows(canvas.to(cuda_dev), idx.to(cuda_dev))
+    assert torch.equal(plain.cpu(), src)
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+def run_gemm_case(dev, M, N, K, *, lowrank, bias, dtype=torch.bfloat16, seed=0, epilogue=None, extreme=False):
+    g = torch.Generator().manual_seed(seed)
+    if extreme:
+        xq = torch.full((M, K), 127, dtype=torch.int8); xq[::2] = -127
+        wq = torch.full((N, K), 127, dtype=torch.int8); wq[1::3] = -127
+    else:
+        xq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
+        wq = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8)
+    sr = torch.rand(M, generator=g) * 0.05 + 0.001
+    sc = torch.rand(N, generator=g) * 0.002 + 0.0001
+    b = torch.randn(N, generator=g) * 0.01 if bias else None
+    t = lb = None
+    if lowrank:
+        t = (torch.randn(M, 32, generator=g) * 1.0).to(dtype)
+        lb = (torch.randn(32, N, generator=g) * 0.02).to(dtype)
+    if epilogue is not None:
+        _lib.set_option("gemm_epilogue", epilogue)
+    try:
+        to = lambda v: None if v is None else v.to(dev)
+        out, acc = ops.int8_gemm_debug(to(xq), to(sr), to(wq), to(sc), to(b), to(t), to(lb), dtype)
+        torch.cuda.synchronize()
+    finally:
+        if epilogue is not None:
+            _lib.set_option("gemm_epilogue", 1)
+    acc_ref = oracle.int_mm(xq, wq)
+    assert torch.equal(acc.cpu(), acc_ref), f"int32 accumulators differ at {(acc.cpu() != acc_ref).sum().item()} places"
+    ref64 = oracle.exact_dequant_f64(acc_ref, sr, sc, b, t, lb)
+    err = max_rel_err(out.cpu(), ref64)
+    assert err <= TOL, err
+    # against the fp32 restatement of the kernel's epilogue the gap is rounding noise only
+    y32 = oracle.epilogue(acc_ref, sr, sc, b, t, lb, dtype)
+    assert max_rel_err(out.cpu(), y32.double()) <= 8e-3
+    return out
+
+
+@pytest.mark.parametrize("epilogue", [0, 1])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (1, 256, 64), (8, 128, 64), (17, 384, 192), (154, 640, 640),
+                                   (300, 512, 1280), (1000, 3072, 512), (257, 1280, 2560)])
+def test_gemm_small_shapes(cuda_dev, epilogue, M, N, K):
+    run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=True, seed=M + N + K, epilogue=epilogue)
+    run_gemm_case(cuda_dev, M, N, K, lowrank=False, bias=False, seed=M + N + K + 1, epilogue=epilogue)
+
+
+@pytest.mark.parametrize("epilogue", [0, 1])
+def test_gemm_extreme_accumulators_exact(cuda_dev, epilogue):
+    # |acc| = K * 127^2 = 2.0e8 > 2^24: only true int32 accumulation gets this right
+    run_gemm_case(cuda_dev, 256, 512, 12288, lowrank=False, bias=True, extreme=True, epilogue=epilogue)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("lowrank,bias", [(True, True), (True, False), (False, True)])
+def test_gemm_dtypes_and_options(cuda_dev, dtype, lowrank, bias):
+    run_gemm_case(cuda_dev, 777, 768, 1024, lowrank=lowrank, bias=bias, dtype=dtype, seed=3)
+
+
+@pytest.mark.parametrize("bn,stages", [(128, 2), (128, 4), (128, 6), (256, 2), (256, 3), (256, 4)])
+def test_gemm_tile_variants(cuda_dev, bn, stages):
+    _lib.set_option("gemm_block_n", bn); _lib.set_option("gemm_stages", stages)
+    try:
+        run_gemm_case(cuda_dev, 1500, 1024, 768, lowrank=True, bias=True, seed=bn + stages)
+    finally:
+        _lib.set_option("gemm_block_n", 0); _lib.set_option("gemm_stages", 0)
+
+
+def test_gemm_persistent_many_tiles_per_cta(cuda_dev):
+    # few CTAs, many tiles each: exercises the accumulator double buffer and barrier phases
+    _lib.set_option("gemm_max_ctas", 3)
+    try:
+        run_gemm_case(cuda_dev, 2000, 2048, 384, lowrank=True, bias=True, seed=9)
+    finally:
+        _lib.set_option("gemm_max_ctas", 0)
+
+
+def test_gemm_cfg0_layer(cuda_dev):
+    """BASELINE config 0: M=4608, K=N=3072, rank-32 branch and bias, through Int8Linear.forward."""
+    L = oracle.make_layer(0, 4608, 3072, 3072)
+    lin = nn.Linear(3072, 3072, bias=True).to(torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.copy_(L["w"]); lin.bias.copy_(L["bias"].to(torch.bfloat16))
+    q = int8_exec.Int8Linear(lin, device=cuda_dev, lowrank=(L["lr_A"], L["lr_B"]))
+    wq, ws = oracle.quant_weight(L["w"])
+    assert torch.equal(q.weight_int8.cpu(), wq) and torch.equal(q.w_scale.cpu(), ws)
+    x = L["x"].to(cuda_dev)
+    y = q(x)
+    assert y.dtype == torch.bfloat16 and y.shape == (4608, 3072)
+    # integer stages bit-exact
+    xq, sx = int8_exec.quant_rows(x)
+    xqo, sxo = oracle.quant_rows(L["x"])
+    assert torch.equal(xq.cpu(), xqo) and torch.equal(sx.cpu(), sxo)
+    t_gpu = (x @ q.lr_A)
+    _, acc = ops.int8_gemm_debug(xq, sx, q.weight_int8, q.w_scale, q.bias, t_gpu, q.lr_B, torch.bfloat16)
+    acc_ref = oracle.int_mm(xqo, wq)
+    assert torch.equal(acc.cpu(), acc_ref)
+    # output against the exact dequantised math and against the restated forward
+    bias32 = lin.bias.detach().float()
+    t_ref = (L["x"].float() @ L["lr_A"].float()).to(torch.bfloat16)
+    ref64 = oracle.exact_dequant_f64(acc_ref, sxo, ws, bias32, t_ref, L["lr_B"])
+    assert max_rel_err(y.cpu(), ref64) <= TOL
+    y_or = oracle.int8_linear_forward(L["x"], wq, ws, bias32, L["lr_A"], L["lr_B"])
+    rel_l2 = ((y.cpu().float() - y_or.float()).norm() / y_or.float().norm()).item()
+    assert rel_l2 < 1e-3, rel_l2
+    # 3-D input gives the same rows (reference self-test vi)
+    y3 = q(x[:2048].reshape(8, 256, 3072))
+    assert torch.equal(y3.reshape(2048, -1), q(x[:2048]))
+
+
+def test_gemm_grouped_two_tiers(cuda_dev):
+    g = torch.Generator().manual_seed(21)
+    M, N, K, m_hi = 1000, 768, 512, 389
+    xq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
+    w8 = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8)
+    s8 = torch.rand(N, generator=g) * 0.002 + 1e-4
+    w4, s4 = oracle.nested4_from_int8(w8, s8)
+    sr = torch.rand(M, generator=g) * 0.05 + 0.001
+    b = torch.randn(N, generator=g) * 0.01
+    t = torch.randn(M, 32, generator=g).to(torch.bfloat16)
+    lb = (torch.randn(32, N, generator=g) * 0.02).to(torch.bfloat16)
+    d = cuda_dev
+    for mh in (m_hi, 0, M, 128):
+        y = int8_exec.int8_gemm_grouped(xq.to(d), sr.to(d), w8.to(d), s8.to(d), w4.to(d), s4.to(d), b.to(d),
+                                        t.to(d), lb.to(d), mh, torch.bfloat16).cpu()
+        ref = torch.empty(M, N, dtype=torch.float64)
+        ref[:mh] = oracle.exact_dequant_f64(oracle.int_mm(xq[:mh], w8), sr[:mh], s8, b, t[:mh], lb) if mh else ref[:mh]
+        if mh < M:
+            ref[mh:] = oracle.exact_dequant_f64(oracle.int_mm(xq[mh:], w4), sr[mh:], s4, b, t[mh:], lb)
+        assert max_rel_err(y, ref) <= TOL, mh
+
+
+def test_dequant_epilogue_and_linear_2d(cuda_dev):
+    L = oracle.make_layer(5, 300, 512, 256, lowrank=False)
+    wq, ws = oracle.quant_weight(L["w"])
+    xq, sx = oracle.quant_rows(L["x"])
+    acc = oracle.int_mm(xq, wq)
+    d = cuda_dev
+    y = int8_exec.dequant_epilogue(acc.to(d), sx.to(d), ws.to(d), L["bias"].to(d), torch.bfloat16)
+    assert torch.equal(y.cpu(), oracle.epilogue(acc, sx, ws, L["bias"], None, None, torch.bfloat16))
+    for backend in (None, "triton", "cublas"):
+        y2 = int8_exec.int8_linear_2d(L["x"].to(d), wq.to(d), ws.to(d), L["bias"].to(d), backend=backend)
+        assert max_rel_err(y2.cpu(), oracle.exact_dequant_f64(acc, sx, ws, L["bias"], None, None)) <= TOL
+    with pytest.raises(ValueError):
+        int8_exec.int8_linear_2d(L["x"].to(d), wq.to(d), ws.to(d), None, backend="nope")
+
+
+def test_reference_selftest_assertions(cuda_dev):
+    """The reference's own numerical self-test (deploy/int8_exec.py:498-536) with its thresholds."""
+    rep = int8_exec.selftest_and_bench(Ms=())["selftest"]
+    assert rep["act_quant_mismatch_elems"] == 0 and rep["act_scale_max_rel_err"] == 0.0
+
+
+# ------------------------------------------------------------------------------------------------ full-size properties
+def test_full_size_quant_and_gemm_properties(cuda_dev):
+    """BASELINE config 2 row count (M = 65536 + 512) at K = 3072 -> N = 3072: sizes the CPU oracle cannot
+    finish quickly, so parity is checked through exact size-independent identities:
+      column checksum  sum_m acc[m,:] == (sum_m xq[m,:]) @ w^T        (int64, exact)
+      row checksum     sum_n acc[m,:] == xq[m,:] @ (sum_n w[n,:])     (int64, exact)
+    plus the per-row quantisation identities |x - q*s| <= s/2 and max|q| == 127."""
+    d = cuda_dev
+    M, K, N = 66048, 3072, 3072
+    g = torch.Generator(device=d).manual_seed(2)
+    x = torch.randn(M, K, generator=g, device=d, dtype=torch.float32)
+    x[:, ::211] *= 20.0
+    x = x.to(torch.bfloat16)
+    q, s = int8_exec.quant_rows(x)
+    xf = x.float()
+    s_ref = xf.abs().amax(1).clamp_min(1e-8) / 127
+    assert torch.equal(s, s_ref)
+    assert int(q.abs().amax(1).min()) == 127
+    assert bool(((xf - q.float() * s[:, None]).abs() <= s[:, None] * 0.5000001).all())
+    del xf
+    w = torch.randint(-127, 128, (N, K), generator=g, device=d, dtype=torch.int8)
+    sc = torch.rand(N, generator=g, device=d) * 1e-3 + 1e-4
+    out, acc = ops.int8_gemm_debug(q, s, w, sc, None, None, None, torch.bfloat16)
+    col = acc.sum(0, dtype=torch.int64).cpu()
+    row = acc.sum(1, dtype=torch.int64).cpu()
+    qs = q.sum(0, dtype=torch.int64).cpu()
+    ws = w.sum(0, dtype=torch.int64).cpu()
+    assert torch.equal(col, w.cpu().to(torch.int64) @ qs)
+    row_ref = torch.empty(M, dtype=torch.int64)
+    qc = q.cpu()
+    for i in range(0, M, 8192):
+        row_ref[i:i + 8192] = qc[i:i + 8192].to(torch.int64) @ ws
+    assert torch.equal(row, row_ref)
+    # output = rounding of acc * (s_row*s_col): recompute from the verified accumulators in chunks
+    for i in range(0, M, 16384):
+        ref = (acc[i:i + 16384].float() * (s[i:i + 16384, None] * sc[None, :])).to(torch.bfloat16)
+        assert torch.equal(out[i:i + 16384], ref)
+
+
+# ------------------------------------------------------------------------------------------------ gather / scatter
+def test_scatter_matches_reference_fixture(cuda_dev, golden):
+    g = golden("routing_gather_scatter.npz")
+    boxes = [tuple(b) for b in g["boxes"].tolist()]
+    bg = from_bf16_bits(g["background_bits"])
+    for prefix, halo, fb, bx, key in (("", 2, 1.0, boxes, "n_buckets"), ("h3_", 3, 0.75, boxes[:4], "h3_n_buckets")):
+        plan = routing.build_route_plan((24, 24), bx, halo, fusion_beta=fb)
+        y = torch.cat([from_bf16_bits(g[f"{prefix}bucket{i}_out_bits"]).reshape(-1, bg.shape[-1])
+                       for i in range(int(g[key]))])
+        fused = routing.fuse_rows(bg.to(cuda_dev), y.to(cuda_dev), plan)
+        assert torch.equal(fused.cpu(), from_bf16_bits(g[f"{prefix}fused_bits"]))
+    hidden = from_bf16_bits(g["hidden_bits"]).reshape(24 * 24, -1)
+    plan = routing.build_route_plan((24, 24), boxes, 2)
+    got = routing.gather_rows(hidden.to(cuda_dev), plan)
+    want = torch.cat([from_bf16_bits(g[f"bucket{i}_hidden_bits"]).reshape(-1, hidden.shape[1])
+                      for i in range(int(g["n_buckets"]))])
+    assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_routed_gather_scatter_vs_oracle(cuda_dev, dtype):
+    """64x64 token canvas, 8x8 leaves of 8 tokens, Bernoulli(0.3) selection, halo 2, C = 256."""
+    H = W = 64; C = 256
+    g = torch.Generator().manual_seed(4)
+    sel = (torch.rand(8, 8, generator=g) < 0.3).float().numpy()
+    boxes = routing.leaf_run_boxes(sel, 16)                     # leaf = 16 latent = 8 tokens
+    canvas = torch.randn(1, H, W, C, generator=g).to(dtype)
+    bg = torch.randn(1, H, W, C, generator=g).to(dtype)
+    plan = routing.build_route_plan((H, W), boxes, 2, dtype=dtype)
+    buckets = oracle.gather_buckets(canvas, boxes, 2)
+    want_rows = torch.cat([t.reshape(-1, C) for _hw, t, _g in buckets])
+    d = cuda_dev
+    rows = routing.gather_rows(canvas.reshape(H * W, C).to(d), plan)
+    assert torch.equal(rows.cpu(), want_rows)
+    q, s = routing.gather_quant_rows(canvas.reshape(H * W, C).to(d), plan)
+    qo, so = oracle.quant_rows(want_rows)
+    assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+    outs, ys = [], []
+    for hw, t, geoms in buckets:
+        o = (torch.randn(t.shape, generator=g) * 2).to(dtype)
+        outs.append(((hw, geoms), o)); ys.append(o.reshape(-1, C))
+    want = oracle.fuse_buckets(bg, outs, 1.0)
+    got = routing.fuse_rows(bg.to(d), torch.cat(ys).to(d), plan)
+    assert torch.equal(got.cpu(), want)
+    # untouched tokens are bit-identical to the background
+    touched = torch.zeros(H * W, dtype=torch.bool); touched[torch.from_numpy(plan.tokens).long()] = True
+    assert torch.equal(got.cpu().reshape(H * W, C)[~touched], bg.reshape(H * W, C)[~touched])
+
+
+def test_routed_two_tier_linear(cuda_dev):
+    """Config-4 shape in miniature: routed rows -> Linear with per-leaf hi/lo weights -> scatter."""
+    H = W = 32; K = 256; N = 512
+    g = torch.Generator().manual_seed(8)
+    sel = (torch.rand(4, 4, generator=g) < 0.4).float().numpy(); sel[0, 0] = 1; sel[1, 0] = 1
+    scores = torch.rand(4, 4, generator=g).numpy()
+    hi = routing.inner_split_median(scores, sel, 1.0)
+    tmap = routing.leaf_tier_to_token_map(hi, (H, W))
+    plan = routing.build_route_plan((H, W), routing.leaf_run_boxes(sel, 16), 2, token_tier_hi=tmap)
+    canvas = rand_act(H * W, K, torch.bfloat16, 31)
+    lin = nn.Linear(K, N, bias=True).to(torch.bfloat16)
+    A = (torch.randn(K, 32, generator=g) * 0.02).to(torch.bfloat16)
+    B = (torch.randn(32, N, generator=g) * 0.02).to(torch.bfloat16)
+    q = int8_exec.Int8LinearRouted(lin, device=cuda_dev, lowrank=(A, B))
+    y = q.forward_gathered(canvas.to(cuda_dev), plan.to(cuda_dev)["row_idx"], plan.m_hi).cpu()
+    rows = canvas[torch.from_numpy(plan.row_idx).long()]
+    w8, s8 = oracle.quant_weight(lin.weight.detach())
+    w4, s4 = oracle.nested4_from_int8(w8, s8)
+    xq, sx = oracle.quant_rows(rows)
+    t = (rows.float() @ A.float()).to(torch.bfloat16)
+    b32 = lin.bias.detach().float()
+    mh = plan.m_hi
+    ref = torch.cat([oracle.exact_dequant_f64(oracle.int_mm(xq[:mh], w8), sx[:mh], s8, b32, t[:mh], B),
+                     oracle.exact_dequant_f64(oracle.int_mm(xq[mh:], w4), sx[mh:], s4, b32, t[mh:], B)])
+    assert 0 < mh < plan.n_rows
+    assert max_rel_err(y, ref) <= TOL
+    y2 = q.forward_rows(rows.to(cuda_dev), mh).cpu()
+    assert max_rel_err(y2, ref) <= TOL
