@@ -52,10 +52,10 @@ namespace {
 int* option_slot(const char* key) {
   Options& o = options();
   if (key == nullptr) return nullptr;
-  if (std::strcmp(key, "gemm_epilogue") == 0) return &o.gemm_epilogue;
   if (std::strcmp(key, "gemm_stages") == 0) return &o.gemm_stages;
   if (std::strcmp(key, "gemm_block_n") == 0) return &o.gemm_block_n;
-  if (std::strcmp(key, "gemm_group_m") == 0) return &o.gemm_group_m;
+  if (std::strcmp(key, "gemm_pm") == 0) return &o.gemm_pm;
+  if (std::strcmp(key, "gemm_pn") == 0) return &o.gemm_pn;
   if (std::strcmp(key, "gemm_max_ctas") == 0) return &o.gemm_max_ctas;
   return nullptr;
 }

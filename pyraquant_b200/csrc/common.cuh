@@ -35,10 +35,10 @@ int sm_count();
 
 // Option table shared by the .cu files (see pq_set_option).
 struct Options {
-  int gemm_epilogue = 1;   // 0: one row per thread (32x32b loads, scalar low-rank), 1: fragment (16x256b, mma.sync low-rank)
   int gemm_stages = 0;     // 0 = auto
   int gemm_block_n = 0;    // 0 = auto, else 128 or 256
-  int gemm_group_m = 16;   // tile rasterisation: M tiles per group
+  int gemm_pm = 0;         // tile schedule override: CTA grid rows (0 = auto)
+  int gemm_pn = 0;         // tile schedule override: CTA grid columns (0 = auto)
   int gemm_max_ctas = 0;   // 0 = one per SM
 };
 Options& options();
@@ -239,18 +239,32 @@ __device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&v)
       : "memory");
 }
 
+// Same arrangement, 64 columns: v[4j..4j+3] belong to columns 8j..8j+7.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // legacy warp MMA used for the rank-32 low-rank term inside the GEMM epilogue
 // ---------------------------------------------------------------------------------------------
 template <bool BF16>
 __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   if constexpr (BF16) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   } else {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -261,6 +275,18 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t sme
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(smem_addr));
+}
+
+// ---------------------------------------------------------------------------------------------
+// conversions that stay off the (slow) conversion pipe
+// ---------------------------------------------------------------------------------------------
+// Correctly rounded int32 -> fp32 (same result as cvt.rn.f32.s32) from integer/FMA-pipe operations only:
+// v = hi * 2048 + lo with lo in [0, 2048) and |hi| <= 2^20; both halves convert exactly through the
+// "add a large power of two" trick and one fused multiply-add rounds the sum once.
+__device__ __forceinline__ float int_to_float_rn(int32_t v) {
+  const float fh = __int_as_float(0x4B400000 + (v >> 11)) - 12582912.0f;             // exact: |hi| < 2^22
+  const float fl = __int_as_float(0x4B000000 | (v & 0x7FF)) - 8388608.0f;            // exact: 0 <= lo < 2^23
+  return fmaf(fh, 2048.0f, fl);
 }
 
 // ---------------------------------------------------------------------------------------------

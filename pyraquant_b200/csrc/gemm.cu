@@ -1,15 +1,16 @@
 // Fused INT8 GEMM for sm_100a: out = float(xq @ w^T) * (s_row x s_col) (+ t @ lb) (+ bias).
 //
-// One persistent CTA per SM, 192 threads, three roles:
+// One persistent CTA per SM, 320 threads, three roles:
 //   warp 0      TMA producer: streams 128 x 128-byte tiles of xq and BN x 128-byte tiles of w into a
 //               ring of shared-memory stages (128-byte swizzle), one mbarrier pair per stage;
 //   warp 1      MMA issuer: one thread issues tcgen05.mma kind::i8 (128 x BN x 32 per instruction) from the
 //               staged tiles into an int32 accumulator in tensor memory; two accumulators alternate so
 //               that the next tile's main loop overlaps the previous tile's epilogue;
-//   warps 2-5   epilogue: read the accumulator back with tcgen05.ld, apply the row/column scales, add
-//               the rank-32 low-rank term (warp-level bf16 mma.sync on fragments that tcgen05.ld
-//               .16x256b delivers in the matching register arrangement) and the bias, round to the
-//               output type and store.
+//   warps 2-9   epilogue: read the accumulator back with tcgen05.ld.16x256b (which hands out the registers
+//               in the mma.sync accumulator arrangement), apply the row/column scales, add the rank-32
+//               low-rank term with warp-level bf16 mma.sync on the same fragments, add the bias, round to
+//               the output type, transpose inside each quad with shuffles and store 16 bytes per thread.
+//               Loads of the next 16x64 block are in flight while the current one is processed.
 // Every wait on an mbarrier is bounded; a wait that gives up writes a code to the status word, raises
 // a CTA-wide abort flag and the CTA drains and exits.  No cluster launch, no multicast.
 #include <mutex>
@@ -25,8 +26,8 @@ namespace {
 constexpr int BM = 128;          // rows per tile = tensor-memory lanes
 constexpr int BK = 128;          // K bytes per stage = one 128-byte swizzle row
 constexpr int UMMA_K = 32;       // K per tcgen05.mma kind::i8
-constexpr int kGemmThreads = 192;
-constexpr int kNumEpiWarps = 4;
+constexpr int kNumEpiWarps = 8;
+constexpr int kGemmThreads = 64 + 32 * kNumEpiWarps;
 constexpr int kLR = 32;          // low-rank width handled in the epilogue
 
 struct GemmParams {
@@ -41,8 +42,9 @@ struct GemmParams {
   int64_t ldt, ldb, ldo;
   int M, N, K;
   int m_split;          // rows [0, m_split) use weight set 0, rows [m_split, M) weight set 1
-  int group_m;
-  int has_lr;
+  int sched_pm, sched_pn;   // the CTAs form a sched_pm x sched_pn grid over (row tile, column tile)
+  int sched_m_steps;        // ceil(row tiles / sched_pm)
+  int sched_n_rounds;       // ceil(column tiles / sched_pn)
   int has_bias;
 };
 
@@ -67,28 +69,37 @@ struct TileCoord {
   int row0, row_end, n0, set;
 };
 
-// Tile order: groups of `group_m` row tiles; inside a group the row tile index runs fastest so that
-// CTAs working at the same time share weight tiles and a small set of activation tiles in L2.
-__device__ __forceinline__ TileCoord decode_tile(int tile, int mt0, int mt_total, int nt, const GemmParams& p, int BN) {
-  const int per_group = p.group_m * nt;
-  const int group = tile / per_group;
-  const int first_m = group * p.group_m;
-  const int gsize = min(mt_total - first_m, p.group_m);
-  const int in_group = tile - group * per_group;
-  const int mt = first_m + in_group % gsize;
-  const int ntile = in_group / gsize;
-  TileCoord c;
-  if (mt < mt0) {
-    c.set = 0; c.row0 = mt * BM; c.row_end = p.m_split;
-  } else {
-    c.set = 1; c.row0 = p.m_split + (mt - mt0) * BM; c.row_end = p.M;
+// Tile schedule.  CTA b sits at (bm, bn) = (b / pn, b % pn) of a pm x pn grid laid over the tile matrix and
+// walks it with strides (pm, pn): all row tiles of one column tile first, then the next column tile.  At any
+// moment the CTAs touch pn weight tiles (each shared by pm CTAs, unchanged from step to step, so they stay in
+// L2) and pm activation tiles (each shared by pn CTAs); a CTA's column tile changes only every m_steps
+// tiles, so the epilogue's per-column data is loaded rarely.  The walker holds the position of one role; all
+// roles walk the same sequence.  No divisions: the loops are counters.
+struct TileWalker {
+  int mt, ntile;        // current row tile / column tile
+  int bm, pm, pn, mt_total, nt, mt0;
+  __device__ __forceinline__ void init(const GemmParams& p, int mt0_, int mt_total_, int nt_) {
+    pm = p.sched_pm; pn = p.sched_pn; mt_total = mt_total_; nt = nt_; mt0 = mt0_;
+    bm = static_cast<int>(blockIdx.x) / pn;
+    mt = bm; ntile = static_cast<int>(blockIdx.x) - bm * pn;
   }
-  c.n0 = ntile * BN;
-  return c;
-}
+  __device__ __forceinline__ bool valid() const { return ntile < nt && mt < mt_total; }
+  __device__ __forceinline__ void advance() {       // to the next existing tile of this CTA (or past the end)
+    mt += pm;
+    if (mt >= mt_total) { mt = bm; ntile += pn; }
+  }
+  __device__ __forceinline__ TileCoord coord(const GemmParams& p, int BN) const {
+    TileCoord c;
+    if (mt < mt0) { c.set = 0; c.row0 = mt * BM; c.row_end = p.m_split; }
+    else { c.set = 1; c.row0 = p.m_split + (mt - mt0) * BM; c.row_end = p.M; }
+    c.n0 = ntile * BN;
+    return c;
+  }
+};
 
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait on an mbarrier phase.  The first probe is inline; the polling loop (wall-clock budget, abort
+// flag) lives out of line to keep the role loops small.
+__device__ __noinline__ bool wait_or_abort_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   uint64_t t0 = 0;
   for (uint32_t i = 1; i < kWaitMaxPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -101,26 +112,63 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   }
   return false;
 }
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return wait_or_abort_slow(bar, parity, abort_flag);
+}
 
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-template <typename OutT>
-__device__ __forceinline__ void store_pair(OutT* out, int64_t ldo, int row, int col, int row_end, int N, float a, float b) {
-  if (row >= row_end) return;
-  OutT* p = out + static_cast<int64_t>(row) * ldo + col;
-  if (col + 1 < N) {
-    *reinterpret_cast<uint32_t*>(p) = pack2(a, b, OutT{});
-  } else if (col < N) {
-    if constexpr (std::is_same<OutT, __nv_bfloat16>::value) p[0] = __float2bfloat16_rn(a);
-    else p[0] = __float2half_rn(a);
+// In-quad 4x4 transpose: on entry lane q of a quad holds w[j] = word (source lane q, block j); on exit it
+// holds w[k] = word (source lane k, block q).
+__device__ __forceinline__ void quad_transpose(uint32_t (&w)[4], int q) {
+  const bool hi = (q & 2) != 0;
+  uint32_t s0 = hi ? w[0] : w[2], s1 = hi ? w[1] : w[3];
+  uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 2), r1 = __shfl_xor_sync(0xffffffffu, s1, 2);
+  uint32_t v0 = hi ? r0 : w[0], v1 = hi ? r1 : w[1], v2 = hi ? w[2] : r0, v3 = hi ? w[3] : r1;
+  const bool odd = (q & 1) != 0;
+  s0 = odd ? v0 : v1; s1 = odd ? v2 : v3;
+  r0 = __shfl_xor_sync(0xffffffffu, s0, 1); r1 = __shfl_xor_sync(0xffffffffu, s1, 1);
+  w[0] = odd ? r0 : v0; w[1] = odd ? v1 : r0; w[2] = odd ? r1 : v2; w[3] = odd ? v3 : r1;
+}
+
+// Ragged / unaligned outputs: one packed pair (columns col, col+1 of one row) at a time.  Kept out of line so
+// that the common path stays small.
+__device__ __noinline__ void store_pairs_slow(void* out, int64_t ldo, int rA, int rB, int col0, int row_end, int N,
+                                              uint4 a, uint4 b) {
+  const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+  unsigned short* o = static_cast<unsigned short*>(out);
+#pragma unroll 1
+  for (int j = 0; j < 4; ++j) {
+    const int col = col0 + j * 8;
+#pragma unroll 1
+    for (int r = 0; r < 2; ++r) {
+      const int row = r == 0 ? rA : rB;
+      const uint32_t w = r == 0 ? wa[j] : wb[j];
+      if (row >= row_end) continue;
+      unsigned short* p = o + static_cast<int64_t>(row) * ldo + col;
+      if (col < N) p[0] = static_cast<unsigned short>(w & 0xFFFFu);
+      if (col + 1 < N) p[1] = static_cast<unsigned short>(w >> 16);
+    }
   }
 }
 
-template <int BN, int STAGES, typename OutT, typename LrT>
+// Test hook: raw accumulators of one n8 block (rows rA / rB, columns col, col+1).
+__device__ __noinline__ void dump_acc(int32_t* dbg, int N, int rA, int rB, int col, int row_end, uint32_t v0, uint32_t v1,
+                                      uint32_t v2, uint32_t v3) {
+  if (rA < row_end && col < N) dbg[static_cast<int64_t>(rA) * N + col] = static_cast<int32_t>(v0);
+  if (rA < row_end && col + 1 < N) dbg[static_cast<int64_t>(rA) * N + col + 1] = static_cast<int32_t>(v1);
+  if (rB < row_end && col < N) dbg[static_cast<int64_t>(rB) * N + col] = static_cast<int32_t>(v2);
+  if (rB < row_end && col + 1 < N) dbg[static_cast<int64_t>(rB) * N + col + 1] = static_cast<int32_t>(v3);
+}
+
+// HAS_LR: low-rank term present.  DBG: also dump the raw accumulators (tests only).
+template <int BN, int STAGES, typename OutT, bool HAS_LR, bool DBG>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW0,
-                          const __grid_constant__ CUtensorMap tmW1, const GemmParams p, const int epilogue_mode) {
+                          const __grid_constant__ CUtensorMap tmW1, const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
+  using LrT = OutT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -134,10 +182,8 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   const int lane = threadIdx.x & 31;
 
   const int mt0 = (p.m_split + BM - 1) / BM;
-  const int mt1 = (p.M - p.m_split + BM - 1) / BM;
-  const int mt_total = mt0 + mt1;
+  const int mt_total = mt0 + (p.M - p.m_split + BM - 1) / BM;
   const int nt = (p.N + BN - 1) / BN;
-  const int total_tiles = mt_total * nt;
   const int num_kb = (p.K + BK - 1) / BK;
   constexpr uint32_t kTmemCols = 2 * BN;
 
@@ -164,9 +210,11 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       int stage = 0; uint32_t phase = 0; long long issued = 0; bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const TileCoord c = decode_tile(tile, mt0, mt_total, nt, p, BN);
-        const CUtensorMap* tmW = c.set == 0 ? &tmW0 : &tmW1;
+      TileWalker w; w.init(p, mt0, mt_total, nt);
+#pragma unroll 1
+      for (; w.valid() && ok; w.advance()) {
+        const TileCoord c = w.coord(p, BN);
+#pragma unroll 1
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!wait_or_abort(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             report_timeout(p.status, 1, 1); *abort_flag = 1; ok = false; break;
@@ -174,7 +222,8 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
           uint8_t* a_s = smem + stage * L::kStageBytes;
           mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
           tma_load_2d(a_s, &tmA, &full_bar[stage], kb * BK, c.row0);
-          tma_load_2d(a_s + L::kABytes, tmW, &full_bar[stage], kb * BK, c.n0);
+          if (c.set == 0) tma_load_2d(a_s + L::kABytes, &tmW0, &full_bar[stage], kb * BK, c.n0);
+          else tma_load_2d(a_s + L::kABytes, &tmW1, &full_bar[stage], kb * BK, c.n0);
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -184,8 +233,7 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       for (int i = 0; i < pending; ++i) {
         if (--stage < 0) { stage = STAGES - 1; phase ^= 1u; }
         if (!wait_or_abort(&full_bar[stage], phase, abort_flag)) {
-          // abort raised elsewhere or copy never landed: fall back to a short fixed delay
-          for (int k = 0; k < 64; ++k) __nanosleep(1000);
+          for (int k = 0; k < 64; ++k) __nanosleep(1000);   // abort raised elsewhere: short fixed delay instead
           break;
         }
       }
@@ -195,7 +243,9 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc_i8(BM, BN);
       int stage = 0; uint32_t phase = 0; int it = 0; bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      TileWalker w; w.init(p, mt0, mt_total, nt);
+#pragma unroll 1
+      for (; w.valid() && ok; w.advance(), ++it) {
         const int buf = it & 1;
         const uint32_t use = static_cast<uint32_t>(it >> 1);
         if (!wait_or_abort(&tempty_bar[buf], (use & 1u) ^ 1u, abort_flag)) {
@@ -203,6 +253,7 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+#pragma unroll 1
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!wait_or_abort(&full_bar[stage], phase, abort_flag)) {
             report_timeout(p.status, 2, 1); *abort_flag = 1; ok = false; break;
@@ -224,34 +275,83 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;              // tensor-memory lanes [32*quarter, 32*quarter+32) belong to this warp
-    const int etid = threadIdx.x - 64;         // 0..127 among the epilogue threads
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // Warp w reads tensor-memory lanes [32*(w%4), +32) (hardware rule) and the column half (w-2)/4 of the tile.
+    // The code is kept small on purpose (real loops, slow paths out of line): eight warps run it out of step
+    // with each other and with the two main-loop warps, and an instruction footprint beyond the instruction
+    // cache stalls them on instruction fetch while TMA traffic keeps the memory system busy.
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int etid = threadIdx.x - 64;         // 0..255 among the epilogue threads
+    const int g = lane >> 2, q = lane & 3;     // mma.sync fragment coordinates
+    constexpr int HALF_N = BN / 2;             // columns per warp
+    constexpr int UNIT_N = 64;                 // columns per tcgen05.ld (16 lanes x 64 columns = 32 registers)
+    constexpr int kChunks = HALF_N / UNIT_N;   // column chunks per warp and tile
+    constexpr bool kLrBf16 = std::is_same<LrT, __nv_bfloat16>::value;
     OutT* out = static_cast<OutT*>(p.out);
     const LrT* tptr = static_cast<const LrT*>(p.t);
     const LrT* lbptr = static_cast<const LrT*>(p.lb);
     uint8_t* lb_s = smem + L::kAuxOff;
     float* scol_s = reinterpret_cast<float*>(smem + L::kScolOff);
     float* bias_s = reinterpret_cast<float*>(smem + L::kBiasOff);
+    const bool vec_store = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     bool aborted = false;
     int it = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-      const TileCoord c = decode_tile(tile, mt0, mt_total, nt, p, BN);
+    int aux_n0 = -1, aux_set = -1;             // which column tile / weight set the shared-memory copies belong to
+
+    // per-tile row data of this thread: low-rank A fragments (two 16-row blocks x two k-steps) and row scales;
+    // the loads for the next tile are issued before the current tile is drained
+    uint32_t af[2][2][4], af_nx[2][2][4];
+    float srow[2][2], srow_nx[2][2];
+    auto load_row_data = [&](const TileCoord& tc, uint32_t (&afr)[2][2][4], float (&sr)[2][2]) {
+#pragma unroll
+      for (int mb = 0; mb < 2; ++mb) {
+        const int rA = tc.row0 + quarter * 32 + mb * 16 + g;
+        const int rB = rA + 8;
+        const bool okA = rA < tc.row_end, okB = rB < tc.row_end;
+        sr[mb][0] = okA ? p.s_row[rA] : 0.0f;
+        sr[mb][1] = okB ? p.s_row[rB] : 0.0f;
+        if constexpr (HAS_LR) {
+          const LrT* ta = tptr + static_cast<int64_t>(okA ? rA : 0) * p.ldt + 2 * q;
+          const LrT* tb = tptr + static_cast<int64_t>(okB ? rB : 0) * p.ldt + 2 * q;
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            afr[mb][ks][0] = okA ? *reinterpret_cast<const uint32_t*>(ta + ks * 16) : 0u;
+            afr[mb][ks][2] = okA ? *reinterpret_cast<const uint32_t*>(ta + ks * 16 + 8) : 0u;
+            afr[mb][ks][1] = okB ? *reinterpret_cast<const uint32_t*>(tb + ks * 16) : 0u;
+            afr[mb][ks][3] = okB ? *reinterpret_cast<const uint32_t*>(tb + ks * 16 + 8) : 0u;
+          }
+        }
+      }
+    };
+
+    TileWalker w; w.init(p, mt0, mt_total, nt);
+    TileCoord c = w.coord(p, BN);
+    if (w.valid()) load_row_data(c, af, srow);
+#pragma unroll 1
+    for (; w.valid(); ++it) {
+      w.advance();
+      const bool has_next = w.valid();
+      const TileCoord c_nx = w.coord(p, BN);
       const int buf = it & 1;
       const uint32_t use = static_cast<uint32_t>(it >> 1);
 
-      // column scales, bias and the low-rank up-projection tile of this N range go to shared memory
-      epi_bar_sync();                          // everyone is done reading the previous tile's copies
-      {
-        const float* scol = p.s_col[c.set];
-        for (int i = etid; i < BN; i += 128) {
+      // column scales, bias and the low-rank up-projection tile of this N range live in shared memory and are
+      // reloaded only when the column tile (or the weight set) changes
+      if (c.n0 != aux_n0 || c.set != aux_set) {
+        aux_n0 = c.n0; aux_set = c.set;
+        epi_bar_sync();                        // everyone is done reading the previous copies
+        const float* scol = c.set == 0 ? p.s_col[0] : p.s_col[1];
+#pragma unroll 1
+        for (int i = etid; i < BN; i += kNumEpiWarps * 32) {
           const int col = c.n0 + i;
           scol_s[i] = col < p.N ? scol[col] : 0.0f;
           bias_s[i] = (p.has_bias && col < p.N) ? p.bias[col] : 0.0f;
         }
-        if (p.has_lr) {
+        if constexpr (HAS_LR) {
           constexpr int kChunksPerRow = BN / 8;
-          for (int i = etid; i < kLR * kChunksPerRow; i += 128) {
+#pragma unroll 1
+          for (int i = etid; i < kLR * kChunksPerRow; i += kNumEpiWarps * 32) {
             const int r = i / kChunksPerRow;
             const int ch = i - r * kChunksPerRow;
             const int col = c.n0 + ch * 8;
@@ -260,8 +360,8 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             *reinterpret_cast<uint4*>(lb_s + r * L::kLbStride + ch * 16) = v;
           }
         }
+        epi_bar_sync();
       }
-      epi_bar_sync();
 
       if (!aborted) {
         const bool landed = wait_or_abort(&tfull_bar[buf], use & 1u, abort_flag);
@@ -269,114 +369,97 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
           report_timeout(p.status, 3, 3); *abort_flag = 1; aborted = true;
         }
       }
-      if (aborted) continue;                   // keep the loop shape (named barriers) but touch nothing
+      if (aborted) { c = c_nx; continue; }     // keep the loop shape (named barriers) but touch nothing
       tc_fence_after();
 
-      const uint32_t t_acc = tmem_base + static_cast<uint32_t>(buf * BN);
-      if (epilogue_mode == 0) {
-        // ---- one accumulator row per thread; low-rank term by scalar FMA (reference implementation of the epilogue)
-        const int row = c.row0 + quarter * 32 + lane;
-        const bool row_ok = row < c.row_end;
-        const float sr = row_ok ? p.s_row[row] : 0.0f;
-        float tv[kLR];
-        if (p.has_lr) {
+      const uint32_t t_acc = tmem_base + static_cast<uint32_t>(buf * BN + half * HALF_N);
+      // a unit is 16 rows (block mb) x 64 columns (chunk ch); the load of the next unit is issued before the
+      // current one is processed, va holds the mb = 0 units and vb the mb = 1 units
+      uint32_t va[32], vb[32];
+      auto unit_addr = [&](int ch, int mb) {
+        return t_acc + (static_cast<uint32_t>(quarter * 32 + mb * 16) << 16) + static_cast<uint32_t>(ch * UNIT_N);
+      };
+      auto process = [&](const uint32_t (&v)[32], int ch, int mb, const uint32_t (&afm)[2][4], float srA, float srB) {
+        const int col_unit = half * HALF_N + ch * UNIT_N;                // first tile column of this unit
+        const int rA = c.row0 + quarter * 32 + mb * 16 + g;
+        const int rB = rA + 8;
 #pragma unroll
-          for (int r = 0; r < kLR; ++r)
-            tv[r] = row_ok ? static_cast<float>(tptr[static_cast<int64_t>(row) * p.ldt + r]) : 0.0f;
-        }
-        for (int cc = 0; cc < BN / 32; ++cc) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(t_acc + (static_cast<uint32_t>(quarter * 32) << 16) + cc * 32, v);
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const int cl = cc * 32 + j;
-            float y0 = static_cast<float>(static_cast<int32_t>(v[j])) * (sr * scol_s[cl]);
-            float y1 = static_cast<float>(static_cast<int32_t>(v[j + 1])) * (sr * scol_s[cl + 1]);
-            if (p.has_lr) {
-              float l0 = 0.0f, l1 = 0.0f;
-#pragma unroll
-              for (int r = 0; r < kLR; ++r) {
-                const LrT* lrow = reinterpret_cast<const LrT*>(lb_s + r * L::kLbStride);
-                l0 = fmaf(tv[r], static_cast<float>(lrow[cl]), l0);
-                l1 = fmaf(tv[r], static_cast<float>(lrow[cl + 1]), l1);
-              }
-              y0 += l0; y1 += l1;
-            }
-            y0 += bias_s[cl]; y1 += bias_s[cl + 1];
-            store_pair<OutT>(out, p.ldo, row, c.n0 + cl, c.row_end, p.N, y0, y1);
-            if (p.dbg_acc != nullptr && row_ok) {
-              if (c.n0 + cl < p.N) p.dbg_acc[static_cast<int64_t>(row) * p.N + c.n0 + cl] = static_cast<int32_t>(v[j]);
-              if (c.n0 + cl + 1 < p.N) p.dbg_acc[static_cast<int64_t>(row) * p.N + c.n0 + cl + 1] = static_cast<int32_t>(v[j + 1]);
-            }
-          }
-        }
-      } else {
-        // ---- fragment epilogue: tcgen05.ld.16x256b hands out the accumulator in the mma.sync C arrangement
-        const int g = lane >> 2, q = lane & 3;
-#pragma unroll 1
-        for (int mb = 0; mb < 2; ++mb) {
-          const int rA = c.row0 + quarter * 32 + mb * 16 + g;
-          const int rB = rA + 8;
-          const bool okA = rA < c.row_end, okB = rB < c.row_end;
-          const float srA = okA ? p.s_row[rA] : 0.0f;
-          const float srB = okB ? p.s_row[rB] : 0.0f;
-          uint32_t af[2][4] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};
-          if (p.has_lr) {
-#pragma unroll
-            for (int ks = 0; ks < 2; ++ks) {
-              const int k0 = ks * 16 + 2 * q;
-              if (okA) {
-                af[ks][0] = *reinterpret_cast<const uint32_t*>(tptr + static_cast<int64_t>(rA) * p.ldt + k0);
-                af[ks][2] = *reinterpret_cast<const uint32_t*>(tptr + static_cast<int64_t>(rA) * p.ldt + k0 + 8);
-              }
-              if (okB) {
-                af[ks][1] = *reinterpret_cast<const uint32_t*>(tptr + static_cast<int64_t>(rB) * p.ldt + k0);
-                af[ks][3] = *reinterpret_cast<const uint32_t*>(tptr + static_cast<int64_t>(rB) * p.ldt + k0 + 8);
-              }
-            }
-          }
-          const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32 + mb * 16) << 16;
-#pragma unroll 2
-          for (int cc = 0; cc < BN / 32; ++cc) {
-            uint32_t v[16];
-            tmem_ld_16x256b_x4(t_acc + lane_addr + cc * 32, v);
-            tc_wait_ld();
+        for (int grp = 0; grp < 2; ++grp) {                              // 4 n8 blocks = 32 columns per group
+          uint32_t wA[4], wB[4];
+          // the group's legacy MMAs are issued back to back before any result is used: they queue behind the
+          // tcgen05 stream on the tensor pipe, so their latency is long and has to be overlapped
+          float lr[4][4];
+          if constexpr (HAS_LR) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const int cl = cc * 32 + j * 8 + 2 * q;      // column inside the tile
-              float lr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-              if (p.has_lr) {
-                uint32_t bf[4];
-                ldmatrix_x4_trans(bf, smem_u32(lb_s + lane * L::kLbStride + (cc * 32 + j * 8) * 2));
-                mma_m16n8k16<std::is_same<LrT, __nv_bfloat16>::value>(lr, af[0], bf[0], bf[1]);
-                mma_m16n8k16<std::is_same<LrT, __nv_bfloat16>::value>(lr, af[1], bf[2], bf[3]);
-              }
-              const float2 sc = *reinterpret_cast<const float2*>(scol_s + cl);
-              const float2 bi = *reinterpret_cast<const float2*>(bias_s + cl);
-              float y0 = static_cast<float>(static_cast<int32_t>(v[4 * j + 0])) * (srA * sc.x);
-              float y1 = static_cast<float>(static_cast<int32_t>(v[4 * j + 1])) * (srA * sc.y);
-              float y2 = static_cast<float>(static_cast<int32_t>(v[4 * j + 2])) * (srB * sc.x);
-              float y3 = static_cast<float>(static_cast<int32_t>(v[4 * j + 3])) * (srB * sc.y);
-              y0 += lr[0]; y1 += lr[1]; y2 += lr[2]; y3 += lr[3];
-              y0 += bi.x; y1 += bi.y; y2 += bi.x; y3 += bi.y;
-              const int col = c.n0 + cl;
-              store_pair<OutT>(out, p.ldo, rA, col, c.row_end, p.N, y0, y1);
-              store_pair<OutT>(out, p.ldo, rB, col, c.row_end, p.N, y2, y3);
-              if (p.dbg_acc != nullptr) {
-                if (okA && col < p.N) p.dbg_acc[static_cast<int64_t>(rA) * p.N + col] = static_cast<int32_t>(v[4 * j + 0]);
-                if (okA && col + 1 < p.N) p.dbg_acc[static_cast<int64_t>(rA) * p.N + col + 1] = static_cast<int32_t>(v[4 * j + 1]);
-                if (okB && col < p.N) p.dbg_acc[static_cast<int64_t>(rB) * p.N + col] = static_cast<int32_t>(v[4 * j + 2]);
-                if (okB && col + 1 < p.N) p.dbg_acc[static_cast<int64_t>(rB) * p.N + col + 1] = static_cast<int32_t>(v[4 * j + 3]);
-              }
+              uint32_t bf[4];
+              ldmatrix_x4_trans(bf, smem_u32(lb_s + lane * L::kLbStride + (col_unit + (grp * 4 + j) * 8) * 2));
+              lr[j][0] = lr[j][1] = lr[j][2] = lr[j][3] = 0.0f;
+              mma_m16n8k16<kLrBf16>(lr[j], afm[0], bf[0], bf[1]);
+              mma_m16n8k16<kLrBf16>(lr[j], afm[1], bf[2], bf[3]);
             }
           }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int nb = grp * 4 + j;
+            const int cl = col_unit + nb * 8 + 2 * q;                    // column inside the tile
+            const float2 sc = *reinterpret_cast<const float2*>(scol_s + cl);
+            const float2 bi = *reinterpret_cast<const float2*>(bias_s + cl);
+            // same operation order as the reference kernel: acc * (s_row * s_col), + low rank, + bias
+            float y0 = __fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 0])), __fmul_rn(srA, sc.x));
+            float y1 = __fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 1])), __fmul_rn(srA, sc.y));
+            float y2 = __fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 2])), __fmul_rn(srB, sc.x));
+            float y3 = __fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 3])), __fmul_rn(srB, sc.y));
+            if constexpr (HAS_LR) {
+              y0 = __fadd_rn(y0, lr[j][0]); y1 = __fadd_rn(y1, lr[j][1]); y2 = __fadd_rn(y2, lr[j][2]); y3 = __fadd_rn(y3, lr[j][3]);
+            }
+            y0 = __fadd_rn(y0, bi.x); y1 = __fadd_rn(y1, bi.y); y2 = __fadd_rn(y2, bi.x); y3 = __fadd_rn(y3, bi.y);
+            wA[j] = pack2(y0, y1, OutT{});
+            wB[j] = pack2(y2, y3, OutT{});
+            if constexpr (DBG)
+              dump_acc(p.dbg_acc, p.N, rA, rB, c.n0 + cl, c.row_end, v[4 * nb + 0], v[4 * nb + 1], v[4 * nb + 2], v[4 * nb + 3]);
+          }
+          const int col_grp = c.n0 + col_unit + grp * 32;                // first output column of the group
+          if (vec_store && col_grp + 32 <= p.N) {
+            // 4x4 transpose inside each quad: lane q ends up with all 8 columns of n8 block q -> one 16-byte store per row
+            quad_transpose(wA, q);
+            quad_transpose(wB, q);
+            if (rA < c.row_end)
+              st_v4(out + static_cast<int64_t>(rA) * p.ldo + col_grp + q * 8, make_uint4(wA[0], wA[1], wA[2], wA[3]));
+            if (rB < c.row_end)
+              st_v4(out + static_cast<int64_t>(rB) * p.ldo + col_grp + q * 8, make_uint4(wB[0], wB[1], wB[2], wB[3]));
+          } else {
+            store_pairs_slow(p.out, p.ldo, rA, rB, col_grp + 2 * q, c.row_end, p.N, make_uint4(wA[0], wA[1], wA[2], wA[3]),
+                             make_uint4(wB[0], wB[1], wB[2], wB[3]));
+          }
         }
+      };
+      tmem_ld_16x256b_x8(unit_addr(0, 0), va);
+      if (has_next) load_row_data(c_nx, af_nx, srow_nx);     // in flight while this tile is drained
+#pragma unroll 1
+      for (int ch = 0; ch < kChunks; ++ch) {
+        tc_wait_ld();
+        tmem_ld_16x256b_x8(unit_addr(ch, 1), vb);
+        process(va, ch, 0, af[0], srow[0][0], srow[0][1]);
+        tc_wait_ld();
+        if (ch + 1 < kChunks) tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+        process(vb, ch, 1, af[1], srow[1][0], srow[1][1]);
       }
       // accumulator drained: hand the buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      c = c_nx;
+#pragma unroll
+      for (int mb = 0; mb < 2; ++mb) {
+        srow[mb][0] = srow_nx[mb][0]; srow[mb][1] = srow_nx[mb][1];
+        if constexpr (HAS_LR) {
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) af[mb][ks][e] = af_nx[mb][ks][e];
+        }
+      }
     }
   }
 
@@ -497,11 +580,11 @@ int weight_map(CUtensorMap* out, const void* w, int64_t N, int64_t K, int64_t ld
   return PQ_OK;
 }
 
-template <int BN, int STAGES, typename OutT, typename LrT>
+template <int BN, int STAGES, typename OutT, bool HAS_LR, bool DBG>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmW0, const CUtensorMap& tmW1, const GemmParams& p,
-                int epilogue_mode, int grid, cudaStream_t st) {
+                int grid, cudaStream_t st) {
   using L = SmemLayout<BN, STAGES>;
-  auto kern = pq_int8_gemm_fused_kernel<BN, STAGES, OutT, LrT>;
+  auto kern = pq_int8_gemm_fused_kernel<BN, STAGES, OutT, HAS_LR, DBG>;
   static bool attr_set[64] = {false};     // per device; benign race: the attribute value never changes
   int dev = 0;
   PQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -509,22 +592,31 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmW0, const CUtensorM
     PQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
-  kern<<<grid, kGemmThreads, L::kDynamic, st>>>(tmA, tmW0, tmW1, p, epilogue_mode);
+  kern<<<grid, kGemmThreads, L::kDynamic, st>>>(tmA, tmW0, tmW1, p);
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
 }
 
-template <typename OutT, typename LrT>
-int launch_by_shape(int bn, int stages, const CUtensorMap& tmA, const CUtensorMap& tmW0, const CUtensorMap& tmW1,
-                    const GemmParams& p, int epilogue_mode, int grid, cudaStream_t st) {
-  if (bn == 256) {
-    if (stages == 2) return launch_gemm<256, 2, OutT, LrT>(tmA, tmW0, tmW1, p, epilogue_mode, grid, st);
-    if (stages == 3) return launch_gemm<256, 3, OutT, LrT>(tmA, tmW0, tmW1, p, epilogue_mode, grid, st);
-    return launch_gemm<256, 4, OutT, LrT>(tmA, tmW0, tmW1, p, epilogue_mode, grid, st);
+template <int BN, int STAGES, typename OutT>
+int launch_by_flags(bool has_lr, bool dbg, const CUtensorMap& tmA, const CUtensorMap& tmW0, const CUtensorMap& tmW1,
+                    const GemmParams& p, int grid, cudaStream_t st) {
+  if (dbg) {
+    if (has_lr) return launch_gemm<BN, STAGES, OutT, true, true>(tmA, tmW0, tmW1, p, grid, st);
+    return launch_gemm<BN, STAGES, OutT, false, true>(tmA, tmW0, tmW1, p, grid, st);
   }
-  if (stages == 2) return launch_gemm<128, 2, OutT, LrT>(tmA, tmW0, tmW1, p, epilogue_mode, grid, st);
-  if (stages == 4) return launch_gemm<128, 4, OutT, LrT>(tmA, tmW0, tmW1, p, epilogue_mode, grid, st);
-  return launch_gemm<128, 6, OutT, LrT>(tmA, tmW0, tmW1, p, epilogue_mode, grid, st);
+  if (has_lr) return launch_gemm<BN, STAGES, OutT, true, false>(tmA, tmW0, tmW1, p, grid, st);
+  return launch_gemm<BN, STAGES, OutT, false, false>(tmA, tmW0, tmW1, p, grid, st);
+}
+
+template <typename OutT>
+int launch_by_shape(int bn, int stages, bool has_lr, bool dbg, const CUtensorMap& tmA, const CUtensorMap& tmW0,
+                    const CUtensorMap& tmW1, const GemmParams& p, int grid, cudaStream_t st) {
+  if (bn == 256) {
+    if (stages == 3) return launch_by_flags<256, 3, OutT>(has_lr, dbg, tmA, tmW0, tmW1, p, grid, st);
+    return launch_by_flags<256, 4, OutT>(has_lr, dbg, tmA, tmW0, tmW1, p, grid, st);
+  }
+  if (stages == 4) return launch_by_flags<128, 4, OutT>(has_lr, dbg, tmA, tmW0, tmW1, p, grid, st);
+  return launch_by_flags<128, 6, OutT>(has_lr, dbg, tmA, tmW0, tmW1, p, grid, st);
 }
 
 int choose_block_n(int64_t M, int64_t N) {
@@ -567,8 +659,8 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
 
   const int bn = choose_block_n(M, N);
   int stages = options().gemm_stages;
-  if (bn == 256) { if (stages != 2 && stages != 3) stages = 4; }
-  else { if (stages != 2 && stages != 4) stages = 6; }
+  if (bn == 256) { if (stages != 3) stages = 4; }
+  else { if (stages != 4) stages = 6; }
 
   CUtensorMap tmA, tmW0, tmW1;
   int rc = make_tile_map(&tmA, xq, M, K, ldx, BM);
@@ -588,20 +680,37 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
   p.ldt = ldt; p.ldb = ldb; p.ldo = ldo;
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
   p.m_split = static_cast<int>(m_split);
-  int gm = options().gemm_group_m; if (gm < 1) gm = 1;
-  p.group_m = gm;
-  p.has_lr = has_lr ? 1 : 0;
   p.has_bias = bias != nullptr ? 1 : 0;
 
-  const int64_t mt = (m_split + BM - 1) / BM + (M - m_split + BM - 1) / BM;
-  const int64_t tiles = mt * ((N + bn - 1) / bn);
+  // CTA grid pm x pn over the tile matrix: fewest steps first, then the widest pn (fewer sweeps over the rows)
+  const int mt = static_cast<int>((m_split + BM - 1) / BM + (M - m_split + BM - 1) / BM);
+  const int ntl = static_cast<int>((N + bn - 1) / bn);
   int max_ctas = options().gemm_max_ctas > 0 ? options().gemm_max_ctas : sm_count();
-  const int grid = static_cast<int>(tiles < max_ctas ? tiles : max_ctas);
-  const int epi = options().gemm_epilogue;
+  int best_pm = 1, best_pn = 1;
+  long long best_steps = -1;
+  for (int pn = 1; pn <= ntl && pn <= max_ctas; ++pn) {
+    int pm = max_ctas / pn;
+    if (pm > mt) pm = mt;
+    if (pm < 1) continue;
+    const long long steps = static_cast<long long>((mt + pm - 1) / pm) * ((ntl + pn - 1) / pn);
+    if (best_steps < 0 || steps < best_steps || (steps == best_steps && pn > best_pn)) {
+      best_steps = steps; best_pm = pm; best_pn = pn;
+    }
+  }
+  if (options().gemm_pn > 0 && options().gemm_pn <= ntl && options().gemm_pn <= max_ctas) {
+    best_pn = options().gemm_pn;
+    best_pm = max_ctas / best_pn; if (best_pm > mt) best_pm = mt;
+    if (options().gemm_pm > 0 && options().gemm_pm <= best_pm) best_pm = options().gemm_pm;
+  }
+  p.sched_pm = best_pm; p.sched_pn = best_pn;
+  p.sched_m_steps = (mt + best_pm - 1) / best_pm;
+  p.sched_n_rounds = (ntl + best_pn - 1) / best_pn;
+  const int grid = best_pm * best_pn;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool dbg = dbg_acc != nullptr;
   if (out_dtype == PQ_DTYPE_BF16)
-    return launch_by_shape<__nv_bfloat16, __nv_bfloat16>(bn, stages, tmA, tmW0, tmW1, p, epi, grid, st);
-  return launch_by_shape<__half, __half>(bn, stages, tmA, tmW0, tmW1, p, epi, grid, st);
+    return launch_by_shape<__nv_bfloat16>(bn, stages, has_lr, dbg, tmA, tmW0, tmW1, p, grid, st);
+  return launch_by_shape<__half>(bn, stages, has_lr, dbg, tmA, tmW0, tmW1, p, grid, st);
 }
 
 }  // namespace

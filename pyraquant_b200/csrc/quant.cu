@@ -29,18 +29,21 @@ template <> __device__ __forceinline__ uint32_t abs2_max<__half>(uint32_t acc, u
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
-// One element: returns the int8 code in the low byte (two's complement).
+// One element: returns the int8 code in the low byte (two's complement).  No float->int conversion
+// instruction is used (those run on the slow conversion pipe): adding 1.5 * 2^23 rounds to the nearest-even
+// integer and leaves that integer in the low mantissa bits.
 __device__ __forceinline__ uint32_t quant1(float x, float scale, float inv) {
-  const float kMagic = 12582912.0f;                 // 1.5 * 2^23: adding it rounds to nearest-even integer
+  const float kMagic = 12582912.0f;
   float r = x * inv;
   float m = r + kMagic;
   float qf = m - kMagic;
   float d = fabsf(r - qf);
   if (d > 0.5f - 1.220703125e-4f) {                 // within 2^-13 of a tie: decide with the exact quotient
-    qf = rintf(__fdiv_rn(x, scale));
+    m = __fdiv_rn(x, scale) + kMagic;               // IEEE quotient, then round-half-even by the same trick
+    qf = m - kMagic;
   }
-  qf = fminf(fmaxf(qf, -127.0f), 127.0f);
-  return static_cast<uint32_t>(__float2int_rn(qf)) & 0xFFu;
+  m = fminf(fmaxf(m, kMagic - 127.0f), kMagic + 127.0f);      // clamp the code to [-127, 127]
+  return static_cast<uint32_t>(__float_as_int(m)) & 0xFFu;
 }
 
 template <typename T>
@@ -215,8 +218,8 @@ pq_dequant_epilogue_kernel(const int32_t* __restrict__ acc, const float* __restr
        i += static_cast<int64_t>(gridDim.x) * kThreads) {
     const int64_t m = i / N;
     const int64_t n = i - m * N;
-    float yv = static_cast<float>(acc[i]) * (s_row[m] * s_col[n]);
-    if (bias != nullptr) yv += bias[n];
+    float yv = __fmul_rn(int_to_float_rn(acc[i]), __fmul_rn(s_row[m], s_col[n]));
+    if (bias != nullptr) yv = __fadd_rn(yv, bias[n]);
     if constexpr (sizeof(OutT) == 2 && __is_same(OutT, __nv_bfloat16)) out[i] = __float2bfloat16_rn(yv);
     else out[i] = __float2half_rn(yv);
   }

@@ -113,9 +113,14 @@ LOWRANK_B_ATTR = "_lowrank_B"
 
 
 def _quantize_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Per-output-channel symmetric absmax INT8 (reference :355-357): fp32 math, round-half-even."""
+    """Per-output-channel symmetric absmax INT8 (reference :355-357): fp32 math, round-half-even.
+
+    The divisor 127 is passed as a tensor: torch's CUDA kernel turns division by a Python scalar into a
+    multiplication with its reciprocal, which moves some scales by one ulp; tensor / tensor is an IEEE
+    division on every device, so CPU and GPU conversions give identical codes and scales."""
     wf = w.float()
-    scale = wf.abs().amax(dim=1).clamp_min(1e-8) / 127.0
+    amax = wf.abs().amax(dim=1).clamp_min(1e-8)
+    scale = amax / torch.full_like(amax, 127.0)
     codes = torch.round(wf / scale[:, None]).clamp_(-127, 127).to(torch.int8)
     return codes.contiguous(), scale.contiguous()
 
@@ -314,8 +319,9 @@ def selftest_and_bench(Ms=(4352, 16640, 33744, 65792), iters=10):
     xq, sx = quant_rows(x)
     acc = torch._int_mm(xq, q.weight_int8.t()).float() if xq.shape[0] > 16 else xq.float() @ q.weight_int8.float().t()
     ref_int8 = (acc * sx[:, None] * q.w_scale[None, :] + q.bias[None, :]).to(torch.bfloat16).float()
-    xf = x.float(); sc = xf.abs().amax(1, keepdim=True).clamp_min(1e-8) / 127
-    xq_ref = torch.round(xf / sc).clamp(-127, 127).to(torch.int8)
+    # torch reference quantizer, evaluated on the CPU where scalar division is an IEEE division
+    xf = x.float().cpu(); sc = xf.abs().amax(1, keepdim=True).clamp_min(1e-8) / 127
+    xq_ref = torch.round(xf / sc).clamp(-127, 127).to(torch.int8).to(dev); sc = sc.to(dev)
     x_plain = torch.randn(4352, 3072, device=dev).to(torch.bfloat16)
     y_plain = q(x_plain).float(); ref_plain = F.linear(x_plain, lin.weight, lin.bias).float()
     xs = x[:8]

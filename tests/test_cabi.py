@@ -36,10 +36,10 @@ def test_version_and_status_strings():
 
 
 def test_options_roundtrip():
-    old = _lib.get_option("gemm_group_m")
-    _lib.set_option("gemm_group_m", 4)
-    assert _lib.get_option("gemm_group_m") == 4
-    _lib.set_option("gemm_group_m", old)
+    old = _lib.get_option("gemm_pn")
+    _lib.set_option("gemm_pn", 4)
+    assert _lib.get_option("gemm_pn") == 4
+    _lib.set_option("gemm_pn", old)
     with pytest.raises(RuntimeError):
         _lib.set_option("no_such_knob", 1)
 

@@ -120,7 +120,7 @@ def test_gather_quant_rows_bit_exact(cuda_dev):
 
 
 # ------------------------------------------------------------------------------------------------ GEMM
-def run_gemm_case(dev, M, N, K, *, lowrank, bias, dtype=torch.bfloat16, seed=0, epilogue=None, extreme=False):
+def run_gemm_case(dev, M, N, K, *, lowrank, bias, dtype=torch.bfloat16, seed=0, extreme=False):
     g = torch.Generator().manual_seed(seed)
     if extreme:
         xq = torch.full((M, K), 127, dtype=torch.int8); xq[::2] = -127
@@ -135,38 +135,35 @@ def run_gemm_case(dev, M, N, K, *, lowrank, bias, dtype=torch.bfloat16, seed=0, 
     if lowrank:
         t = (torch.randn(M, 32, generator=g) * 1.0).to(dtype)
         lb = (torch.randn(32, N, generator=g) * 0.02).to(dtype)
-    if epilogue is not None:
-        _lib.set_option("gemm_epilogue", epilogue)
-    try:
-        to = lambda v: None if v is None else v.to(dev)
-        out, acc = ops.int8_gemm_debug(to(xq), to(sr), to(wq), to(sc), to(b), to(t), to(lb), dtype)
-        torch.cuda.synchronize()
-    finally:
-        if epilogue is not None:
-            _lib.set_option("gemm_epilogue", 1)
+    to = lambda v: None if v is None else v.to(dev)
+    out, acc = ops.int8_gemm_debug(to(xq), to(sr), to(wq), to(sc), to(b), to(t), to(lb), dtype)
+    torch.cuda.synchronize()
     acc_ref = oracle.int_mm(xq, wq)
     assert torch.equal(acc.cpu(), acc_ref), f"int32 accumulators differ at {(acc.cpu() != acc_ref).sum().item()} places"
     ref64 = oracle.exact_dequant_f64(acc_ref, sr, sc, b, t, lb)
     err = max_rel_err(out.cpu(), ref64)
     assert err <= TOL, err
-    # against the fp32 restatement of the kernel's epilogue the gap is rounding noise only
+    # against the fp32 restatement of the kernel's epilogue: identical bits without the low-rank term (same
+    # operations in the same order), summation-order noise of the rank-32 dot product with it
     y32 = oracle.epilogue(acc_ref, sr, sc, b, t, lb, dtype)
-    assert max_rel_err(out.cpu(), y32.double()) <= 8e-3
+    if not lowrank:
+        assert torch.equal(out.cpu(), y32)
+    else:
+        assert max_rel_err(out.cpu(), y32.double()) <= 8e-3
     return out
 
 
-@pytest.mark.parametrize("epilogue", [0, 1])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (1, 256, 64), (8, 128, 64), (17, 384, 192), (154, 640, 640),
-                                   (300, 512, 1280), (1000, 3072, 512), (257, 1280, 2560)])
-def test_gemm_small_shapes(cuda_dev, epilogue, M, N, K):
-    run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=True, seed=M + N + K, epilogue=epilogue)
-    run_gemm_case(cuda_dev, M, N, K, lowrank=False, bias=False, seed=M + N + K + 1, epilogue=epilogue)
+                                   (300, 512, 1280), (1000, 3072, 512), (257, 1280, 2560), (129, 264, 80),
+                                   (4350, 1288, 144)])
+def test_gemm_small_shapes(cuda_dev, M, N, K):
+    run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=True, seed=M + N + K)
+    run_gemm_case(cuda_dev, M, N, K, lowrank=False, bias=False, seed=M + N + K + 1)
 
 
-@pytest.mark.parametrize("epilogue", [0, 1])
-def test_gemm_extreme_accumulators_exact(cuda_dev, epilogue):
+def test_gemm_extreme_accumulators_exact(cuda_dev):
     # |acc| = K * 127^2 = 2.0e8 > 2^24: only true int32 accumulation gets this right
-    run_gemm_case(cuda_dev, 256, 512, 12288, lowrank=False, bias=True, extreme=True, epilogue=epilogue)
+    run_gemm_case(cuda_dev, 256, 512, 12288, lowrank=False, bias=True, extreme=True)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -193,6 +190,16 @@ def test_gemm_persistent_many_tiles_per_cta(cuda_dev):
         _lib.set_option("gemm_max_ctas", 0)
 
 
+@pytest.mark.parametrize("pm,pn", [(1, 1), (2, 3), (5, 2), (16, 8)])
+def test_gemm_schedule_grids(cuda_dev, pm, pn):
+    # ragged CTA grids over the tile matrix: idle steps, column tile changes, both accumulator buffers
+    _lib.set_option("gemm_pn", pn); _lib.set_option("gemm_pm", pm)
+    try:
+        run_gemm_case(cuda_dev, 1700, 2304, 256, lowrank=True, bias=True, seed=pm * 10 + pn)
+    finally:
+        _lib.set_option("gemm_pn", 0); _lib.set_option("gemm_pm", 0)
+
+
 def test_gemm_cfg0_layer(cuda_dev):
     """BASELINE config 0: M=4608, K=N=3072, rank-32 branch and bias, through Int8Linear.forward."""
     L = oracle.make_layer(0, 4608, 3072, 3072)
@@ -215,8 +222,11 @@ def test_gemm_cfg0_layer(cuda_dev):
     assert torch.equal(acc.cpu(), acc_ref)
     # output against the exact dequantised math and against the restated forward
     bias32 = lin.bias.detach().float()
+    # the down-projection t = x @ lr_A is torch's bf16 matmul, as in the reference (:390); its rounding to bf16
+    # may differ from the CPU's by one ulp, so the GEMM is judged on the t it was given and t on its own
     t_ref = (L["x"].float() @ L["lr_A"].float()).to(torch.bfloat16)
-    ref64 = oracle.exact_dequant_f64(acc_ref, sxo, ws, bias32, t_ref, L["lr_B"])
+    assert bool(((t_gpu.cpu().float() - t_ref.float()).abs() <= t_ref.float().abs() * 2.0 ** -7 + 1e-3).all())
+    ref64 = oracle.exact_dequant_f64(acc_ref, sxo, ws, bias32, t_gpu.cpu(), L["lr_B"])
     assert max_rel_err(y.cpu(), ref64) <= TOL
     y_or = oracle.int8_linear_forward(L["x"], wq, ws, bias32, L["lr_A"], L["lr_B"])
     rel_l2 = ((y.cpu().float() - y_or.float()).norm() / y_or.float().norm()).item()
@@ -284,10 +294,11 @@ def test_full_size_quant_and_gemm_properties(cuda_dev):
     x = x.to(torch.bfloat16)
     q, s = int8_exec.quant_rows(x)
     xf = x.float()
-    s_ref = xf.abs().amax(1).clamp_min(1e-8) / 127
+    amax = xf.abs().amax(1).clamp_min(1e-8)
+    s_ref = amax / torch.full_like(amax, 127.0)            # tensor / tensor: IEEE division on CUDA as well
     assert torch.equal(s, s_ref)
     assert int(q.abs().amax(1).min()) == 127
-    assert bool(((xf - q.float() * s[:, None]).abs() <= s[:, None] * 0.5000001).all())
+    assert bool(((xf - q.float() * s[:, None]).abs() <= s[:, None] * 0.5001).all())
     del xf
     w = torch.randint(-127, 128, (N, K), generator=g, device=d, dtype=torch.int8)
     sc = torch.rand(N, generator=g, device=d) * 1e-3 + 1e-4
@@ -376,7 +387,7 @@ def test_routed_two_tier_linear(cuda_dev):
     w8, s8 = oracle.quant_weight(lin.weight.detach())
     w4, s4 = oracle.nested4_from_int8(w8, s8)
     xq, sx = oracle.quant_rows(rows)
-    t = (rows.float() @ A.float()).to(torch.bfloat16)
+    t = (rows.to(cuda_dev) @ A.to(cuda_dev)).cpu()            # the module's own down-projection (torch bf16 matmul)
     b32 = lin.bias.detach().float()
     mh = plan.m_hi
     ref = torch.cat([oracle.exact_dequant_f64(oracle.int_mm(xq[:mh], w8), sx[:mh], s8, b32, t[:mh], B),

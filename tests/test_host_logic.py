@@ -93,7 +93,6 @@ def test_plan_tier_ordering_keeps_scatter_result(golden):
     y_flat = torch.cat([from_bf16_bits(g[f"bucket{i}_out_bits"]).reshape(-1, bg.shape[1])
                         for i in range(int(g["n_buckets"]))])
     # the same per-row outputs, permuted like the rows, must blend to the same canvas
-    order = {(int(t), k): i for k, (i, t) in enumerate([])}
     perm = np.argsort(~tmap.reshape(-1)[flat.row_idx], kind="stable")
     got = emulate_scatter(y_flat[torch.from_numpy(perm)], tiered, bg)
     assert torch.equal(got.reshape(1, 24, 24, -1), from_bf16_bits(g["fused_bits"]))
