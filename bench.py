@@ -61,7 +61,7 @@ def step_ops(rows: int) -> float:
 
 # ------------------------------------------------------------------------------------------------ clocks
 class ClockSampler:
-    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    """nvidia-smi sampled every 50 ms while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -73,7 +73,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -306,13 +306,18 @@ def main_ours(args):
     gemm_ops = step_ops(rows)
     achieved = gemm_ops / (gemm_ms_sum * 1e-3) / 1e12
     peak = 2.0 * float(peaks["bf16_sustained"])
+    # DRAM traffic of the GEMM launches of one step: bytes per row from the committed ncu summary (captured at
+    # 8192 rows), scaled by the rows of a full launch
     traffic = None
-    tp = ROOT / "profiles" / "gemm_dram_traffic.json"
+    tp = ROOT / "profiles" / "gemm_fused_flux4k_rows8192_full.md"
     if tp.exists():
-        try:
-            traffic = json.loads(tp.read_text()).get("bytes_per_step_scaled")
-        except Exception:
-            traffic = None
+        per_row = {}
+        for ln in tp.read_text().splitlines():
+            if ln.startswith("TRAFFIC_BYTES_PER_ROW"):
+                _tag, name, val = ln.split()
+                per_row[name] = float(val)
+        if all(n in per_row for n, _K, _N in LAYERS):
+            traffic = sum(per_row[n] * rows for n, _K, _N in LAYERS)
     line = {
         "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
@@ -322,7 +327,7 @@ def main_ours(args):
                    "parallelism": f"row-sharded x{world}, weights replicated", "allgather": bool(args.allgather and world > 1),
                    "l2": "inputs (2.4 GB) and outputs (3.2 GB) exceed L2; no flush needed"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOPS", "frac": achieved / peak,
-                     "traffic": traffic, "kernel": "pq_int8_gemm_fused_kernel",
+                     "traffic": traffic, "kernel": "pq_int8_gemm_fused_kernel (both launches of a step)",
                      "peak_basis": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json (INT8 issues at twice the bf16 rate)",
                      "frac_of_datasheet_4500": achieved / DATASHEET_INT8_TOPS,
                      "ops_per_launch": [2.0 * rows * K * N for _n, K, N in LAYERS]},
@@ -344,11 +349,11 @@ def main_ours(args):
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--allgather", action="store_true", help="also all-gather the outputs over NCCL inside the step")
-    ap.add_argument("--cpu-sample-rows", type=int, default=1024)
+    ap.add_argument("--cpu-sample-rows", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=M_TOTAL,
                     help="total token rows (default: the 4K stage's 66048); smaller values are for profiler captures only")
     ap.add_argument("--no-e2e", action="store_true")

@@ -122,6 +122,22 @@ int pq_int8_gemm_grouped(const int8_t* xq, int64_t ldx, const float* s_row,
                          int64_t M_hi, int64_t M, int64_t N, int64_t K,
                          void* workspace, size_t ws_bytes, void* stream);
 
+/* Group-32 W8A8 GEMM (SDXL round-to-nearest arm):
+ *   out[m,n] = sum_g s_a[m,g] * s_w[g,n] * (sum_{k in group g} xq[m,k] * w[n,k])  (+ bias[n])
+ * with the weight grid of qdq_weight(w, 8, 32) (pyraquant/quantizers_weight.py:96-109) and the
+ * activation grid of pq_quant_rows_g32 (pyraquant/external_quant.py:104-109).  Per-group int32 partial
+ * sums are exact; the fp32 combination runs in ascending group order as
+ * sum = fma(float(partial), s_a * s_w, sum).  No counterpart kernel exists in the reference (its
+ * SDXL deployment arm is per-channel; the group-32 grid is only simulated there).
+ *   s_a [M, K/32] fp32 contiguous (as written by pq_quant_rows_g32);
+ *   s_w [K/32, N] fp32 contiguous (group-major: the transpose of the [N, K/32] scale table);
+ *   K % 128 == 0, N % 4 == 0, ldx % 16 == 0, ldw % 16 == 0, 16-byte aligned xq, w, s_a, s_w. */
+int pq_int8_gemm_g32(const int8_t* xq, int64_t ldx, const float* s_a,
+                     const int8_t* w, int64_t ldw, const float* s_w, const float* bias,
+                     void* out, int out_dtype, int64_t ldo,
+                     int64_t M, int64_t N, int64_t K,
+                     void* workspace, size_t ws_bytes, void* stream);
+
 /* Feathered scatter of routed rows back over the cached canvas, in place: the pull form of
  * fuse_patch_predictions (flux/routing.py:328-379).  For canvas token j with contributor list
  * e in [ptr[j], ptr[j+1]):  local = sum_e beta[e] * y[src[e], :], bsum = sum_e beta[e] (both

@@ -137,7 +137,7 @@ def selftest_unfused_reference(xq, sx, w_int8, w_scale, bias, out_dtype=torch.bf
 def gemm_g32(xq: torch.Tensor, s_a: torch.Tensor, wq: torch.Tensor, s_w: torch.Tensor, bias, out_dtype,
              group: int = 32) -> torch.Tensor:
     """y[m,n] = sum_g s_a[m,g] s_w[n,g] sum_{k in g} xq[m,k] wq[n,k] (+bias): exact per-group int32
-    partials, fp32 combination in ascending group order.  Grids: pyraquant/quantizers_weight.py:96-109
+    partials, fp32 combination in ascending group order with one fused multiply-add per group.  Grids: pyraquant/quantizers_weight.py:96-109
     and pyraquant/external_quant.py:104-109."""
     M, K = xq.shape
     N = wq.shape[0]
@@ -146,8 +146,11 @@ def gemm_g32(xq: torch.Tensor, s_a: torch.Tensor, wq: torch.Tensor, s_w: torch.T
     for g in range(G):
         a = xq[:, g * group:(g + 1) * group].to(torch.int32)
         b = wq[:, g * group:(g + 1) * group].to(torch.int32)
-        part = (a @ b.t()).float()
-        y = y + part * (s_a[:, g][:, None] * s_w[:, g][None, :])
+        part = (a @ b.t()).double()                       # |part| <= 32 * 127^2: exact
+        s = (s_a[:, g][:, None] * s_w[:, g][None, :])     # fp32 product of the two scales
+        # fused multiply-add in fp32: the product part * s is exact in fp64 (20 + 24 bits) and the sum is rounded
+        # to fp32 afterwards
+        y = (y.double() + part * s.double()).float()
     if bias is not None:
         y = y + bias[None, :]
     return y.to(out_dtype)

@@ -18,14 +18,11 @@
 #include <unordered_map>
 #include <vector>
 
-#include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace pq {
 namespace {
 
-constexpr int BM = 128;          // rows per tile = tensor-memory lanes
-constexpr int BK = 128;          // K bytes per stage = one 128-byte swizzle row
-constexpr int UMMA_K = 32;       // K per tcgen05.mma kind::i8
 constexpr int kNumEpiWarps = 8;
 constexpr int kGemmThreads = 64 + 32 * kNumEpiWarps;
 constexpr int kLR = 32;          // low-rank width handled in the epilogue
@@ -69,89 +66,16 @@ struct TileCoord {
   int row0, row_end, n0, set;
 };
 
-// Tile schedule.  CTA b sits at (bm, bn) = (b / pn, b % pn) of a pm x pn grid laid over the tile matrix and
-// walks it with strides (pm, pn): all row tiles of one column tile first, then the next column tile.  At any
-// moment the CTAs touch pn weight tiles (each shared by pm CTAs, unchanged from step to step, so they stay in
-// L2) and pm activation tiles (each shared by pn CTAs); a CTA's column tile changes only every m_steps
-// tiles, so the epilogue's per-column data is loaded rarely.  The walker holds the position of one role; all
-// roles walk the same sequence.  No divisions: the loops are counters.
-struct TileWalker {
-  int mt, ntile;        // current row tile / column tile
-  int bm, pm, pn, mt_total, nt, mt0;
-  __device__ __forceinline__ void init(const GemmParams& p, int mt0_, int mt_total_, int nt_) {
-    pm = p.sched_pm; pn = p.sched_pn; mt_total = mt_total_; nt = nt_; mt0 = mt0_;
-    bm = static_cast<int>(blockIdx.x) / pn;
-    mt = bm; ntile = static_cast<int>(blockIdx.x) - bm * pn;
-  }
-  __device__ __forceinline__ bool valid() const { return ntile < nt && mt < mt_total; }
-  __device__ __forceinline__ void advance() {       // to the next existing tile of this CTA (or past the end)
-    mt += pm;
-    if (mt >= mt_total) { mt = bm; ntile += pn; }
-  }
-  __device__ __forceinline__ TileCoord coord(const GemmParams& p, int BN) const {
-    TileCoord c;
-    if (mt < mt0) { c.set = 0; c.row0 = mt * BM; c.row_end = p.m_split; }
-    else { c.set = 1; c.row0 = p.m_split + (mt - mt0) * BM; c.row_end = p.M; }
-    c.n0 = ntile * BN;
-    return c;
-  }
-};
-
-// Bounded wait on an mbarrier phase.  The first probe is inline; the polling loop (wall-clock budget, abort
-// flag) lives out of line to keep the role loops small.
-__device__ __noinline__ bool wait_or_abort_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  uint64_t t0 = 0;
-  for (uint32_t i = 1; i < kWaitMaxPolls; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 0) {
-      if (*abort_flag != 0) return false;
-      uint64_t now = global_timer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitBudgetNs) return false;
-    }
-  }
-  return false;
-}
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return wait_or_abort_slow(bar, parity, abort_flag);
+// Row range, column start and weight set of the walker's current tile.
+__device__ __forceinline__ TileCoord tile_coord(const TileWalker& w, const GemmParams& p, int mt0, int BN) {
+  TileCoord c;
+  if (w.mt < mt0) { c.set = 0; c.row0 = w.mt * BM; c.row_end = p.m_split; }
+  else { c.set = 1; c.row0 = p.m_split + (w.mt - mt0) * BM; c.row_end = p.M; }
+  c.n0 = w.ntile * BN;
+  return c;
 }
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-
-// In-quad 4x4 transpose: on entry lane q of a quad holds w[j] = word (source lane q, block j); on exit it
-// holds w[k] = word (source lane k, block q).
-__device__ __forceinline__ void quad_transpose(uint32_t (&w)[4], int q) {
-  const bool hi = (q & 2) != 0;
-  uint32_t s0 = hi ? w[0] : w[2], s1 = hi ? w[1] : w[3];
-  uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 2), r1 = __shfl_xor_sync(0xffffffffu, s1, 2);
-  uint32_t v0 = hi ? r0 : w[0], v1 = hi ? r1 : w[1], v2 = hi ? w[2] : r0, v3 = hi ? w[3] : r1;
-  const bool odd = (q & 1) != 0;
-  s0 = odd ? v0 : v1; s1 = odd ? v2 : v3;
-  r0 = __shfl_xor_sync(0xffffffffu, s0, 1); r1 = __shfl_xor_sync(0xffffffffu, s1, 1);
-  w[0] = odd ? r0 : v0; w[1] = odd ? v1 : r0; w[2] = odd ? r1 : v2; w[3] = odd ? v3 : r1;
-}
-
-// Ragged / unaligned outputs: one packed pair (columns col, col+1 of one row) at a time.  Kept out of line so
-// that the common path stays small.
-__device__ __noinline__ void store_pairs_slow(void* out, int64_t ldo, int rA, int rB, int col0, int row_end, int N,
-                                              uint4 a, uint4 b) {
-  const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
-  unsigned short* o = static_cast<unsigned short*>(out);
-#pragma unroll 1
-  for (int j = 0; j < 4; ++j) {
-    const int col = col0 + j * 8;
-#pragma unroll 1
-    for (int r = 0; r < 2; ++r) {
-      const int row = r == 0 ? rA : rB;
-      const uint32_t w = r == 0 ? wa[j] : wb[j];
-      if (row >= row_end) continue;
-      unsigned short* p = o + static_cast<int64_t>(row) * ldo + col;
-      if (col < N) p[0] = static_cast<unsigned short>(w & 0xFFFFu);
-      if (col + 1 < N) p[1] = static_cast<unsigned short>(w >> 16);
-    }
-  }
-}
 
 // Test hook: raw accumulators of one n8 block (rows rA / rB, columns col, col+1).
 __device__ __noinline__ void dump_acc(int32_t* dbg, int N, int rA, int rB, int col, int row_end, uint32_t v0, uint32_t v1,
@@ -210,10 +134,10 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       int stage = 0; uint32_t phase = 0; long long issued = 0; bool ok = true;
-      TileWalker w; w.init(p, mt0, mt_total, nt);
+      TileWalker w; w.init(p.sched_pm, p.sched_pn, mt_total, nt);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance()) {
-        const TileCoord c = w.coord(p, BN);
+        const TileCoord c = tile_coord(w, p, mt0, BN);
 #pragma unroll 1
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!wait_or_abort(&empty_bar[stage], phase ^ 1u, abort_flag)) {
@@ -243,7 +167,7 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc_i8(BM, BN);
       int stage = 0; uint32_t phase = 0; int it = 0; bool ok = true;
-      TileWalker w; w.init(p, mt0, mt_total, nt);
+      TileWalker w; w.init(p.sched_pm, p.sched_pn, mt_total, nt);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance(), ++it) {
         const int buf = it & 1;
@@ -325,14 +249,14 @@ pq_int8_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       }
     };
 
-    TileWalker w; w.init(p, mt0, mt_total, nt);
-    TileCoord c = w.coord(p, BN);
+    TileWalker w; w.init(p.sched_pm, p.sched_pn, mt_total, nt);
+    TileCoord c = tile_coord(w, p, mt0, BN);
     if (w.valid()) load_row_data(c, af, srow);
 #pragma unroll 1
     for (; w.valid(); ++it) {
       w.advance();
       const bool has_next = w.valid();
-      const TileCoord c_nx = w.coord(p, BN);
+      const TileCoord c_nx = tile_coord(w, p, mt0, BN);
       const int buf = it & 1;
       const uint32_t use = static_cast<uint32_t>(it >> 1);
 
@@ -518,37 +442,6 @@ pq_i8_mma_issue_loop_kernel(int iters, long long* cycles, int32_t* status) {
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      return nullptr;
-    return reinterpret_cast<EncodeTiledFn>(f);
-  }();
-  return fn;
-}
-
-// int8 matrix [rows, K] with row stride ld bytes; box = 128 bytes x box_rows, 128-byte swizzle, zero fill.
-int make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return PQ_ERR_CUDA;
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) { g_last_cuda_error = static_cast<int>(r); return PQ_ERR_CUDA; }
-  return PQ_OK;
-}
-
 struct WKey {
   const void* ptr; int64_t N, K, ld; int bn;
   bool operator==(const WKey& o) const { return ptr == o.ptr && N == o.N && K == o.K && ld == o.ld && bn == o.bn; }
@@ -687,21 +580,7 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
   const int ntl = static_cast<int>((N + bn - 1) / bn);
   int max_ctas = options().gemm_max_ctas > 0 ? options().gemm_max_ctas : sm_count();
   int best_pm = 1, best_pn = 1;
-  long long best_steps = -1;
-  for (int pn = 1; pn <= ntl && pn <= max_ctas; ++pn) {
-    int pm = max_ctas / pn;
-    if (pm > mt) pm = mt;
-    if (pm < 1) continue;
-    const long long steps = static_cast<long long>((mt + pm - 1) / pm) * ((ntl + pn - 1) / pn);
-    if (best_steps < 0 || steps < best_steps || (steps == best_steps && pn > best_pn)) {
-      best_steps = steps; best_pm = pm; best_pn = pn;
-    }
-  }
-  if (options().gemm_pn > 0 && options().gemm_pn <= ntl && options().gemm_pn <= max_ctas) {
-    best_pn = options().gemm_pn;
-    best_pm = max_ctas / best_pn; if (best_pm > mt) best_pm = mt;
-    if (options().gemm_pm > 0 && options().gemm_pm <= best_pm) best_pm = options().gemm_pm;
-  }
+  choose_cta_grid(mt, ntl, max_ctas, &best_pm, &best_pn);
   p.sched_pm = best_pm; p.sched_pn = best_pn;
   p.sched_m_steps = (mt + best_pm - 1) / best_pm;
   p.sched_n_rounds = (ntl + best_pn - 1) / best_pn;

@@ -16,7 +16,7 @@ as the reference's ``quant_rows`` does, :221), and the shape rules are wider (K 
 multiple of 8, instead of K % 64 == 0 and N % 256 == 0).
 
 Added entry points (not in the reference module): ``quant_rows_g32``, ``gather_quant_rows``,
-``int8_gemm_grouped``, ``nested4_codes``, ``Int8LinearRouted``.
+``int8_gemm_grouped``, ``int8_gemm_g32``, ``nested4_codes``, ``Int8LinearRouted``, ``Int8LinearG32``.
 """
 from __future__ import annotations
 
@@ -90,6 +90,12 @@ def int8_gemm_grouped(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, m_hi: int,
     assert xq.is_cuda
     return torch.ops.pq_b200.int8_gemm_grouped(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, int(m_hi),
                                                ops.dtype_code(out_dtype))
+
+
+def int8_gemm_g32(xq, s_a, w_int8, s_w_gm, bias, out_dtype):
+    """Group-32 GEMM: s_a [M, K/32] (from ``quant_rows_g32``), s_w_gm [K/32, N] group-major weight scales."""
+    assert xq.is_cuda
+    return torch.ops.pq_b200.int8_gemm_g32(xq, s_a, w_int8, s_w_gm, bias, ops.dtype_code(out_dtype))
 
 
 def dequant_epilogue(acc: torch.Tensor, s_row: torch.Tensor, s_col: torch.Tensor,
@@ -195,6 +201,50 @@ class Int8Linear(nn.Module):
     def extra_repr(self) -> str:
         return (f"in={self.in_features}, out={self.out_features}, int8 per-channel W / per-token A, "
                 f"sm_100a tcgen05 kernel")
+
+
+def _quantize_weight_g32(w: torch.Tensor, group: int = 32) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Group-32 symmetric absmax INT8 weights: the integer grid behind ``qdq_weight(w, 8, 32)``
+    (pyraquant/quantizers_weight.py:96-109).  Returns codes [N,K] and scales [N, K/32]."""
+    out_f, in_f = w.shape
+    wg = w.float().reshape(out_f, in_f // group, group)
+    amax = wg.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8)
+    scale = amax / torch.full_like(amax, 127.0)
+    codes = torch.round(wg / scale).clamp_(-127, 127).to(torch.int8)
+    return codes.reshape(out_f, in_f).contiguous(), scale[..., 0].contiguous()
+
+
+class Int8LinearG32(nn.Module):
+    """W8A8 Linear with one scale per 32 input channels on both operands (the SDXL round-to-nearest arm:
+    weights on the ``qdq_weight(w, 8, 32)`` grid, activations on the per-token ``dyn_group`` grid with group 32),
+    executed on the integer grid.  Needs in_features % 128 == 0."""
+
+    def __init__(self, lin: nn.Linear, device: Optional[torch.device] = None):
+        super().__init__()
+        w = lin.weight.detach()
+        if device is not None:
+            w = w.to(device)
+        codes, scale = _quantize_weight_g32(w)
+        self.register_buffer("weight_int8", codes)
+        self.register_buffer("w_scale", scale)                               # [N, K/32]
+        self.register_buffer("w_scale_gm", scale.t().contiguous(), persistent=False)   # [K/32, N] for the kernel
+        if lin.bias is not None:
+            b = lin.bias.detach().float()
+            self.register_buffer("bias", (b.to(device) if device is not None else b).contiguous())
+        else:
+            self.bias = None
+        self.in_features = int(lin.in_features)
+        self.out_features = int(lin.out_features)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        xq, sa = quant_rows_g32(x2)
+        y = int8_gemm_g32(xq, sa, self.weight_int8, self.w_scale_gm, self.bias, x2.dtype)
+        return y.reshape(*shape[:-1], self.out_features)
+
+    def extra_repr(self) -> str:
+        return f"in={self.in_features}, out={self.out_features}, int8 group-32 W / per-token group-32 A"
 
 
 class Int8LinearRouted(Int8Linear):

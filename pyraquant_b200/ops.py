@@ -173,6 +173,28 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
     return out
 
 
+def _gemm_g32_impl(xq: Tensor, s_a: Tensor, w_int8: Tensor, s_w_gm: Tensor, bias: Optional[Tensor],
+                   out_dtype: torch.dtype) -> Tensor:
+    """s_a [M, K/32]; s_w_gm [K/32, N] (group-major)."""
+    assert xq.is_cuda and xq.dtype == torch.int8 and xq.dim() == 2 and w_int8.dtype == torch.int8
+    M, K = xq.shape
+    N = w_int8.shape[0]
+    assert w_int8.shape[1] == K and K % 128 == 0, (w_int8.shape, K)
+    assert s_a.shape == (M, K // 32) and s_w_gm.shape == (K // 32, N), (s_a.shape, s_w_gm.shape)
+    xq = xq.contiguous(); w_int8 = w_int8.contiguous()
+    s_a = s_a.contiguous().float(); s_w_gm = s_w_gm.contiguous().float()
+    if bias is not None:
+        bias = bias.contiguous().float()
+    out = torch.empty((M, N), dtype=out_dtype, device=xq.device)
+    ws = status_word(xq.device)
+    with torch.cuda.device(xq.device):
+        rc = _lib.load().pq_int8_gemm_g32(xq.data_ptr(), K, s_a.data_ptr(), w_int8.data_ptr(), K, s_w_gm.data_ptr(),
+                                          _ptr(bias), out.data_ptr(), _dt(out_dtype), N, M, N, K, ws.data_ptr(),
+                                          ws.numel() * 4, _stream(xq))
+    _lib.check(rc, f"pq_int8_gemm_g32(M={M}, N={N}, K={K})")
+    return out
+
+
 def _dequant_epilogue_impl(acc: Tensor, s_row: Tensor, s_col: Tensor, bias: Optional[Tensor],
                            out_dtype: torch.dtype) -> Tensor:
     assert acc.is_cuda and acc.dtype == torch.int32 and acc.is_contiguous()
@@ -270,6 +292,17 @@ def int8_gemm_grouped_op(xq: Tensor, s_row: Tensor, w_hi: Tensor, s_hi: Tensor, 
 @int8_gemm_grouped_op.register_fake
 def _(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, m_hi, out_dtype_code):
     return xq.new_empty((xq.shape[0], w_hi.shape[0]), dtype=_CODE2DT[out_dtype_code])
+
+
+@torch.library.custom_op("pq_b200::int8_gemm_g32", mutates_args=(), device_types="cuda")
+def int8_gemm_g32_op(xq: Tensor, s_a: Tensor, w_int8: Tensor, s_w_gm: Tensor, bias: Optional[Tensor],
+                     out_dtype_code: int) -> Tensor:
+    return _gemm_g32_impl(xq, s_a, w_int8, s_w_gm, bias, _CODE2DT[out_dtype_code])
+
+
+@int8_gemm_g32_op.register_fake
+def _(xq, s_a, w_int8, s_w_gm, bias, out_dtype_code):
+    return xq.new_empty((xq.shape[0], w_int8.shape[0]), dtype=_CODE2DT[out_dtype_code])
 
 
 @torch.library.custom_op("pq_b200::dequant_epilogue", mutates_args=(), device_types="cuda")

@@ -279,6 +279,43 @@ def test_reference_selftest_assertions(cuda_dev):
     assert rep["act_quant_mismatch_elems"] == 0 and rep["act_scale_max_rel_err"] == 0.0
 
 
+# ------------------------------------------------------------------------------------------------ group-32 path
+@pytest.mark.parametrize("M,K,N", [(128, 128, 128), (300, 640, 640), (257, 1280, 1280), (1000, 2560, 640),
+                                   (77, 640, 5120), (512, 5120, 1280), (130, 256, 264)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_gemm_g32_matches_oracle(cuda_dev, M, K, N, dtype):
+    """SDXL W8A8 group-32 shapes (config 3) in miniature: integer grid from the oracle, GEMM on the GPU."""
+    g = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    w = torch.randn(N, K, generator=g) * 0.02
+    b = torch.randn(N, generator=g) * 0.01
+    xq, sa = oracle.quant_rows_g32(x)
+    wq, sw = oracle.quant_weight_g32(w)
+    d = cuda_dev
+    for bias in (b, None):
+        y = int8_exec.int8_gemm_g32(xq.to(d), sa.to(d), wq.to(d), sw.t().contiguous().to(d),
+                                    None if bias is None else bias.to(d), dtype).cpu()
+        want = oracle.gemm_g32(xq, sa, wq, sw, bias, dtype)
+        assert torch.equal(y, want)                  # exact partial sums and the same fp32 operation order
+        assert max_rel_err(y, oracle.gemm_g32_f64(xq, sa, wq, sw, bias)) <= TOL
+
+
+def test_int8linear_g32_module(cuda_dev):
+    g = torch.Generator().manual_seed(33)
+    lin = nn.Linear(640, 1280, bias=True)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(1280, 640, generator=g) * 0.02); lin.bias.copy_(torch.randn(1280, generator=g) * 0.01)
+    x = torch.randn(3, 77, 640, generator=g).to(torch.float16)
+    q = int8_exec.Int8LinearG32(lin.to(torch.float16), device=cuda_dev)
+    wq, sw = oracle.quant_weight_g32(lin.weight.detach().float())
+    assert torch.equal(q.weight_int8.cpu(), wq) and torch.equal(q.w_scale.cpu(), sw)
+    y = q(x.to(cuda_dev)).cpu()
+    xq, sa = oracle.quant_rows_g32(x.reshape(-1, 640))
+    want = oracle.gemm_g32(xq, sa, wq, sw, lin.bias.detach().float(), torch.float16).reshape(3, 77, 1280)
+    assert torch.equal(y, want)
+    assert set(q.state_dict()) == {"weight_int8", "w_scale", "bias"}
+
+
 # ------------------------------------------------------------------------------------------------ full-size properties
 def test_full_size_quant_and_gemm_properties(cuda_dev):
     """BASELINE config 2 row count (M = 65536 + 512) at K = 3072 -> N = 3072: sizes the CPU oracle cannot
