@@ -151,6 +151,30 @@ int pq_scatter_rows(const void* y, int64_t ldy, int64_t M_act,
                     int64_t n_tokens, void* canvas, int64_t ldc, int64_t rows, int64_t C,
                     int dtype, void* stream);
 
+/* Linear forward for callers that cannot allocate device memory (no counterpart in the reference, which
+ * allocates its intermediates with torch.empty on every call):
+ *   out = fused_gemm(quant_rows(x), w, s_col, bias)      -- Int8Linear without a low-rank branch.
+ * Some callers may not call cudaMalloc at all: a server that gave all device memory to its own pool, code inside
+ * a stream capture, a plugin with a fixed memory budget.  They still need somewhere to put the int8 codes and
+ * row scales that exist only between the two kernels; here that place is a fixed __device__ array inside the
+ * library (pq_noalloc_scratch_bytes() bytes, about 16 MiB, held on every GPU that loads the library until the
+ * process exits).  The call performs no cudaMalloc/cudaFree and uses no allocating library routine.
+ * Limits: M <= PQ_NOALLOC_MAX_ROWS and M * K <= PQ_NOALLOC_MAX_CODE_BYTES, else PQ_ERR_WORKSPACE; otherwise
+ * the rules of pq_quant_rows and pq_int8_gemm apply (x and out in `dtype`).
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current): make that first call before starting any stream capture.
+ * All calls share the one array: two calls whose kernels can overlap on the GPU (different streams, or
+ * different host threads on different streams) race on it -- serialise them.  *status_word (optional)
+ * receives the device address whose first word the GEMM sets if a bounded wait gives up; it is cleared at the
+ * start of every call and can be read with pq_read_status_word. */
+#define PQ_NOALLOC_MAX_ROWS 16384
+#define PQ_NOALLOC_MAX_CODE_BYTES (16u * 1024u * 1024u)
+size_t pq_noalloc_scratch_bytes(void);
+int pq_int8_linear_noalloc(const void* x, int dtype, int64_t ldx,
+                           const int8_t* w, int64_t ldw, const float* s_col, const float* bias,
+                           void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                           void** status_word, void* stream);
+
 /* Copies the workspace status word to the host after synchronising `stream` and maps it to a
  * pq_status (PQ_OK or PQ_ERR_TIMEOUT); *raw receives the word itself (role and barrier that gave
  * up) when raw != NULL.  The word is cleared when `clear` is non-zero. */

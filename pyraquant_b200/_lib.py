@@ -47,6 +47,9 @@ SIGNATURES = {
                                  c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
     "pq_scatter_rows": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                 c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "pq_noalloc_scratch_bytes": (c_size_t, []),
+    "pq_int8_linear_noalloc": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                       c_int64, c_int64, c_int64, c_int64, POINTER(c_void_p), c_void_p]),
     "pq_read_status_word": (c_int, [c_void_p, POINTER(c_int32), c_int, c_void_p]),
     "pq_i8_mma_issue_loop": (c_int, [c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
 }
