@@ -66,8 +66,8 @@ extern "C" int pq_int8_linear_noalloc(const void* x, int dtype, int64_t ldx, con
   float* scales = reinterpret_cast<float*>(b + kScalesOff);
   int8_t* codes = reinterpret_cast<int8_t*>(b + kCodesOff);
   // The array keeps whatever the previous call left.  Codes and scales are fully overwritten for the rows in
-  // use; the status word must read zero unless THIS call fails, so it is cleared first (a memset node, not an
-  // allocation).
+  // use; the status word must read zero unless THIS call fails, so it is cleared first (cudaMemsetAsync
+  // allocates nothing).
   PQ_CUDA_TRY(cudaMemsetAsync(b, 0, sizeof(int32_t), static_cast<cudaStream_t>(stream)));
   rc = pq_quant_rows(x, dtype, M, K, ldx, codes, scales, stream);
   if (rc != PQ_OK) return rc;
