@@ -95,6 +95,9 @@ int pq_dequant_epilogue(const int32_t* acc, const float* s_row, const float* s_c
  *   s_row [M], s_col [N], bias [N] or NULL: fp32;
  *   t [M,R] (row stride ldt) and lb [R,N] (row stride ldb) in lr_dtype, both NULL or both set,
  *   R == 32 (the reference's rank) when set;
+ *   lb_t: NULL, or the transpose of lb as a contiguous [N,R] matrix (16-byte aligned).  With it the rank-32
+ *   term is computed by tcgen05.mma kind::f16 on the tensor cores; without it by warp-level mma.sync in the
+ *   epilogue, which is markedly slower for small K.  Same result up to fp32 summation order;
  *   out [M,N] row stride ldo in out_dtype;
  *   dbg_acc: NULL, or int32 [M,N] contiguous that receives the raw accumulators (tests);
  *   workspace: NULL or >= PQ_GEMM_WORKSPACE_BYTES device bytes; word 0 is a status word that the
@@ -103,7 +106,7 @@ int pq_dequant_epilogue(const int32_t* acc, const float* s_row, const float* s_c
 #define PQ_GEMM_WORKSPACE_BYTES 256
 int pq_int8_gemm(const int8_t* xq, int64_t ldx, const float* s_row,
                  const int8_t* w, int64_t ldw, const float* s_col, const float* bias,
-                 const void* t, int64_t ldt, const void* lb, int64_t ldb, int R, int lr_dtype,
+                 const void* t, int64_t ldt, const void* lb, int64_t ldb, const void* lb_t, int R, int lr_dtype,
                  void* out, int out_dtype, int64_t ldo,
                  int64_t M, int64_t N, int64_t K,
                  void* workspace, size_t ws_bytes, int32_t* dbg_acc, void* stream);
@@ -117,8 +120,8 @@ int pq_int8_gemm_grouped(const int8_t* xq, int64_t ldx, const float* s_row,
                          const int8_t* w_hi, const float* s_col_hi,
                          const int8_t* w_lo, const float* s_col_lo, int64_t ldw,
                          const float* bias,
-                         const void* t, int64_t ldt, const void* lb, int64_t ldb, int R, int lr_dtype,
-                         void* out, int out_dtype, int64_t ldo,
+                         const void* t, int64_t ldt, const void* lb, int64_t ldb, const void* lb_t, int R,
+                         int lr_dtype, void* out, int out_dtype, int64_t ldo,
                          int64_t M_hi, int64_t M, int64_t N, int64_t K,
                          void* workspace, size_t ws_bytes, void* stream);
 

@@ -19,31 +19,11 @@
 #include <vector>
 
 #include "gemm_common.cuh"
+#include "gemm_lr_tc.cuh"
 
 namespace pq {
 namespace {
 
-constexpr int kNumEpiWarps = 8;
-constexpr int kGemmThreads = 64 + 32 * kNumEpiWarps;
-constexpr int kLR = 32;          // low-rank width handled in the epilogue
-
-struct GemmParams {
-  const float* s_row;
-  const float* s_col[2];
-  const float* bias;
-  const void* t;        // [M, 32] low-rank activations
-  const void* lb;       // [32, N] low-rank up-projection
-  void* out;
-  int32_t* dbg_acc;
-  int32_t* status;
-  int64_t ldt, ldb, ldo;
-  int M, N, K;
-  int m_split;          // rows [0, m_split) use weight set 0, rows [m_split, M) weight set 1
-  int sched_pm, sched_pn;   // the CTAs form a sched_pm x sched_pn grid over (row tile, column tile)
-  int sched_m_steps;        // ceil(row tiles / sched_pm)
-  int sched_n_rounds;       // ceil(column tiles / sched_pn)
-  int has_bias;
-};
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -61,21 +41,6 @@ struct SmemLayout {
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamic = kTotal + 1024;                // slack for manual 1024-byte alignment
 };
-
-struct TileCoord {
-  int row0, row_end, n0, set;
-};
-
-// Row range, column start and weight set of the walker's current tile.
-__device__ __forceinline__ TileCoord tile_coord(const TileWalker& w, const GemmParams& p, int mt0, int BN) {
-  TileCoord c;
-  if (w.mt < mt0) { c.set = 0; c.row0 = w.mt * BM; c.row_end = p.m_split; }
-  else { c.set = 1; c.row0 = p.m_split + (w.mt - mt0) * BM; c.row_end = p.M; }
-  c.n0 = w.ntile * BN;
-  return c;
-}
-
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // Test hook: raw accumulators of one n8 block (rows rA / rB, columns col, col+1).
 __device__ __noinline__ void dump_acc(int32_t* dbg, int N, int rA, int rB, int col, int row_end, uint32_t v0, uint32_t v1,
@@ -526,8 +491,8 @@ int choose_block_n(int64_t M, int64_t N) {
 
 int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t* w0, const float* sc0,
                 const int8_t* w1, const float* sc1, int64_t ldw, const float* bias, const void* t, int64_t ldt,
-                const void* lb, int64_t ldb, int R, int lr_dtype, void* out, int out_dtype, int64_t ldo,
-                int64_t m_split, int64_t M, int64_t N, int64_t K, void* workspace, size_t ws_bytes,
+                const void* lb, int64_t ldb, const void* lb_t, int R, int lr_dtype, void* out, int out_dtype,
+                int64_t ldo, int64_t m_split, int64_t M, int64_t N, int64_t K, void* workspace, size_t ws_bytes,
                 int32_t* dbg_acc, void* stream) {
   if (M < 0 || N <= 0 || K <= 0 || m_split < 0 || m_split > M) return PQ_ERR_SHAPE;
   if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return PQ_ERR_SHAPE;
@@ -547,6 +512,7 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
     if (lr_dtype != out_dtype) return PQ_ERR_UNSUPPORTED;
     if (ldt < R || ldb < N) return PQ_ERR_SHAPE;
     if (ldt % 8 != 0 || ldb % 8 != 0 || N % 8 != 0 || !aligned_to(t, 16) || !aligned_to(lb, 16)) return PQ_ERR_ALIGN;
+    if (lb_t != nullptr && !aligned_to(lb_t, 16)) return PQ_ERR_ALIGN;
   }
   if (workspace != nullptr && ws_bytes < PQ_GEMM_WORKSPACE_BYTES) return PQ_ERR_WORKSPACE;
 
@@ -587,6 +553,8 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
   const int grid = best_pm * best_pn;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool dbg = dbg_acc != nullptr;
+  if (has_lr && lb_t != nullptr)      // rank-32 term on the tensor cores (needs the K-major copy of lb)
+    return launch_gemm_lr_tc(bn, out_dtype == PQ_DTYPE_BF16, dbg, tmA, tmW0, tmW1, t, ldt, lb_t, M, N, p, grid, st);
   if (out_dtype == PQ_DTYPE_BF16)
     return launch_by_shape<__nv_bfloat16>(bn, stages, has_lr, dbg, tmA, tmW0, tmW1, p, grid, st);
   return launch_by_shape<__half>(bn, stages, has_lr, dbg, tmA, tmW0, tmW1, p, grid, st);
@@ -599,18 +567,20 @@ using namespace pq;
 
 extern "C" int pq_int8_gemm(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t* w, int64_t ldw,
                             const float* s_col, const float* bias, const void* t, int64_t ldt, const void* lb,
-                            int64_t ldb, int R, int lr_dtype, void* out, int out_dtype, int64_t ldo, int64_t M,
-                            int64_t N, int64_t K, void* workspace, size_t ws_bytes, int32_t* dbg_acc, void* stream) {
-  return gemm_common(xq, ldx, s_row, w, s_col, nullptr, nullptr, ldw, bias, t, ldt, lb, ldb, R, lr_dtype, out,
+                            int64_t ldb, const void* lb_t, int R, int lr_dtype, void* out, int out_dtype, int64_t ldo,
+                            int64_t M, int64_t N, int64_t K, void* workspace, size_t ws_bytes, int32_t* dbg_acc,
+                            void* stream) {
+  return gemm_common(xq, ldx, s_row, w, s_col, nullptr, nullptr, ldw, bias, t, ldt, lb, ldb, lb_t, R, lr_dtype, out,
                      out_dtype, ldo, M, M, N, K, workspace, ws_bytes, dbg_acc, stream);
 }
 
 extern "C" int pq_int8_gemm_grouped(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t* w_hi,
                                     const float* s_col_hi, const int8_t* w_lo, const float* s_col_lo, int64_t ldw,
                                     const float* bias, const void* t, int64_t ldt, const void* lb, int64_t ldb,
-                                    int R, int lr_dtype, void* out, int out_dtype, int64_t ldo, int64_t M_hi,
-                                    int64_t M, int64_t N, int64_t K, void* workspace, size_t ws_bytes, void* stream) {
-  return gemm_common(xq, ldx, s_row, w_hi, s_col_hi, w_lo, s_col_lo, ldw, bias, t, ldt, lb, ldb, R, lr_dtype, out,
+                                    const void* lb_t, int R, int lr_dtype, void* out, int out_dtype, int64_t ldo,
+                                    int64_t M_hi, int64_t M, int64_t N, int64_t K, void* workspace, size_t ws_bytes,
+                                    void* stream) {
+  return gemm_common(xq, ldx, s_row, w_hi, s_col_hi, w_lo, s_col_lo, ldw, bias, t, ldt, lb, ldb, lb_t, R, lr_dtype, out,
                      out_dtype, ldo, M_hi, M, N, K, workspace, ws_bytes, nullptr, stream);
 }
 

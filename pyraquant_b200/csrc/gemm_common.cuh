@@ -6,11 +6,38 @@
 #include "common.cuh"
 
 namespace pq {
+
+struct GemmParams {
+  const float* s_row;
+  const float* s_col[2];
+  const float* bias;
+  const void* t;        // [M, 32] low-rank activations
+  const void* lb;       // [32, N] low-rank up-projection
+  void* out;
+  int32_t* dbg_acc;
+  int32_t* status;
+  int64_t ldt, ldb, ldo;
+  int M, N, K;
+  int m_split;          // rows [0, m_split) use weight set 0, rows [m_split, M) weight set 1
+  int sched_pm, sched_pn;   // the CTAs form a sched_pm x sched_pn grid over (row tile, column tile)
+  int sched_m_steps;        // ceil(row tiles / sched_pm)
+  int sched_n_rounds;       // ceil(column tiles / sched_pn)
+  int has_bias;
+};
+
+struct TileCoord {
+  int row0, row_end, n0, set;
+};
+
 namespace {
 
 constexpr int BM = 128;          // rows per tile = tensor-memory lanes
 constexpr int BK = 128;          // K bytes per stage = one 128-byte swizzle row
 constexpr int UMMA_K = 32;       // K per tcgen05.mma kind::i8
+
+constexpr int kNumEpiWarps = 8;
+constexpr int kGemmThreads = 64 + 32 * kNumEpiWarps;
+constexpr int kLR = 32;          // low-rank width handled in the epilogue
 
 // Bounded wait on an mbarrier phase.  The first probe is inline; the polling loop (wall-clock budget, abort
 // flag) lives out of line to keep the role loops small.
@@ -31,6 +58,8 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   if (mbar_try_wait(bar, parity)) return true;
   return wait_or_abort_slow(bar, parity, abort_flag);
 }
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // In-quad 4x4 transpose: on entry lane q of a quad holds w[j] = word (source lane q, block j); on exit it
 // holds w[k] = word (source lane k, block q).
@@ -86,6 +115,15 @@ struct TileWalker {
     if (mt >= mt_total) { mt = bm; ntile += pn; }
   }
 };
+
+// Row range, column start and weight set of the walker's current tile.
+__device__ __forceinline__ TileCoord tile_coord(const TileWalker& w, const GemmParams& p, int mt0, int BN) {
+  TileCoord c;
+  if (w.mt < mt0) { c.set = 0; c.row0 = w.mt * BM; c.row_end = p.m_split; }
+  else { c.set = 1; c.row0 = p.m_split + (w.mt - mt0) * BM; c.row_end = p.M; }
+  c.n0 = w.ntile * BN;
+  return c;
+}
 
 // Host: CTA grid pm x pn (pm * pn <= max_ctas) with the fewest steps ceil(mt/pm) * ceil(nt/pn); ties go to
 // the widest pn (fewer sweeps over the rows).  Option overrides gemm_pn / gemm_pm win when they fit.

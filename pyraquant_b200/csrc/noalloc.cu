@@ -71,6 +71,7 @@ extern "C" int pq_int8_linear_noalloc(const void* x, int dtype, int64_t ldx, con
   PQ_CUDA_TRY(cudaMemsetAsync(b, 0, sizeof(int32_t), static_cast<cudaStream_t>(stream)));
   rc = pq_quant_rows(x, dtype, M, K, ldx, codes, scales, stream);
   if (rc != PQ_OK) return rc;
-  return pq_int8_gemm(codes, K, scales, w, ldw, s_col, bias, nullptr, 0, nullptr, 0, 0, dtype, out, dtype, ldo, M, N, K,
+  return pq_int8_gemm(codes, K, scales, w, ldw, s_col, bias, nullptr, 0, nullptr, 0, nullptr, 0, dtype, out, dtype, ldo, M, N,
+                      K,
                       b, kStatusBytes, nullptr, stream);
 }

@@ -79,17 +79,19 @@ def int8_gemm_fused(xq: torch.Tensor, s_row: torch.Tensor, w_int8: torch.Tensor,
     return torch.ops.pq_b200.int8_gemm(xq, s_row, w_int8, w_scale, bias, None, None, ops.dtype_code(out_dtype))
 
 
-def int8_gemm_lr(xq, s_row, w_i8, w_scale, bias, t, lb, out_dtype):
-    """Fused GEMM with the low-rank up-projection ``t @ lb`` added before the bias (reference :303-309)."""
+def int8_gemm_lr(xq, s_row, w_i8, w_scale, bias, t, lb, out_dtype, lb_t=None):
+    """Fused GEMM with the low-rank up-projection ``t @ lb`` added before the bias (reference :303-309).
+    ``lb_t`` (optional, not in the reference signature) is a cached ``lb.t().contiguous()``; without it the
+    transpose is made on every call."""
     assert xq.is_cuda
-    return torch.ops.pq_b200.int8_gemm(xq, s_row, w_i8, w_scale, bias, t, lb, ops.dtype_code(out_dtype))
+    return torch.ops.pq_b200.int8_gemm(xq, s_row, w_i8, w_scale, bias, t, lb, ops.dtype_code(out_dtype), lb_t)
 
 
-def int8_gemm_grouped(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, m_hi: int, out_dtype):
+def int8_gemm_grouped(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, m_hi: int, out_dtype, lb_t=None):
     """Rows [0, m_hi) against (w_hi, s_hi), rows [m_hi, M) against (w_lo, s_lo), one launch."""
     assert xq.is_cuda
     return torch.ops.pq_b200.int8_gemm_grouped(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, int(m_hi),
-                                               ops.dtype_code(out_dtype))
+                                               ops.dtype_code(out_dtype), lb_t)
 
 
 def int8_gemm_g32(xq, s_a, w_int8, s_w_gm, bias, out_dtype):
@@ -175,6 +177,14 @@ class Int8Linear(nn.Module):
             self.lr_A = None
             self.lr_B = None
 
+    def _lr_Bt(self) -> torch.Tensor:
+        """K-major copy of lr_B for the tensor-core low-rank path, made once per device/dtype (not part of the state)."""
+        c = getattr(self, "_lr_Bt_cache", None)
+        if c is None or c.device != self.lr_B.device or c.dtype != self.lr_B.dtype or c.shape[0] != self.lr_B.shape[1]:
+            c = self.lr_B.t().contiguous()
+            self._lr_Bt_cache = c
+        return c
+
     def _fusable_lowrank(self, x2: torch.Tensor) -> bool:
         return (self.lr_A is not None and self.lr_A.shape[1] == 32 and x2.shape[1] % 32 == 0
                 and self.lr_A.dtype == x2.dtype and self.out_features % 8 == 0)
@@ -187,7 +197,7 @@ class Int8Linear(nn.Module):
         if self._fusable_lowrank(x2):
             t = x2.to(self.lr_A.dtype) @ self.lr_A                 # [M, r], rounded to the activation dtype
             xq, sx = quant_rows(x2)
-            y = int8_gemm_lr(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B, x2.dtype)
+            y = int8_gemm_lr(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B, x2.dtype, self._lr_Bt())
             return y.reshape(*shape[:-1], self.out_features)
         y = int8_linear_2d(x2, self.weight_int8, self.w_scale, self.bias)
         if self.lr_A is not None:                                  # shapes the fused epilogue does not take
@@ -260,24 +270,24 @@ class Int8LinearRouted(Int8Linear):
 
     def forward_rows(self, x2: torch.Tensor, m_hi: int) -> torch.Tensor:
         """x2 [M,K] already gathered and ordered hi-tier rows first."""
-        t = lb = None
+        t = lb = lbt = None
         if self._fusable_lowrank(x2):
             t = x2.to(self.lr_A.dtype) @ self.lr_A
-            lb = self.lr_B
+            lb = self.lr_B; lbt = self._lr_Bt()
         xq, sx = quant_rows(x2)
         return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self.weight_lo, self.w_scale_lo,
-                                 self.bias, t, lb, m_hi, x2.dtype)
+                                 self.bias, t, lb, m_hi, x2.dtype, lbt)
 
     def forward_gathered(self, canvas: torch.Tensor, row_idx: torch.Tensor, m_hi: int) -> torch.Tensor:
         """Gather + quantise in one kernel straight from the canvas, then the two-tier GEMM."""
-        t = lb = None
+        t = lb = lbt = None
         xq, sx = gather_quant_rows(canvas, row_idx)
         if self.lr_A is not None and self.lr_A.shape[1] == 32 and self.lr_A.dtype == canvas.dtype:
             xg = torch.ops.pq_b200.gather_rows(canvas, row_idx)
             t = xg @ self.lr_A
-            lb = self.lr_B
+            lb = self.lr_B; lbt = self._lr_Bt()
         return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self.weight_lo, self.w_scale_lo,
-                                 self.bias, t, lb, m_hi, canvas.dtype)
+                                 self.bias, t, lb, m_hi, canvas.dtype, lbt)
 
 
 # --------------------------------------------------------------------------- model conversion

@@ -17,6 +17,8 @@ from . import _lib
 Tensor = torch.Tensor
 
 _DT = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16}
+# rank-32 term of the fused GEMM: tcgen05 tensor cores (True) or warp-level mma.sync in the epilogue (False)
+LOWRANK_ON_TENSOR_CORES = True
 _status_words: Dict[int, Tensor] = {}
 
 
@@ -124,7 +126,7 @@ def _gather_rows_impl(canvas: Tensor, row_idx: Tensor) -> Tensor:
 def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias: Optional[Tensor],
                t: Optional[Tensor], lb: Optional[Tensor], out_dtype: torch.dtype,
                dbg_acc: Optional[Tensor] = None, w_lo: Optional[Tensor] = None, s_lo: Optional[Tensor] = None,
-               m_hi: Optional[int] = None) -> Tensor:
+               m_hi: Optional[int] = None, lb_t: Optional[Tensor] = None) -> Tensor:
     assert xq.is_cuda and xq.dtype == torch.int8 and xq.dim() == 2 and xq.stride(1) == 1
     assert w_int8.dtype == torch.int8 and w_int8.dim() == 2 and w_int8.stride(1) == 1
     M, K = xq.shape
@@ -153,20 +155,24 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
         ldt, ldb = t.stride(0), lb.stride(0)
         if M == 1:
             ldt = max(ldt, R)
+        if lb_t is None and R == 32 and LOWRANK_ON_TENSOR_CORES:
+            lb_t = lb.t().contiguous()        # K-major copy for the tcgen05 low-rank path (callers may cache it)
+        if lb_t is not None:
+            assert lb_t.shape == (N, R) and lb_t.dtype == out_dtype and lb_t.is_contiguous()
     ws = status_word(xq.device)
     lib = _lib.load()
     ldx = xq.stride(0) if M > 1 else max(K, xq.stride(0))
     with torch.cuda.device(xq.device):
         if w_lo is None:
             rc = lib.pq_int8_gemm(xq.data_ptr(), ldx, s_row.data_ptr(), w_int8.data_ptr(), w_int8.stride(0),
-                                  w_scale.data_ptr(), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, R, _dt(out_dtype),
-                                  out.data_ptr(), _dt(out_dtype), N, M, N, K, ws.data_ptr(), ws.numel() * 4,
+                                  w_scale.data_ptr(), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, _ptr(lb_t), R,
+                                  _dt(out_dtype), out.data_ptr(), _dt(out_dtype), N, M, N, K, ws.data_ptr(), ws.numel() * 4,
                                   _ptr(dbg_acc), _stream(xq))
         else:
             assert w_lo.shape == w_int8.shape and w_lo.stride() == w_int8.stride() and s_lo is not None
             rc = lib.pq_int8_gemm_grouped(xq.data_ptr(), ldx, s_row.data_ptr(), w_int8.data_ptr(),
                                           w_scale.data_ptr(), w_lo.data_ptr(), s_lo.contiguous().data_ptr(),
-                                          w_int8.stride(0), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, R,
+                                          w_int8.stride(0), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, _ptr(lb_t), R,
                                           _dt(out_dtype), out.data_ptr(), _dt(out_dtype), N, int(m_hi), M, N, K,
                                           ws.data_ptr(), ws.numel() * 4, _stream(xq))
     _lib.check(rc, f"pq_int8_gemm(M={M}, N={N}, K={K})")
@@ -273,24 +279,25 @@ def _(canvas, row_idx):
 
 @torch.library.custom_op("pq_b200::int8_gemm", mutates_args=(), device_types="cuda")
 def int8_gemm_op(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias: Optional[Tensor],
-                 t: Optional[Tensor], lb: Optional[Tensor], out_dtype_code: int) -> Tensor:
-    return _gemm_impl(xq, s_row, w_int8, w_scale, bias, t, lb, _CODE2DT[out_dtype_code])
+                 t: Optional[Tensor], lb: Optional[Tensor], out_dtype_code: int,
+                 lb_t: Optional[Tensor] = None) -> Tensor:
+    return _gemm_impl(xq, s_row, w_int8, w_scale, bias, t, lb, _CODE2DT[out_dtype_code], lb_t=lb_t)
 
 
 @int8_gemm_op.register_fake
-def _(xq, s_row, w_int8, w_scale, bias, t, lb, out_dtype_code):
+def _(xq, s_row, w_int8, w_scale, bias, t, lb, out_dtype_code, lb_t=None):
     return xq.new_empty((xq.shape[0], w_int8.shape[0]), dtype=_CODE2DT[out_dtype_code])
 
 
 @torch.library.custom_op("pq_b200::int8_gemm_grouped", mutates_args=(), device_types="cuda")
 def int8_gemm_grouped_op(xq: Tensor, s_row: Tensor, w_hi: Tensor, s_hi: Tensor, w_lo: Tensor, s_lo: Tensor,
                          bias: Optional[Tensor], t: Optional[Tensor], lb: Optional[Tensor], m_hi: int,
-                         out_dtype_code: int) -> Tensor:
-    return _gemm_impl(xq, s_row, w_hi, s_hi, bias, t, lb, _CODE2DT[out_dtype_code], None, w_lo, s_lo, m_hi)
+                         out_dtype_code: int, lb_t: Optional[Tensor] = None) -> Tensor:
+    return _gemm_impl(xq, s_row, w_hi, s_hi, bias, t, lb, _CODE2DT[out_dtype_code], None, w_lo, s_lo, m_hi, lb_t)
 
 
 @int8_gemm_grouped_op.register_fake
-def _(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, m_hi, out_dtype_code):
+def _(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, m_hi, out_dtype_code, lb_t=None):
     return xq.new_empty((xq.shape[0], w_hi.shape[0]), dtype=_CODE2DT[out_dtype_code])
 
 

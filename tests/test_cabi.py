@@ -66,7 +66,7 @@ def test_gemm_argument_checks():
 
     def gemm(xq=p16, ldx=64, s_row=p16, w=p16, ldw=64, s_col=p16, bias=None, t=None, ldt=0, lb=None, ldb=0, R=0,
              lr_dtype=0, out=p16, out_dtype=0, ldo=64, M=8, N=64, K=64, ws=None, ws_bytes=0):
-        return lib.pq_int8_gemm(xq, ldx, s_row, w, ldw, s_col, bias, t, ldt, lb, ldb, R, lr_dtype, out, out_dtype,
+        return lib.pq_int8_gemm(xq, ldx, s_row, w, ldw, s_col, bias, t, ldt, lb, ldb, None, R, lr_dtype, out, out_dtype,
                                 ldo, M, N, K, ws, ws_bytes, None, None)
 
     assert gemm(M=0) == 0

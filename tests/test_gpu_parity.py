@@ -157,8 +157,13 @@ def run_gemm_case(dev, M, N, K, *, lowrank, bias, dtype=torch.bfloat16, seed=0, 
                                    (300, 512, 1280), (1000, 3072, 512), (257, 1280, 2560), (129, 264, 80),
                                    (4350, 1288, 144)])
 def test_gemm_small_shapes(cuda_dev, M, N, K):
-    run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=True, seed=M + N + K)
+    run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=True, seed=M + N + K)        # low-rank term on tcgen05
     run_gemm_case(cuda_dev, M, N, K, lowrank=False, bias=False, seed=M + N + K + 1)
+    ops.LOWRANK_ON_TENSOR_CORES = False                                             # low-rank term by mma.sync
+    try:
+        run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=True, seed=M + N + K)
+    finally:
+        ops.LOWRANK_ON_TENSOR_CORES = True
 
 
 def test_gemm_extreme_accumulators_exact(cuda_dev):
