@@ -48,7 +48,7 @@ const char* pq_status_str(int status);
 int pq_last_cuda_error(void);
 
 /* Internal tuning / test knobs ("gemm_stages", "gemm_block_n", "gemm_pm", "gemm_pn",
- * "gemm_max_ctas").  Unknown keys return PQ_ERR_UNSUPPORTED.  Not part of the reference API. */
+ * "gemm_max_ctas", "gemm_pair").  Unknown keys return PQ_ERR_UNSUPPORTED.  Not part of the reference API. */
 int pq_set_option(const char* key, int value);
 int pq_get_option(const char* key, int* value);
 

@@ -40,6 +40,8 @@ struct Options {
   int gemm_pm = 0;         // tile schedule override: CTA grid rows (0 = auto)
   int gemm_pn = 0;         // tile schedule override: CTA grid columns (0 = auto)
   int gemm_max_ctas = 0;   // 0 = one per SM
+  int gemm_debug_timing = 0;   // experiments: cycle counters into workspace + 256 (CTA-pair kernel)
+  int gemm_pair = 1;       // CTA-pair (cta_group::2) kernel: 0 off, 1 when the problem is large enough, 2 whenever it applies
 };
 Options& options();
 
@@ -100,6 +102,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking probe of a phase (try_wait may suspend the thread for a while; this never does).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "gemm_common.cuh"
+#include "gemm_2cta.cuh"
 #include "gemm_lr_tc.cuh"
 
 namespace pq {
@@ -521,6 +522,25 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
   if (bn == 256) { if (stages != 3) stages = 4; }
   else { if (stages != 4) stages = 6; }
 
+  GemmParams p;
+  p.s_row = s_row; p.s_col[0] = sc0; p.s_col[1] = (m_split < M) ? sc1 : sc0; p.bias = bias;
+  p.t = t; p.lb = lb; p.out = out; p.dbg_acc = dbg_acc; p.status = static_cast<int32_t*>(workspace);
+  p.ldt = ldt; p.ldb = ldb; p.ldo = ldo;
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+  p.m_split = static_cast<int>(m_split);
+  p.has_bias = bias != nullptr ? 1 : 0;
+  p.timing = (options().gemm_debug_timing != 0 && workspace != nullptr && ws_bytes >= 256 + 4096 * 64)
+                 ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + 256) : nullptr;
+  p.sched_pm = p.sched_pn = p.sched_m_steps = p.sched_n_rounds = 1;
+
+  // CTA-pair kernel: one weight set, 256-column tiles, enough 256-row tiles to occupy the SM pairs, and the
+  // K-major low-rank factor when there is a low-rank term
+  if (options().gemm_pair != 0 && m_split == M && bn == 256 && (!has_lr || lb_t != nullptr) &&
+      ((M + 255) / 256) * ((N + 255) / 256) >= (options().gemm_pair == 2 ? 1 : sm_count() / 2)) {
+    return launch_gemm_pair(out_dtype == PQ_DTYPE_BF16, dbg_acc != nullptr, xq, ldx, w0, ldw, has_lr ? t : nullptr, ldt,
+                            has_lr ? lb_t : nullptr, M, N, K, p, static_cast<cudaStream_t>(stream));
+  }
+
   CUtensorMap tmA, tmW0, tmW1;
   int rc = make_tile_map(&tmA, xq, M, K, ldx, BM);
   if (rc != PQ_OK) return rc;
@@ -532,14 +552,6 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
   } else {
     tmW1 = tmW0;
   }
-
-  GemmParams p;
-  p.s_row = s_row; p.s_col[0] = sc0; p.s_col[1] = (m_split < M) ? sc1 : sc0; p.bias = bias;
-  p.t = t; p.lb = lb; p.out = out; p.dbg_acc = dbg_acc; p.status = static_cast<int32_t*>(workspace);
-  p.ldt = ldt; p.ldb = ldb; p.ldo = ldo;
-  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
-  p.m_split = static_cast<int>(m_split);
-  p.has_bias = bias != nullptr ? 1 : 0;
 
   // CTA grid pm x pn over the tile matrix: fewest steps first, then the widest pn (fewer sweeps over the rows)
   const int mt = static_cast<int>((m_split + BM - 1) / BM + (M - m_split + BM - 1) / BM);

@@ -1,0 +1,596 @@
+// Fused INT8 GEMM on CTA pairs (tcgen05 cta_group::2): out = float(xq @ w^T) * (s_row x s_col) (+ t @ lb) (+ bias).
+//
+// Two CTAs on neighbouring SMs (a cluster of 2) compute one 256 x 256 tile: CTA r owns rows [128 r, 128 r + 128) of
+// the tile and keeps them in its own tensor memory; each CTA stages its own 128 x 128-byte activation tile and only
+// HALF of the weight tile (rows [128 r, +128) of the 256) per stage, and one thread of CTA 0 issues every
+// tcgen05.mma.cta_group::2 (256 x 256 x 32) for the pair.  Compared with the single-CTA kernel this halves the
+// weight bytes each SM pulls from L2 and writes into shared memory, which is what bounds that kernel, and leaves
+// room for a six-stage ring.  No TMA multicast is used: every CTA loads its own bytes.
+//
+// Synchronisation.  "full" barriers live in CTA 0 and count the bytes of both CTAs' copies (CTA 1's TMA instructions
+// name CTA 0's barrier).  Everything the MMA thread publishes ("stage free", "accumulator complete", "low-rank MMAs
+// done") is committed twice, once to each CTA's copy of the barrier.  What the MMA thread waits for from the
+// epilogues ("accumulator drained", "scaled accumulator written back") is one barrier in CTA 0 with 16 arrivals, the
+// eight epilogue warps of CTA 1 arriving remotely.  Every wait is bounded; a wait that gives up records a code in the
+// status word, raises its CTA's abort flag and lets the CTA drain; the peer then runs into its own limits.  Both
+// CTAs meet at a cluster barrier before they exit so that neither leaves while its peer may still signal it.
+#include <type_traits>
+
+#include "gemm_2cta.cuh"
+#include "gemm_common.cuh"
+
+namespace pq {
+namespace {
+
+constexpr int PBN = 256;                   // tile columns
+constexpr int PSTAGES = 6;
+constexpr int kHalfB = PBN / 2;            // weight rows staged per CTA
+constexpr int kRowBytesLr = kLR * 2;       // 64-byte rows of the t / lbT tiles
+
+struct PairSmem {
+  static constexpr int kABytes = BM * BK;
+  static constexpr int kBBytes = kHalfB * BK;
+  static constexpr int kStageBytes = kABytes + kBBytes;            // per CTA
+  static constexpr int kTOff = PSTAGES * kStageBytes;
+  static constexpr int kTBytes = BM * kRowBytesLr;                 // per CTA: its 128 rows of t
+  static constexpr int kLbOff = kTOff + 2 * kTBytes;
+  static constexpr int kLbBytes = kHalfB * kRowBytesLr;            // per CTA: its 128 rows of lbT
+  static constexpr int kScolOff = kLbOff + 2 * kLbBytes;            // two lbT buffers: consecutive column tiles alternate
+  static constexpr int kBiasOff = kScolOff + PBN * 4;
+  static constexpr int kBarOff = kBiasOff + PBN * 4;
+  // full[S], empty[S], tfull[2], tempty[2], t_full[2], lb_full[2], ylr_ready[2], lr_done[2]
+  static constexpr int kNumBars = 2 * PSTAGES + 12;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kTotal = kMiscOff + 16;
+  static_assert(kTotal <= 232448, "exceeds the 227 KB shared memory of one CTA");
+};
+
+// ---------------------------------------------------------------------------------------------
+// cluster / pair primitives
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `smem_addr` (an address of the executing CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load whose completion bytes are counted by a barrier that may live in the peer CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(m), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// completion of all MMAs issued so far -> one arrival on the barrier at `cluster_addr` (any CTA of the pair)
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t kmajor_sw64_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(512 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(4) << 61;
+  return d;
+}
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N, bool bf16) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x8.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __noinline__ void dump_acc_pair(int32_t* dbg, int N, int rA, int rB, int col, int row_end, uint32_t v0, uint32_t v1,
+                                           uint32_t v2, uint32_t v3) {
+  if (rA < row_end && col < N) dbg[static_cast<int64_t>(rA) * N + col] = static_cast<int32_t>(v0);
+  if (rA < row_end && col + 1 < N) dbg[static_cast<int64_t>(rA) * N + col + 1] = static_cast<int32_t>(v1);
+  if (rB < row_end && col < N) dbg[static_cast<int64_t>(rB) * N + col] = static_cast<int32_t>(v2);
+  if (rB < row_end && col + 1 < N) dbg[static_cast<int64_t>(rB) * N + col + 1] = static_cast<int32_t>(v3);
+}
+
+// Walker over pair tiles: the pairs (not the CTAs) form the pm x pn grid.
+struct PairWalker {
+  int mt, ntile, bm, pm, pn, mt_total, nt;
+  __device__ __forceinline__ void init(int pair, int pm_, int pn_, int mt_total_, int nt_) {
+    pm = pm_; pn = pn_; mt_total = mt_total_; nt = nt_;
+    bm = pair / pn; mt = bm; ntile = pair - bm * pn;
+  }
+  __device__ __forceinline__ bool valid() const { return ntile < nt && mt < mt_total; }
+  __device__ __forceinline__ void advance() { mt += pm; if (mt >= mt_total) { mt = bm; ntile += pn; } }
+};
+
+template <typename OutT, bool HAS_LR, bool DBG>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+                               const __grid_constant__ CUtensorMap tmT, const __grid_constant__ CUtensorMap tmLbT,
+                               const GemmParams p) {
+  using L = PairSmem;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* empty_bar = full_bar + PSTAGES;
+  uint64_t* tfull_bar = empty_bar + PSTAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint64_t* t_full = tempty_bar + 2;
+  uint64_t* lb_full = t_full + 2;
+  uint64_t* ylr_ready = lb_full + 2;
+  uint64_t* lr_done = ylr_ready + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();          // 0 = leader (issues the MMAs), 1 = peer
+  const bool aligned_ok = (smem_u32(smem) & 1023u) == 0;
+
+  const int mt_total = (p.M + 2 * BM - 1) / (2 * BM);   // pair tiles of 256 rows
+  const int nt = (p.N + PBN - 1) / PBN;
+  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr uint32_t kTmemCols = 2 * PBN;
+  const int pair = static_cast<int>(blockIdx.x) >> 1;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmW);
+    if (HAS_LR) { tma_prefetch_desc(&tmT); tma_prefetch_desc(&tmLbT); }
+    for (int s = 0; s < PSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 2 * kNumEpiWarps);
+      mbar_init(&t_full[b], 1); mbar_init(&ylr_ready[b], 2 * kNumEpiWarps); mbar_init(&lr_done[b], 1);
+    }
+    mbar_init(&lb_full[0], 1); mbar_init(&lb_full[1], 1);
+    *abort_flag = aligned_ok ? 0 : 1;
+    if (!aligned_ok) report_timeout(p.status, 7, 7);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) { tmem_alloc_pair(tmem_holder, kTmemCols); tmem_relinquish_pair(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                 // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const bool run = aligned_ok;
+
+  // barrier addresses in the leader CTA (for remote arrivals / byte counts) and in the peer (for the second commit)
+  auto leader_addr = [&](const uint64_t* bar) { return map_to_cta(smem_u32(bar), 0u); };
+  auto peer_addr = [&](const uint64_t* bar) { return map_to_cta(smem_u32(bar), 1u); };
+
+  if (run && warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      int stage = 0; uint32_t phase = 0; long long issued = 0; bool ok = true;
+      int it = 0; int lb_col = -1; uint32_t lb_count = 0;
+      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
+#pragma unroll 1
+      for (; w.valid() && ok; w.advance(), ++it) {
+        const int row0 = w.mt * 2 * BM + static_cast<int>(rank) * BM;       // this CTA's 128 rows
+        const int n0 = w.ntile * PBN;
+        const int nhalf0 = n0 + static_cast<int>(rank) * kHalfB;            // this CTA's half of the weight tile
+        const int buf = it & 1;
+        if (HAS_LR && w.ntile != lb_col) {
+          // consecutive column tiles alternate between two lbT buffers; the buffer about to be overwritten was last
+          // read by low-rank MMAs of a tile at least two back in this CTA's sequence
+          if (it >= 2 && !wait_or_abort(&lr_done[buf], static_cast<uint32_t>(((it - 2) >> 1) & 1), abort_flag)) {
+            report_timeout(p.status, 1, 5); *abort_flag = 1; ok = false; break;
+          }
+          lb_col = w.ntile;
+          const int lbuf = static_cast<int>(lb_count & 1u);
+          if (rank == 0) mbar_arrive_expect_tx(&lb_full[lbuf], 2 * L::kLbBytes);
+          tma_load_2d_pair(smem + L::kLbOff + lbuf * L::kLbBytes, &tmLbT, leader_addr(&lb_full[lbuf]), 0, nhalf0);
+          ++lb_count;
+        }
+#pragma unroll 1
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_or_abort(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+            report_timeout(p.status, 1, 1); *abort_flag = 1; ok = false; break;
+          }
+          uint8_t* a_s = smem + stage * L::kStageBytes;
+          const uint32_t fb = leader_addr(&full_bar[stage]);
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
+          tma_load_2d_pair(a_s, &tmA, fb, kb * BK, row0);
+          tma_load_2d_pair(a_s + L::kABytes, &tmW, fb, kb * BK, nhalf0);
+          ++issued;
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (HAS_LR) {
+          // this CTA's rows of t: the slot is free once the low-rank MMAs of two tiles ago have completed
+          if (it >= 2 && !wait_or_abort(&lr_done[buf], static_cast<uint32_t>(((it - 2) >> 1) & 1), abort_flag)) {
+            report_timeout(p.status, 1, 6); *abort_flag = 1; ok = false; break;
+          }
+          if (rank == 0) mbar_arrive_expect_tx(&t_full[buf], 2 * L::kTBytes);
+          tma_load_2d_pair(smem + L::kTOff + buf * L::kTBytes, &tmT, leader_addr(&t_full[buf]), 0, row0);
+        }
+      }
+      // copies in flight must land before the CTA may exit: the last stages issued are consumed by MMAs whose
+      // completion is committed to this CTA's empty barriers
+      const int pending = issued < PSTAGES ? static_cast<int>(issued) : PSTAGES;
+      for (int i = 0; i < pending; ++i) {
+        if (--stage < 0) { stage = PSTAGES - 1; phase ^= 1u; }
+        if (!wait_or_abort(&empty_bar[stage], phase, abort_flag)) {
+          for (int k = 0; k < 64; ++k) __nanosleep(1000);
+          break;
+        }
+      }
+    }
+  } else if (run && warp == 1 && rank == 0) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_i8(2 * BM, PBN);
+      constexpr uint32_t idesc_lr = idesc_f16(2 * BM, PBN, std::is_same<OutT, __nv_bfloat16>::value);
+      int stage = 0; uint32_t phase = 0; int it = 0; bool ok = true;
+      int pending = -1, pending_col = -1, lb_col = -1; uint32_t lb_count = 0;
+      long long tm_tempty = 0, tm_full = 0;
+      auto commit_both = [&](uint64_t* bar) { tc_commit_pair(smem_u32(bar)); tc_commit_pair(peer_addr(bar)); };
+      auto issue_lowrank = [&](int pt, int pcol) -> bool {
+        const int pb = pt & 1;
+        const uint32_t par = static_cast<uint32_t>(pt >> 1) & 1u;
+        if (!wait_or_abort(&ylr_ready[pb], par, abort_flag)) { report_timeout(p.status, 2, 3); return false; }
+        if (!wait_or_abort(&t_full[pb], par, abort_flag)) { report_timeout(p.status, 2, 4); return false; }
+        if (pcol != lb_col) {          // first tile of a column: its lbT buffer is (column ordinal) & 1
+          if (!wait_or_abort(&lb_full[lb_count & 1u], (lb_count >> 1) & 1u, abort_flag)) { report_timeout(p.status, 2, 5); return false; }
+          lb_col = pcol; ++lb_count;
+        }
+        tc_fence_after();
+        const uint64_t a_desc = kmajor_sw64_desc(smem_u32(smem + L::kTOff + pb * L::kTBytes));
+        const uint64_t b_desc = kmajor_sw64_desc(smem_u32(smem + L::kLbOff + static_cast<int>((lb_count - 1u) & 1u) * L::kLbBytes));
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(pb * PBN);
+        tc_mma_f16_pair(d_tmem, a_desc, b_desc, idesc_lr, 1u);
+        tc_mma_f16_pair(d_tmem, a_desc + 2, b_desc + 2, idesc_lr, 1u);
+        commit_both(&lr_done[pb]);
+        return true;
+      };
+      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
+#pragma unroll 1
+      for (; w.valid() && ok; w.advance(), ++it) {
+        const int buf = it & 1;
+        const uint32_t use = static_cast<uint32_t>(it >> 1);
+        const long long c0 = p.timing ? clock64() : 0;
+        if (!wait_or_abort(&tempty_bar[buf], (use & 1u) ^ 1u, abort_flag)) {
+          report_timeout(p.status, 2, 2); *abort_flag = 1; ok = false; break;
+        }
+        if (p.timing) tm_tempty += clock64() - c0;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * PBN);
+#pragma unroll 1
+        for (int kb = 0; kb < num_kb; ++kb) {
+          {
+            const long long c1 = p.timing ? clock64() : 0;
+            uint64_t t0 = 0; uint32_t polls = 0; bool got = false;
+            while (true) {
+              if (mbar_try_wait(&full_bar[stage], phase)) { got = true; break; }
+              if (HAS_LR && pending >= 0 && mbar_test_wait(&ylr_ready[pending & 1], static_cast<uint32_t>(pending >> 1) & 1u)) {
+                if (!issue_lowrank(pending, pending_col)) break;
+                pending = -1;
+              }
+              if ((++polls & 255u) == 0) {
+                if (*abort_flag != 0) break;
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now; else if (now - t0 > kWaitBudgetNs) break;
+              }
+            }
+            if (!got) { report_timeout(p.status, 2, 1); *abort_flag = 1; ok = false; break; }
+            if (p.timing) tm_full += clock64() - c1;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
+          const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+          const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + L::kABytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc_mma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k), idesc,
+                           (kb > 0 || k > 0) ? 1u : 0u);
+          commit_both(&empty_bar[stage]);
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        commit_both(&tfull_bar[buf]);
+        if (HAS_LR) {
+          if (pending >= 0) {
+            if (!issue_lowrank(pending, pending_col)) { *abort_flag = 1; ok = false; break; }
+          }
+          pending = it; pending_col = w.ntile;
+        }
+      }
+      if (HAS_LR && ok && pending >= 0) {
+        if (!issue_lowrank(pending, pending_col)) *abort_flag = 1;
+      }
+      if (p.timing) { p.timing[blockIdx.x * 8 + 0] = tm_tempty; p.timing[blockIdx.x * 8 + 1] = tm_full; }
+    }
+  } else if (run && warp >= 2) {
+    // ------------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int etid = threadIdx.x - 64;
+    const int g = lane >> 2, q = lane & 3;
+    constexpr int HALF_N = PBN / 2;
+    constexpr int UNIT_N = 64;
+    constexpr int kChunks = HALF_N / UNIT_N;
+    OutT* out = static_cast<OutT*>(p.out);
+    float* scol_s = reinterpret_cast<float*>(smem + L::kScolOff);
+    float* bias_s = reinterpret_cast<float*>(smem + L::kBiasOff);
+    const bool vec_store = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    bool aborted = false;
+    int it = 0;
+    int aux_n0 = -1;
+    long long te_tfull = 0, te_p1 = 0, te_lr = 0, te_p2 = 0, te_aux = 0;
+    PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
+#pragma unroll 1
+    for (; w.valid(); w.advance(), ++it) {
+      const int row0 = w.mt * 2 * BM + static_cast<int>(rank) * BM;
+      const int n0 = w.ntile * PBN;
+      const int row_end = p.M;
+      const int buf = it & 1;
+      const uint32_t par = static_cast<uint32_t>(it >> 1) & 1u;
+
+      const long long e0 = p.timing ? clock64() : 0;
+      if (n0 != aux_n0) {
+        aux_n0 = n0;
+        epi_bar_sync();
+#pragma unroll 1
+        for (int i = etid; i < PBN; i += kNumEpiWarps * 32) {
+          const int col = n0 + i;
+          scol_s[i] = col < p.N ? p.s_col[0][col] : 0.0f;
+          bias_s[i] = (p.has_bias && col < p.N) ? p.bias[col] : 0.0f;
+        }
+        epi_bar_sync();
+      }
+      float srow[2][2];
+#pragma unroll
+      for (int mb = 0; mb < 2; ++mb) {
+        const int rA = row0 + quarter * 32 + mb * 16 + g;
+        srow[mb][0] = rA < row_end ? p.s_row[rA] : 0.0f;
+        srow[mb][1] = rA + 8 < row_end ? p.s_row[rA + 8] : 0.0f;
+      }
+
+      const long long e1 = p.timing ? clock64() : 0;
+      if (!aborted) {
+        const bool landed = wait_or_abort(&tfull_bar[buf], par, abort_flag);
+        if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 3); *abort_flag = 1; aborted = true; }
+      }
+      if (aborted) continue;
+      tc_fence_after();
+      const long long e2 = p.timing ? clock64() : 0;
+      long long e3 = e2, e4 = e2;
+
+      const uint32_t t_acc = tmem_base + static_cast<uint32_t>(buf * PBN + half * HALF_N);
+      auto unit_addr = [&](int ch, int mb) {
+        return t_acc + (static_cast<uint32_t>(quarter * 32 + mb * 16) << 16) + static_cast<uint32_t>(ch * UNIT_N);
+      };
+      uint32_t va[32], vb[32];
+
+      // scale one 16 x 64 block: int32 -> fp32 * (s_row * s_col), in place in the registers
+      auto scale_unit = [&](uint32_t (&v)[32], int ch, int mb) {
+        const int col_unit = half * HALF_N + ch * UNIT_N;
+        const float srA = srow[mb][0], srB = srow[mb][1];
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+          const int cl = col_unit + nb * 8 + 2 * q;
+          const float2 sc = *reinterpret_cast<const float2*>(scol_s + cl);
+          if constexpr (DBG) {
+            const int rA = row0 + quarter * 32 + mb * 16 + g;
+            dump_acc_pair(p.dbg_acc, p.N, rA, rA + 8, n0 + cl, row_end, v[4 * nb + 0], v[4 * nb + 1], v[4 * nb + 2], v[4 * nb + 3]);
+          }
+          v[4 * nb + 0] = __float_as_uint(__fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 0])), __fmul_rn(srA, sc.x)));
+          v[4 * nb + 1] = __float_as_uint(__fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 1])), __fmul_rn(srA, sc.y)));
+          v[4 * nb + 2] = __float_as_uint(__fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 2])), __fmul_rn(srB, sc.x)));
+          v[4 * nb + 3] = __float_as_uint(__fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 3])), __fmul_rn(srB, sc.y)));
+        }
+      };
+      // + bias, round, transpose inside quads, store one 16 x 64 block of fp32 values
+      auto store_unit = [&](const uint32_t (&v)[32], int ch, int mb) {
+        const int col_unit = half * HALF_N + ch * UNIT_N;
+        const int rA = row0 + quarter * 32 + mb * 16 + g;
+        const int rB = rA + 8;
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+          uint32_t wA[4], wB[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int nb = grp * 4 + j;
+            const float2 bi = *reinterpret_cast<const float2*>(bias_s + col_unit + nb * 8 + 2 * q);
+            wA[j] = pack2(__fadd_rn(__uint_as_float(v[4 * nb + 0]), bi.x), __fadd_rn(__uint_as_float(v[4 * nb + 1]), bi.y), OutT{});
+            wB[j] = pack2(__fadd_rn(__uint_as_float(v[4 * nb + 2]), bi.x), __fadd_rn(__uint_as_float(v[4 * nb + 3]), bi.y), OutT{});
+          }
+          const int col_grp = n0 + col_unit + grp * 32;
+          if (vec_store && col_grp + 32 <= p.N) {
+            quad_transpose(wA, q);
+            quad_transpose(wB, q);
+            if (rA < row_end)
+              st_v4(out + static_cast<int64_t>(rA) * p.ldo + col_grp + q * 8, make_uint4(wA[0], wA[1], wA[2], wA[3]));
+            if (rB < row_end)
+              st_v4(out + static_cast<int64_t>(rB) * p.ldo + col_grp + q * 8, make_uint4(wB[0], wB[1], wB[2], wB[3]));
+          } else {
+            store_pairs_slow(p.out, p.ldo, rA, rB, col_grp + 2 * q, row_end, p.N, make_uint4(wA[0], wA[1], wA[2], wA[3]),
+                             make_uint4(wB[0], wB[1], wB[2], wB[3]));
+          }
+        }
+      };
+
+      if constexpr (HAS_LR) {
+        // pass 1: scaled accumulator back to tensor memory, then the MMA thread adds t @ lb on top
+        tmem_ld_16x256b_x8(unit_addr(0, 0), va);
+#pragma unroll 1
+        for (int ch = 0; ch < kChunks; ++ch) {
+          tc_wait_ld(); wait_st();
+          tmem_ld_16x256b_x8(unit_addr(ch, 1), vb);
+          scale_unit(va, ch, 0);
+          tmem_st_x8(unit_addr(ch, 0), va);
+          tc_wait_ld(); wait_st();
+          if (ch + 1 < kChunks) tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+          scale_unit(vb, ch, 1);
+          tmem_st_x8(unit_addr(ch, 1), vb);
+        }
+        wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_addr(&ylr_ready[buf]));
+        if (p.timing) e3 = clock64();
+        const bool landed = wait_or_abort(&lr_done[buf], par, abort_flag);
+        if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 6); *abort_flag = 1; aborted = true; continue; }
+        tc_fence_after();
+        if (p.timing) e4 = clock64();
+      }
+      // final pass: (scale when there is no low-rank term,) + bias, round, store
+      tmem_ld_16x256b_x8(unit_addr(0, 0), va);
+#pragma unroll 1
+      for (int ch = 0; ch < kChunks; ++ch) {
+        tc_wait_ld();
+        tmem_ld_16x256b_x8(unit_addr(ch, 1), vb);
+        if constexpr (!HAS_LR) scale_unit(va, ch, 0);
+        store_unit(va, ch, 0);
+        tc_wait_ld();
+        if (ch + 1 < kChunks) tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+        if constexpr (!HAS_LR) scale_unit(vb, ch, 1);
+        store_unit(vb, ch, 1);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_addr(&tempty_bar[buf]));
+      if (p.timing) { te_aux += e1 - e0; te_tfull += e2 - e1; te_p1 += e3 - e2; te_lr += e4 - e3; te_p2 += clock64() - e4; }
+    }
+    if (p.timing && warp == 2 && lane == 0) {
+      p.timing[blockIdx.x * 8 + 2] = te_aux; p.timing[blockIdx.x * 8 + 3] = te_tfull; p.timing[blockIdx.x * 8 + 4] = te_p1;
+      p.timing[blockIdx.x * 8 + 5] = te_lr; p.timing[blockIdx.x * 8 + 6] = te_p2; p.timing[blockIdx.x * 8 + 7] = it;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                 // neither CTA leaves (or frees tensor memory) while its peer may still signal it
+  if (warp == 1) {
+    if (*abort_flag != 0) {
+      for (int k = 0; k < 64; ++k) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+template <typename OutT, bool HAS_LR, bool DBG>
+int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmT, const CUtensorMap& tmLbT,
+                GemmParams p, int mt_pairs, int ntl, cudaStream_t st) {
+  auto kern = pq_int8_gemm_fused_pair_kernel<OutT, HAS_LR, DBG>;
+  static int max_pairs[64] = {0};
+  int dev = 0;
+  PQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return PQ_ERR_UNSUPPORTED;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = PairSmem::kTotal;
+  cfg.stream = st;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  if (max_pairs[dev] == 0) {
+    PQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kTotal));
+    cfg.gridDim = dim3(2 * sm_count(), 1, 1);
+    int n = 0;
+    PQ_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+    if (n <= 0) return PQ_ERR_UNSUPPORTED;
+    max_pairs[dev] = n;
+  }
+  int pairs_cap = max_pairs[dev];
+  if (options().gemm_max_ctas > 0 && options().gemm_max_ctas / 2 < pairs_cap) pairs_cap = options().gemm_max_ctas / 2;
+  if (pairs_cap < 1) pairs_cap = 1;
+  choose_cta_grid(mt_pairs, ntl, pairs_cap, &p.sched_pm, &p.sched_pn);
+  cfg.gridDim = dim3(2 * p.sched_pm * p.sched_pn, 1, 1);
+  PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmT, tmLbT, p));
+  return PQ_OK;
+}
+
+int make_lr_map64(CUtensorMap* map, const void* base, int64_t rows, int64_t ld, int box_rows, bool bf16) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return PQ_ERR_CUDA;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(kLR), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kLR), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { g_last_cuda_error = static_cast<int>(r); return PQ_ERR_CUDA; }
+  return PQ_OK;
+}
+
+}  // namespace
+
+int launch_gemm_pair(bool bf16, bool dbg, const void* xq, int64_t ldx, const void* w, int64_t ldw, const void* t,
+                     int64_t ldt, const void* lb_t, int64_t M, int64_t N, int64_t K, const GemmParams& p,
+                     cudaStream_t st) {
+  CUtensorMap tmA, tmW, tmT, tmLbT;
+  int rc = make_tile_map(&tmA, xq, M, K, ldx, BM);
+  if (rc != PQ_OK) return rc;
+  rc = make_tile_map(&tmW, w, N, K, ldw, kHalfB);
+  if (rc != PQ_OK) return rc;
+  const bool has_lr = t != nullptr;
+  if (has_lr) {
+    rc = make_lr_map64(&tmT, t, M, ldt, BM, bf16);
+    if (rc != PQ_OK) return rc;
+    rc = make_lr_map64(&tmLbT, lb_t, N, kLR, kHalfB, bf16);
+    if (rc != PQ_OK) return rc;
+  } else {
+    tmT = tmA; tmLbT = tmA;
+  }
+  const int mt_pairs = static_cast<int>((M + 2 * BM - 1) / (2 * BM));
+  const int ntl = static_cast<int>((N + PBN - 1) / PBN);
+  if (bf16) {
+    if (has_lr) return dbg ? launch_pair<__nv_bfloat16, true, true>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st)
+                           : launch_pair<__nv_bfloat16, true, false>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st);
+    return dbg ? launch_pair<__nv_bfloat16, false, true>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st)
+               : launch_pair<__nv_bfloat16, false, false>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st);
+  }
+  if (has_lr) return dbg ? launch_pair<__half, true, true>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st)
+                         : launch_pair<__half, true, false>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st);
+  return dbg ? launch_pair<__half, false, true>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st)
+             : launch_pair<__half, false, false>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st);
+}
+
+}  // namespace pq

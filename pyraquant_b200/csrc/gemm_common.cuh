@@ -23,6 +23,7 @@ struct GemmParams {
   int sched_m_steps;        // ceil(row tiles / sched_pm)
   int sched_n_rounds;       // ceil(column tiles / sched_pn)
   int has_bias;
+  long long* timing;        // experiments: per-CTA cycle counters [grid][8] (NULL in normal use)
 };
 
 struct TileCoord {
@@ -125,8 +126,8 @@ __device__ __forceinline__ TileCoord tile_coord(const TileWalker& w, const GemmP
   return c;
 }
 
-// Host: CTA grid pm x pn (pm * pn <= max_ctas) with the fewest steps ceil(mt/pm) * ceil(nt/pn); ties go to
-// the widest pn (fewer sweeps over the rows).  Option overrides gemm_pn / gemm_pm win when they fit.
+// Host: CTA grid pm x pn (pm * pn <= max_ctas) with the fewest steps ceil(mt/pm) * ceil(nt/pn) plus a small charge
+// per column change; ties go to the widest pn (fewer sweeps over the rows).  Option overrides gemm_pn / gemm_pm win when they fit.
 inline void choose_cta_grid(int mt, int ntl, int max_ctas, int* pm_out, int* pn_out) {
   int best_pm = 1, best_pn = 1;
   long long best_steps = -1;
@@ -134,7 +135,9 @@ inline void choose_cta_grid(int mt, int ntl, int max_ctas, int* pm_out, int* pn_
     int pm = max_ctas / pn;
     if (pm > mt) pm = mt;
     if (pm < 1) continue;
-    const long long steps = static_cast<long long>((mt + pm - 1) / pm) * ((ntl + pn - 1) / pn);
+    // cost in quarter tiles: every step is one tile, every change of column tile costs about a quarter of one
+    const long long rounds = (ntl + pn - 1) / pn;
+    const long long steps = 4 * static_cast<long long>((mt + pm - 1) / pm) * rounds + rounds;
     if (best_steps < 0 || steps < best_steps || (steps == best_steps && pn > best_pn)) {
       best_steps = steps; best_pm = pm; best_pn = pn;
     }

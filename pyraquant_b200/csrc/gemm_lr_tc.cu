@@ -241,7 +241,7 @@ pq_int8_gemm_fused_lr_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             uint64_t t0 = 0; uint32_t polls = 0; bool got = false;
             while (true) {
               if (mbar_try_wait(&full_bar[stage], phase)) { got = true; break; }
-              if (pending >= 0 && mbar_try_wait(&ylr_ready[pending & 1], static_cast<uint32_t>(pending >> 1) & 1u)) {
+              if (pending >= 0 && mbar_test_wait(&ylr_ready[pending & 1], static_cast<uint32_t>(pending >> 1) & 1u)) {
                 if (!issue_lowrank(pending, pending_col)) break;
                 pending = -1;
               }

@@ -205,6 +205,22 @@ def test_gemm_schedule_grids(cuda_dev, pm, pn):
         _lib.set_option("gemm_pn", 0); _lib.set_option("gemm_pm", 0)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (128, 256, 256), (300, 512, 192), (1000, 768, 640), (2049, 1288, 384),
+                                   (4608, 3072, 3072)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_cta_pair_kernel(cuda_dev, M, N, K, dtype):
+    """The cta_group::2 kernel forced on for every shape it accepts: odd numbers of 128-row tiles (one CTA of the
+    last pair has no rows), ragged N, several tiles per pair, with and without the low-rank term."""
+    _lib.set_option("gemm_pair", 2)
+    try:
+        run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=True, dtype=dtype, seed=M + N)
+        run_gemm_case(cuda_dev, M, N, K, lowrank=False, bias=True, dtype=dtype, seed=M + N + 1)
+        _lib.set_option("gemm_max_ctas", 4)          # two pairs only: long per-pair tile sequences
+        run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=False, dtype=dtype, seed=M + N + 2)
+    finally:
+        _lib.set_option("gemm_pair", 1); _lib.set_option("gemm_max_ctas", 0)
+
+
 def test_gemm_cfg0_layer(cuda_dev):
     """BASELINE config 0: M=4608, K=N=3072, rank-32 branch and bias, through Int8Linear.forward."""
     L = oracle.make_layer(0, 4608, 3072, 3072)
