@@ -52,6 +52,7 @@ namespace {
 int* option_slot(const char* key) {
   Options& o = options();
   if (key == nullptr) return nullptr;
+  if (std::strcmp(key, "quant_tpr") == 0) return &o.quant_tpr;
   if (std::strcmp(key, "gemm_stages") == 0) return &o.gemm_stages;
   if (std::strcmp(key, "gemm_block_n") == 0) return &o.gemm_block_n;
   if (std::strcmp(key, "gemm_pm") == 0) return &o.gemm_pm;

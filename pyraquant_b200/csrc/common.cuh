@@ -35,6 +35,7 @@ int sm_count();
 
 // Option table shared by the .cu files (see pq_set_option).
 struct Options {
+  int quant_tpr = 0;       // quantisation kernel: threads per row override (0 = auto)
   int gemm_stages = 0;     // 0 = auto
   int gemm_block_n = 0;    // 0 = auto, else 128 or 256
   int gemm_pm = 0;         // tile schedule override: CTA grid rows (0 = auto)

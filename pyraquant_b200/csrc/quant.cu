@@ -6,8 +6,8 @@
 // Arithmetic contract (bit-exact with torch on CPU; deploy/int8_exec.py:508-509 and :83-101):
 //   scale = max(absmax, 1e-8) / 127        IEEE fp32 division
 //   q     = round_half_even(x / scale)     IEEE fp32 division, clamp to [-127, 127]
-// The division per element is replaced by a multiplication with 1/scale plus a distance-to-tie test;
-// only elements whose product lands within 2^-13 of a rounding boundary take the IEEE division.
+// The division per element is replaced by two fused multiply-adds that bracket the quotient; only chunks in
+// which a bracket straddles a rounding boundary take the IEEE division (see quant_chunk).
 #include "common.cuh"
 
 namespace pq {
@@ -29,30 +29,70 @@ template <> __device__ __forceinline__ uint32_t abs2_max<__half>(uint32_t acc, u
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
-// One element: returns the int8 code in the low byte (two's complement).  No float->int conversion
-// instruction is used (those run on the slow conversion pipe): adding 1.5 * 2^23 rounds to the nearest-even
-// integer and leaves that integer in the low mantissa bits.
-__device__ __forceinline__ uint32_t quant1(float x, float scale, float inv) {
-  const float kMagic = 12582912.0f;
-  float r = x * inv;
-  float m = r + kMagic;
-  float qf = m - kMagic;
-  float d = fabsf(r - qf);
-  if (d > 0.5f - 1.220703125e-4f) {                 // within 2^-13 of a tie: decide with the exact quotient
-    m = __fdiv_rn(x, scale) + kMagic;               // IEEE quotient, then round-half-even by the same trick
-    qf = m - kMagic;
-  }
-  m = fminf(fmaxf(m, kMagic - 127.0f), kMagic + 127.0f);      // clamp the code to [-127, 127]
-  return static_cast<uint32_t>(__float_as_int(m)) & 0xFFu;
+// Quantisation of one 16-byte chunk (8 elements) to 8 int8 codes (two 32-bit words).
+//
+// Exact contract: code = round_half_even(fl(x / scale)) with the IEEE quotient.  Fast path without a division:
+// with inv = fl(1/scale), both x * inv * (1 - 2^-18) and x * inv * (1 + 2^-18) are rounded to the nearest integer by
+// a fused multiply-add with 1.5 * 2^23 (one rounding, integer left in the low mantissa bits).  The IEEE quotient
+// lies between the two products (its relative error and that of inv are below 2^-23), and rounding is monotonic,
+// so whenever both give the same integer it is the exact answer.  If any of the 8 elements disagrees (a quotient
+// within ~2^-17 relative of a rounding boundary, about one chunk in a thousand) the chunk is redone with real
+// divisions.  Codes never leave [-127, 127] because |x| <= absmax.  No conversion instructions are used: those run
+// on a slow pipe and made the first version of this kernel issue-bound.
+struct QuantScale {
+  float scale;       // absmax / 127 (or the 1e-8 floor / 127)
+  float2 inv_lo;     // (1/scale) * (1 - 2^-18), twice
+  float2 inv_hi;     // (1/scale) * (1 + 2^-18), twice
+};
+__device__ __forceinline__ QuantScale make_quant_scale(float amax) {
+  QuantScale qs;
+  qs.scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+  const float inv = __fdiv_rn(1.0f, qs.scale);
+  const float lo = inv * (1.0f - 3.814697265625e-6f), hi = inv * (1.0f + 3.814697265625e-6f);
+  qs.inv_lo = make_float2(lo, lo);
+  qs.inv_hi = make_float2(hi, hi);
+  return qs;
 }
 
 template <typename T>
-__device__ __forceinline__ void quant_chunk(const uint4& v, float scale, float inv, uint32_t& lo, uint32_t& hi) {
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
   T tag{};
-  lo = quant1(lo_f32(v.x, tag), scale, inv) | (quant1(hi_f32(v.x, tag), scale, inv) << 8) |
-       (quant1(lo_f32(v.y, tag), scale, inv) << 16) | (quant1(hi_f32(v.y, tag), scale, inv) << 24);
-  hi = quant1(lo_f32(v.z, tag), scale, inv) | (quant1(hi_f32(v.z, tag), scale, inv) << 8) |
-       (quant1(lo_f32(v.w, tag), scale, inv) << 16) | (quant1(hi_f32(v.w, tag), scale, inv) << 24);
+  return make_float2(lo_f32(w, tag), hi_f32(w, tag));
+}
+
+__device__ __noinline__ void quant_chunk_exact(const float (&f)[8], float scale, uint32_t& lo, uint32_t& hi) {
+  const float kMagic = 12582912.0f;
+  uint32_t c[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) c[i] = static_cast<uint32_t>(__float_as_int(__fdiv_rn(f[i], scale) + kMagic)) & 0xFFu;
+  lo = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+  hi = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+}
+
+template <typename T>
+__device__ __forceinline__ void quant_chunk(const uint4& v, const QuantScale& qs, uint32_t& lo, uint32_t& hi) {
+  const float2 kMagic2 = make_float2(12582912.0f, 12582912.0f);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t m[8];
+  uint32_t differ = 0u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = unpack2<T>(w[i]);
+    const float2 a = __ffma2_rn(f, qs.inv_lo, kMagic2);
+    const float2 b = __ffma2_rn(f, qs.inv_hi, kMagic2);
+    m[2 * i] = __float_as_uint(a.x); m[2 * i + 1] = __float_as_uint(a.y);
+    differ |= (m[2 * i] ^ __float_as_uint(b.x)) | (m[2 * i + 1] ^ __float_as_uint(b.y));
+  }
+  if (differ != 0u) {
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 t = unpack2<T>(w[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    quant_chunk_exact(f, qs.scale, lo, hi);
+    return;
+  }
+  // low bytes of the eight integers -> two words
+  lo = __byte_perm(__byte_perm(m[0], m[1], 0x0040), __byte_perm(m[2], m[3], 0x0040), 0x5410);
+  hi = __byte_perm(__byte_perm(m[4], m[5], 0x0040), __byte_perm(m[6], m[7], 0x0040), 0x5410);
 }
 
 template <typename T>
@@ -110,17 +150,16 @@ pq_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, const int32_t* __rest
 #pragma unroll
       for (int w = 1; w < WPR; ++w) amax = fmaxf(amax, s_part[w0 + w]);
     }
-    const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
-    const float inv = __fdiv_rn(1.0f, scale);
+    const QuantScale qs = make_quant_scale(amax);
     if (row_ok) {
-      if (lane_in_row == 0) s[row] = scale;
+      if (lane_in_row == 0) s[row] = qs.scale;
       int8_t* qrow = q + row * static_cast<int64_t>(K);
 #pragma unroll
       for (int j = 0; j < CPT; ++j) {
         const int c = lane_in_row + j * TPR;
         if (c < nchunk) {
           uint32_t lo, hi;
-          quant_chunk<T>(v[j], scale, inv, lo, hi);
+          quant_chunk<T>(v[j], qs, lo, hi);
           st_v2(qrow + (static_cast<int64_t>(c) << 3), lo, hi);
         }
       }
@@ -136,13 +175,12 @@ pq_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, const int32_t* __rest
       float amax = amax_of_packed<T>(acc);
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
-      const float inv = __fdiv_rn(1.0f, scale);
+      const QuantScale qs = make_quant_scale(amax);
       const int c = lane_in_row + j * TPR;
       if (row_ok && c < nchunk) {
-        if ((c & 3) == 0) s[row * static_cast<int64_t>(ngroup) + (c >> 2)] = scale;
+        if ((c & 3) == 0) s[row * static_cast<int64_t>(ngroup) + (c >> 2)] = qs.scale;
         uint32_t lo, hi;
-        quant_chunk<T>(v[j], scale, inv, lo, hi);
+        quant_chunk<T>(v[j], qs, lo, hi);
         st_v2(q + row * static_cast<int64_t>(K) + (static_cast<int64_t>(c) << 3), lo, hi);
       }
     }
@@ -178,14 +216,13 @@ pq_quant_rows_kernel_long(const T* __restrict__ x, int64_t ldx, const int32_t* _
   amax = s_part[0];
 #pragma unroll
   for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, s_part[w]);
-  const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
-  const float inv = __fdiv_rn(1.0f, scale);
-  if (threadIdx.x == 0) s[row] = scale;
+  const QuantScale qs = make_quant_scale(amax);
+  if (threadIdx.x == 0) s[row] = qs.scale;
   int8_t* qrow = q + row * static_cast<int64_t>(K);
   for (int c = threadIdx.x; c < nchunk; c += kThreads) {
     uint4 v = have_src ? xrow[c] : make_uint4(0u, 0u, 0u, 0u);
     uint32_t lo, hi;
-    quant_chunk<T>(v, scale, inv, lo, hi);
+    quant_chunk<T>(v, qs, lo, hi);
     st_v2(qrow + (static_cast<int64_t>(c) << 3), lo, hi);
   }
 }
@@ -241,7 +278,12 @@ template <typename T, bool GATHER, bool GROUP32>
 int dispatch(const void* x, int64_t ldx, const int32_t* row_idx, int64_t src_rows, int8_t* q, float* s, int64_t M,
              int K, cudaStream_t st) {
   const int nchunk = K >> 3;
-  // pick the smallest team whose registers hold the row with <= 8 chunks per thread
+  // team size (threads per row) and chunks per thread: the row must fit the team's registers
+  const int force = options().quant_tpr;
+  if (force == 32 && nchunk <= 32 * 12) return launch_one<T, GATHER, GROUP32, 32, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (force == 64 && nchunk <= 64 * 8) return launch_one<T, GATHER, GROUP32, 64, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (force == 128 && nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (force == 256 && nchunk <= 256 * 8) return launch_one<T, GATHER, GROUP32, 256, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (nchunk <= 32 * 2) return launch_one<T, GATHER, GROUP32, 32, 2>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (nchunk <= 32 * 4) return launch_one<T, GATHER, GROUP32, 32, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (nchunk <= 64 * 4) return launch_one<T, GATHER, GROUP32, 64, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st);

@@ -24,6 +24,12 @@ class HostRowPipeline:
 
     def __call__(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
         """x_host [M,K] and out_host [M,N] are pinned CPU tensors; returns when out_host is complete."""
+        self.start(x_host, out_host)
+        self.finish()
+
+    def start(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """Enqueues the whole pipeline and returns at once; several pipelines started back to back share the
+        copy engines (PCIe is full duplex, so a read-heavy and a write-heavy layer overlap well)."""
         assert x_host.is_pinned() and out_host.is_pinned()
         M = x_host.shape[0]
         cur = torch.cuda.current_stream(self.device)
@@ -47,5 +53,8 @@ class HostRowPipeline:
                 self.s_out.wait_event(done)
                 out_host[r0:r1].copy_(y, non_blocking=True)
                 y.record_stream(self.s_out)
-        cur.wait_stream(self.s_out)
+
+    def finish(self) -> None:
+        """Blocks until every output row of the last `start` has reached host memory."""
+        torch.cuda.current_stream(self.device).wait_stream(self.s_out)
         self.s_out.synchronize()
