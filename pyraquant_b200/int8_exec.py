@@ -55,27 +55,44 @@ def _m_bucket(M: int) -> int:
 
 
 # --------------------------------------------------------------------------- operator wrappers
+# Every operator exists as a torch custom op (torch.ops.pq_b200.*, with fake implementations, for tracing and
+# torch.compile).  In eager mode the wrappers below call the same implementation function directly: the
+# dispatcher round trip of a Python custom op costs tens of microseconds per call, more than the kernels
+# themselves at the 1K stage (the reference met the same problem with Triton's launcher,
+# deploy/run_sdxl_latency.py:144-147).
+def _eager() -> bool:
+    return not torch.compiler.is_compiling()
+
+
 def quant_rows(x2: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """[M,K] bf16/fp16 -> (int8 codes [M,K], fp32 scale [M]); rows may be strided (no copy)."""
     assert x2.dim() == 2 and x2.is_cuda
+    if _eager():
+        return ops._quant_rows_impl(x2)
     return torch.ops.pq_b200.quant_rows(x2)
 
 
 def quant_rows_g32(x2: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Per-token, per-32-channel scales: (int8 [M,K], fp32 [M, K/32])."""
     assert x2.dim() == 2 and x2.is_cuda
+    if _eager():
+        return ops._quant_rows_g32_impl(x2)
     return torch.ops.pq_b200.quant_rows_g32(x2)
 
 
 def gather_quant_rows(canvas: torch.Tensor, row_idx: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Rows ``row_idx`` (int32, -1 = zero padding row) of ``canvas`` [rows,K], quantised per token."""
     assert canvas.dim() == 2 and canvas.is_cuda
+    if _eager():
+        return ops._gather_quant_rows_impl(canvas, row_idx)
     return torch.ops.pq_b200.gather_quant_rows(canvas, row_idx)
 
 
 def int8_gemm_fused(xq: torch.Tensor, s_row: torch.Tensor, w_int8: torch.Tensor, w_scale: torch.Tensor,
                     bias: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
     assert xq.is_cuda
+    if _eager():
+        return ops._gemm_impl(xq, s_row, w_int8, w_scale, bias, None, None, out_dtype)
     return torch.ops.pq_b200.int8_gemm(xq, s_row, w_int8, w_scale, bias, None, None, ops.dtype_code(out_dtype))
 
 
@@ -84,12 +101,16 @@ def int8_gemm_lr(xq, s_row, w_i8, w_scale, bias, t, lb, out_dtype, lb_t=None):
     ``lb_t`` (optional, not in the reference signature) is a cached ``lb.t().contiguous()``; without it the
     transpose is made on every call."""
     assert xq.is_cuda
+    if _eager():
+        return ops._gemm_impl(xq, s_row, w_i8, w_scale, bias, t, lb, out_dtype, lb_t=lb_t)
     return torch.ops.pq_b200.int8_gemm(xq, s_row, w_i8, w_scale, bias, t, lb, ops.dtype_code(out_dtype), lb_t)
 
 
 def int8_gemm_grouped(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, m_hi: int, out_dtype, lb_t=None):
     """Rows [0, m_hi) against (w_hi, s_hi), rows [m_hi, M) against (w_lo, s_lo), one launch."""
     assert xq.is_cuda
+    if _eager():
+        return ops._gemm_impl(xq, s_row, w_hi, s_hi, bias, t, lb, out_dtype, None, w_lo, s_lo, int(m_hi), lb_t)
     return torch.ops.pq_b200.int8_gemm_grouped(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, int(m_hi),
                                                ops.dtype_code(out_dtype), lb_t)
 
@@ -97,6 +118,8 @@ def int8_gemm_grouped(xq, s_row, w_hi, s_hi, w_lo, s_lo, bias, t, lb, m_hi: int,
 def int8_gemm_g32(xq, s_a, w_int8, s_w_gm, bias, out_dtype):
     """Group-32 GEMM: s_a [M, K/32] (from ``quant_rows_g32``), s_w_gm [K/32, N] group-major weight scales."""
     assert xq.is_cuda
+    if _eager():
+        return ops._gemm_g32_impl(xq, s_a, w_int8, s_w_gm, bias, out_dtype)
     return torch.ops.pq_b200.int8_gemm_g32(xq, s_a, w_int8, s_w_gm, bias, ops.dtype_code(out_dtype))
 
 
@@ -189,9 +212,54 @@ class Int8Linear(nn.Module):
         return (self.lr_A is not None and self.lr_A.shape[1] == 32 and x2.shape[1] % 32 == 0
                 and self.lr_A.dtype == x2.dtype and self.out_features % 8 == 0)
 
+    def _lean_forward(self, x2: torch.Tensor):
+        """Eager fast path for the common case (aligned rows, rank-32 branch or none): the two C-ABI calls are made
+        straight from here with the per-layer constants cached, skipping the generic wrappers' checks.  Returns
+        None when the input does not qualify."""
+        M, K = x2.shape
+        if (M == 0 or not x2.is_cuda or x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16 or K % 16
+                or x2.device != self.weight_int8.device or x2.dtype not in ops._DT or torch.compiler.is_compiling()):
+            return None
+        lr = self.lr_A is not None
+        if lr and not self._fusable_lowrank(x2):
+            return None
+        c = self.__dict__.get("_lean_cache")
+        wptr = self.weight_int8.data_ptr()
+        if c is None or c[0] != wptr or c[1] != x2.dtype:
+            lbt = self._lr_Bt() if lr else None
+            c = (wptr, x2.dtype, self.weight_int8.stride(0), self.w_scale.data_ptr(),
+                 self.bias.data_ptr() if self.bias is not None else None,
+                 self.lr_B.data_ptr() if lr else None, self.lr_B.stride(0) if lr else 0,
+                 lbt.data_ptr() if lr else None, ops._DT[x2.dtype], ops._LIB(), ops.status_word(x2.device))
+            self.__dict__["_lean_cache"] = c
+        _w, _dt_t, ldw, sc_ptr, b_ptr, lb_ptr, ldb, lbt_ptr, code, lib, ws = c
+        N = self.out_features
+        dev = x2.device
+        t_ptr = None
+        ldt = 0
+        if lr:
+            t = x2 @ self.lr_A                                  # [M, 32], torch's bf16/fp16 GEMM as in the reference
+            t_ptr, ldt = t.data_ptr(), t.stride(0)
+        q = torch.empty((M, K), dtype=torch.int8, device=dev)
+        sx = torch.empty((M,), dtype=torch.float32, device=dev)
+        out = torch.empty((M, N), dtype=x2.dtype, device=dev)
+        stream = ops._stream(x2)
+        with ops._on_device(x2):
+            rc = lib.pq_quant_rows(x2.data_ptr(), code, M, K, x2.stride(0) if M > 1 else K, q.data_ptr(), sx.data_ptr(), stream)
+            if rc == 0:
+                rc = lib.pq_int8_gemm(q.data_ptr(), K, sx.data_ptr(), wptr, ldw, sc_ptr, b_ptr, t_ptr, ldt, lb_ptr, ldb,
+                                      lbt_ptr, 32 if lr else 0, code, out.data_ptr(), code, N, M, N, K, ws.data_ptr(),
+                                      ws.numel() * 4, None, stream)
+        if rc:
+            ops._lib.check(rc, f"Int8Linear(M={M}, N={N}, K={K})")
+        return out
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
+        y = self._lean_forward(x2)
+        if y is not None:
+            return y.reshape(*shape[:-1], self.out_features)
         if x2.stride(1) != 1:
             x2 = x2.contiguous()
         if self._fusable_lowrank(x2):

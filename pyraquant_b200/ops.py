@@ -30,11 +30,43 @@ def _dt(dtype: torch.dtype) -> int:
 
 
 def _stream(t: Tensor) -> int:
-    return torch.cuda.current_stream(t.device).cuda_stream
+    """Raw handle of torch's current stream on the tensor's device (the cheap private accessor when it exists)."""
+    idx = t.device.index
+    try:
+        return torch._C._cuda_getCurrentRawStream(idx)
+    except AttributeError:                      # pragma: no cover
+        return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class _on_device:
+    """`with torch.cuda.device(...)` only when the tensor lives on another device than the current one: the
+    context manager costs several microseconds, which matters for the small 1K-stage layers."""
+    __slots__ = ("ctx",)
+
+    def __init__(self, t: Tensor):
+        self.ctx = None if t.device.index == torch.cuda.current_device() else torch.cuda.device(t.device)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *a):
+        if self.ctx is not None:
+            self.ctx.__exit__(*a)
 
 
 def _ptr(t: Optional[Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
+
+
+_lib_handle = None
+
+
+def _LIB():
+    global _lib_handle
+    if _lib_handle is None:
+        _lib_handle = _lib.load()
+    return _lib_handle
 
 
 def status_word(device: torch.device) -> Tensor:
@@ -75,9 +107,10 @@ def _quant_rows_impl(x2: Tensor) -> Tuple[Tensor, Tensor]:
     q = torch.empty((M, K), dtype=torch.int8, device=x2.device)
     s = torch.empty((M,), dtype=torch.float32, device=x2.device)
     ld = x2.stride(0) if M > 1 else max(K, x2.stride(0))
-    with torch.cuda.device(x2.device):
-        rc = _lib.load().pq_quant_rows(x2.data_ptr(), _dt(x2.dtype), M, K, ld, q.data_ptr(), s.data_ptr(), _stream(x2))
-    _lib.check(rc, f"pq_quant_rows(M={M}, K={K})")
+    with _on_device(x2):
+        rc = _LIB().pq_quant_rows(x2.data_ptr(), _dt(x2.dtype), M, K, ld, q.data_ptr(), s.data_ptr(), _stream(x2))
+    if rc:
+        _lib.check(rc, f"pq_quant_rows(M={M}, K={K})")
     return q, s
 
 
@@ -88,8 +121,8 @@ def _quant_rows_g32_impl(x2: Tensor) -> Tuple[Tensor, Tensor]:
     q = torch.empty((M, K), dtype=torch.int8, device=x2.device)
     s = torch.empty((M, K // 32), dtype=torch.float32, device=x2.device)
     ld = x2.stride(0) if M > 1 else max(K, x2.stride(0))
-    with torch.cuda.device(x2.device):
-        rc = _lib.load().pq_quant_rows_g32(x2.data_ptr(), _dt(x2.dtype), M, K, ld, q.data_ptr(), s.data_ptr(),
+    with _on_device(x2):
+        rc = _LIB().pq_quant_rows_g32(x2.data_ptr(), _dt(x2.dtype), M, K, ld, q.data_ptr(), s.data_ptr(),
                                            _stream(x2))
     _lib.check(rc, f"pq_quant_rows_g32(M={M}, K={K})")
     return q, s
@@ -102,8 +135,8 @@ def _gather_quant_rows_impl(canvas: Tensor, row_idx: Tensor) -> Tuple[Tensor, Te
     M = row_idx.numel()
     q = torch.empty((M, K), dtype=torch.int8, device=canvas.device)
     s = torch.empty((M,), dtype=torch.float32, device=canvas.device)
-    with torch.cuda.device(canvas.device):
-        rc = _lib.load().pq_gather_quant_rows(canvas.data_ptr(), _dt(canvas.dtype), rows, K, max(K, canvas.stride(0)),
+    with _on_device(canvas):
+        rc = _LIB().pq_gather_quant_rows(canvas.data_ptr(), _dt(canvas.dtype), rows, K, max(K, canvas.stride(0)),
                                               row_idx.data_ptr(), M, q.data_ptr(), s.data_ptr(), _stream(canvas))
     _lib.check(rc, f"pq_gather_quant_rows(M={M}, K={K})")
     return q, s
@@ -115,8 +148,8 @@ def _gather_rows_impl(canvas: Tensor, row_idx: Tensor) -> Tensor:
     rows, K = canvas.shape
     M = row_idx.numel()
     out = torch.empty((M, K), dtype=canvas.dtype, device=canvas.device)
-    with torch.cuda.device(canvas.device):
-        rc = _lib.load().pq_gather_rows(canvas.data_ptr(), _dt(canvas.dtype), rows, K, max(K, canvas.stride(0)),
+    with _on_device(canvas):
+        rc = _LIB().pq_gather_rows(canvas.data_ptr(), _dt(canvas.dtype), rows, K, max(K, canvas.stride(0)),
                                         row_idx.data_ptr(), M, out.data_ptr(), K, _stream(canvas))
     _lib.check(rc, f"pq_gather_rows(M={M}, K={K})")
     return out
@@ -160,9 +193,9 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
         if lb_t is not None:
             assert lb_t.shape == (N, R) and lb_t.dtype == out_dtype and lb_t.is_contiguous()
     ws = status_word(xq.device)
-    lib = _lib.load()
+    lib = _LIB()
     ldx = xq.stride(0) if M > 1 else max(K, xq.stride(0))
-    with torch.cuda.device(xq.device):
+    with _on_device(xq):
         if w_lo is None:
             rc = lib.pq_int8_gemm(xq.data_ptr(), ldx, s_row.data_ptr(), w_int8.data_ptr(), w_int8.stride(0),
                                   w_scale.data_ptr(), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, _ptr(lb_t), R,
@@ -175,7 +208,8 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
                                           w_int8.stride(0), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, _ptr(lb_t), R,
                                           _dt(out_dtype), out.data_ptr(), _dt(out_dtype), N, int(m_hi), M, N, K,
                                           ws.data_ptr(), ws.numel() * 4, _stream(xq))
-    _lib.check(rc, f"pq_int8_gemm(M={M}, N={N}, K={K})")
+    if rc:
+        _lib.check(rc, f"pq_int8_gemm(M={M}, N={N}, K={K})")
     return out
 
 
@@ -193,8 +227,8 @@ def _gemm_g32_impl(xq: Tensor, s_a: Tensor, w_int8: Tensor, s_w_gm: Tensor, bias
         bias = bias.contiguous().float()
     out = torch.empty((M, N), dtype=out_dtype, device=xq.device)
     ws = status_word(xq.device)
-    with torch.cuda.device(xq.device):
-        rc = _lib.load().pq_int8_gemm_g32(xq.data_ptr(), K, s_a.data_ptr(), w_int8.data_ptr(), K, s_w_gm.data_ptr(),
+    with _on_device(xq):
+        rc = _LIB().pq_int8_gemm_g32(xq.data_ptr(), K, s_a.data_ptr(), w_int8.data_ptr(), K, s_w_gm.data_ptr(),
                                           _ptr(bias), out.data_ptr(), _dt(out_dtype), N, M, N, K, ws.data_ptr(),
                                           ws.numel() * 4, _stream(xq))
     _lib.check(rc, f"pq_int8_gemm_g32(M={M}, N={N}, K={K})")
@@ -206,8 +240,8 @@ def _dequant_epilogue_impl(acc: Tensor, s_row: Tensor, s_col: Tensor, bias: Opti
     assert acc.is_cuda and acc.dtype == torch.int32 and acc.is_contiguous()
     M, N = acc.shape
     out = torch.empty((M, N), dtype=out_dtype, device=acc.device)
-    with torch.cuda.device(acc.device):
-        rc = _lib.load().pq_dequant_epilogue(acc.data_ptr(), s_row.contiguous().data_ptr(),
+    with _on_device(acc):
+        rc = _LIB().pq_dequant_epilogue(acc.data_ptr(), s_row.contiguous().data_ptr(),
                                              s_col.contiguous().data_ptr(), _ptr(bias), out.data_ptr(),
                                              _dt(out_dtype), M, N, _stream(acc))
     _lib.check(rc, "pq_dequant_epilogue")
@@ -222,8 +256,8 @@ def _scatter_rows_impl(y: Tensor, tokens: Tensor, ptr: Tensor, src: Tensor, beta
     assert beta.is_cuda and beta.dtype == torch.float32 and beta.is_contiguous()
     n_tokens = tokens.numel()
     assert ptr.numel() == n_tokens + 1 and src.numel() == beta.numel()
-    with torch.cuda.device(canvas.device):
-        rc = _lib.load().pq_scatter_rows(y.data_ptr(), max(y.stride(0), y.shape[1]), y.shape[0], tokens.data_ptr(),
+    with _on_device(canvas):
+        rc = _LIB().pq_scatter_rows(y.data_ptr(), max(y.stride(0), y.shape[1]), y.shape[0], tokens.data_ptr(),
                                          ptr.data_ptr(), src.data_ptr(), beta.data_ptr(), n_tokens,
                                          canvas.data_ptr(), max(canvas.stride(0), canvas.shape[1]), canvas.shape[0],
                                          canvas.shape[1], _dt(canvas.dtype), _stream(canvas))
