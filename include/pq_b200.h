@@ -47,8 +47,16 @@ const char* pq_status_str(int status);
 /* cudaError_t of the most recent failing CUDA call made by this library on the calling thread. */
 int pq_last_cuda_error(void);
 
-/* Internal tuning / test knobs ("gemm_stages", "gemm_block_n", "gemm_pm", "gemm_pn",
- * "gemm_max_ctas", "gemm_pair").  Unknown keys return PQ_ERR_UNSUPPORTED.  Not part of the reference API. */
+/* Internal tuning / test knobs, 0 = automatic unless stated:
+ *   "quant_tpr"         threads per row of the quantisation kernel (32, 64, 128, 256);
+ *   "gemm_stages"       depth of the operand ring of the single-CTA kernels;
+ *   "gemm_block_n"      column tile of the single-CTA kernels (128 or 256);
+ *   "gemm_pm","gemm_pn" shape of the CTA grid of the tile schedule;
+ *   "gemm_max_ctas"     upper bound of CTAs (or CTA pairs x 2) launched;
+ *   "gemm_pair"         0 = never use the CTA-pair kernel, 1 = automatic (default), 2 = whenever it is legal;
+ *   "gemm_debug_timing" 1 = the CTA-pair kernel writes per-role cycle counters to workspace + 256
+ *                       (needs ws_bytes >= 256 + 4096*64).
+ * Unknown keys return PQ_ERR_UNSUPPORTED.  Not part of the reference API. */
 int pq_set_option(const char* key, int value);
 int pq_get_option(const char* key, int* value);
 
