@@ -26,6 +26,11 @@ constexpr int PBN = 256;                   // tile columns
 constexpr int PSTAGES = 6;
 constexpr int kHalfB = PBN / 2;            // weight rows staged per CTA
 constexpr int kRowBytesLr = kLR * 2;       // 64-byte rows of the t / lbT tiles
+constexpr int kLrChunks = 2;               // the low-rank term is added in column chunks of PBN / kLrChunks
+constexpr int kLrChunkN = PBN / kLrChunks; // 128 columns: one kind::f16 MMA pair per chunk
+constexpr int kLbChunkRows = kLrChunkN / 2;   // lbT rows each CTA stages per chunk
+constexpr int kLrWarp = 2 + kNumEpiWarps;  // warp that issues the low-rank MMAs (leader CTA)
+constexpr int kPairThreads = (kLrWarp + 1) * 32;
 
 struct PairSmem {
   static constexpr int kABytes = BM * BK;
@@ -38,10 +43,10 @@ struct PairSmem {
   static constexpr int kScolOff = kLbOff + 2 * kLbBytes;            // two lbT buffers: consecutive column tiles alternate
   static constexpr int kBiasOff = kScolOff + PBN * 4;
   static constexpr int kBarOff = kBiasOff + PBN * 4;
-  // full[S], empty[S], tfull[2], tempty[2], t_full[2], lb_full[2], ylr_ready[2], lr_done[2]
-  static constexpr int kNumBars = 2 * PSTAGES + 12;
+  // full[S], empty[S], tfull[2], tempty[2], t_full[2], lb_full[2], ylr_ready[2][chunks], lr_done[2][chunks]
+  static constexpr int kNumBars = 2 * PSTAGES + 8 + 4 * kLrChunks;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
-  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kTotal = kMiscOff + 16 + 64;      // + time stamps of the cycle-counter experiments
   static_assert(kTotal <= 232448, "exceeds the 227 KB shared memory of one CTA");
 };
 
@@ -63,8 +68,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
+// Arrival on a barrier of either CTA of the pair.  What the arrival publishes lives in tensor memory or registers and
+// is ordered by tcgen05.wait / tcgen05.fence, so the default (CTA-scope release) form is used: a cluster-scope
+// release would make the warp wait for its outstanding global stores to be acknowledged first.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA tile load whose completion bytes are counted by a barrier that may live in the peer CTA
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y) {
@@ -147,7 +155,7 @@ struct PairWalker {
 };
 
 template <typename OutT, bool HAS_LR, bool DBG>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kPairThreads, 1)
 pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                                const __grid_constant__ CUtensorMap tmT, const __grid_constant__ CUtensorMap tmLbT,
                                const GemmParams p) {
@@ -160,9 +168,10 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   uint64_t* t_full = tempty_bar + 2;
   uint64_t* lb_full = t_full + 2;
   uint64_t* ylr_ready = lb_full + 2;
-  uint64_t* lr_done = ylr_ready + 2;
+  uint64_t* lr_done = ylr_ready + 2 * kLrChunks;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
+  volatile long long* stamp = reinterpret_cast<volatile long long*>(smem + L::kMiscOff + 16);   // [0..3] arrive, [4..7] issue
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -174,6 +183,8 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   const int num_kb = (p.K + BK - 1) / BK;
   constexpr uint32_t kTmemCols = 2 * PBN;
   const int pair = static_cast<int>(blockIdx.x) >> 1;
+  // cycle-counter experiments: wall-clock trace of the first pair, 24 slots per tile
+  long long* trace = (p.timing != nullptr && pair == 0) ? p.timing + 8192 : nullptr;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmW);
@@ -181,7 +192,10 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     for (int s = 0; s < PSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 2 * kNumEpiWarps);
-      mbar_init(&t_full[b], 1); mbar_init(&ylr_ready[b], 2 * kNumEpiWarps); mbar_init(&lr_done[b], 1);
+      mbar_init(&t_full[b], 1);
+      for (int c = 0; c < kLrChunks; ++c) {
+        mbar_init(&ylr_ready[b * kLrChunks + c], 2 * kNumEpiWarps); mbar_init(&lr_done[b * kLrChunks + c], 1);
+      }
     }
     mbar_init(&lb_full[0], 1); mbar_init(&lb_full[1], 1);
     *abort_flag = aligned_ok ? 0 : 1;
@@ -216,13 +230,17 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         if (HAS_LR && w.ntile != lb_col) {
           // consecutive column tiles alternate between two lbT buffers; the buffer about to be overwritten was last
           // read by low-rank MMAs of a tile at least two back in this CTA's sequence
-          if (it >= 2 && !wait_or_abort(&lr_done[buf], static_cast<uint32_t>(((it - 2) >> 1) & 1), abort_flag)) {
+          if (it >= 2 && !wait_or_abort(&lr_done[buf * kLrChunks + kLrChunks - 1], static_cast<uint32_t>(((it - 2) >> 1) & 1), abort_flag)) {
             report_timeout(p.status, 1, 5); *abort_flag = 1; ok = false; break;
           }
           lb_col = w.ntile;
           const int lbuf = static_cast<int>(lb_count & 1u);
           if (rank == 0) mbar_arrive_expect_tx(&lb_full[lbuf], 2 * L::kLbBytes);
-          tma_load_2d_pair(smem + L::kLbOff + lbuf * L::kLbBytes, &tmLbT, leader_addr(&lb_full[lbuf]), 0, nhalf0);
+          // chunk c of the low-rank MMAs covers columns [n0 + c * kLrChunkN, + kLrChunkN): this CTA supplies its half
+#pragma unroll
+          for (int c = 0; c < kLrChunks; ++c)
+            tma_load_2d_pair(smem + L::kLbOff + lbuf * L::kLbBytes + c * kLbChunkRows * kRowBytesLr, &tmLbT,
+                             leader_addr(&lb_full[lbuf]), 0, n0 + c * kLrChunkN + static_cast<int>(rank) * kLbChunkRows);
           ++lb_count;
         }
 #pragma unroll 1
@@ -241,7 +259,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         if (!ok) break;
         if (HAS_LR) {
           // this CTA's rows of t: the slot is free once the low-rank MMAs of two tiles ago have completed
-          if (it >= 2 && !wait_or_abort(&lr_done[buf], static_cast<uint32_t>(((it - 2) >> 1) & 1), abort_flag)) {
+          if (it >= 2 && !wait_or_abort(&lr_done[buf * kLrChunks + kLrChunks - 1], static_cast<uint32_t>(((it - 2) >> 1) & 1), abort_flag)) {
             report_timeout(p.status, 1, 6); *abort_flag = 1; ok = false; break;
           }
           if (rank == 0) mbar_arrive_expect_tx(&t_full[buf], 2 * L::kTBytes);
@@ -261,31 +279,15 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     }
   } else if (run && warp == 1 && rank == 0) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    // The loop is kept minimal on purpose: one barrier probe, four MMAs and two commits per k-block.  A probe of a
+    // shared-memory barrier takes a few hundred cycles while the tensor cores and the TMA unit saturate shared
+    // memory, so every extra probe per k-block (a run-ahead limit, a look at the low-rank barriers) made this thread
+    // the bottleneck; the low-rank MMAs therefore have an issuing thread of their own (warp kLrWarp).
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc_i8(2 * BM, PBN);
-      constexpr uint32_t idesc_lr = idesc_f16(2 * BM, PBN, std::is_same<OutT, __nv_bfloat16>::value);
       int stage = 0; uint32_t phase = 0; int it = 0; bool ok = true;
-      int pending = -1, pending_col = -1, lb_col = -1; uint32_t lb_count = 0;
       long long tm_tempty = 0, tm_full = 0;
       auto commit_both = [&](uint64_t* bar) { tc_commit_pair(smem_u32(bar)); tc_commit_pair(peer_addr(bar)); };
-      auto issue_lowrank = [&](int pt, int pcol) -> bool {
-        const int pb = pt & 1;
-        const uint32_t par = static_cast<uint32_t>(pt >> 1) & 1u;
-        if (!wait_or_abort(&ylr_ready[pb], par, abort_flag)) { report_timeout(p.status, 2, 3); return false; }
-        if (!wait_or_abort(&t_full[pb], par, abort_flag)) { report_timeout(p.status, 2, 4); return false; }
-        if (pcol != lb_col) {          // first tile of a column: its lbT buffer is (column ordinal) & 1
-          if (!wait_or_abort(&lb_full[lb_count & 1u], (lb_count >> 1) & 1u, abort_flag)) { report_timeout(p.status, 2, 5); return false; }
-          lb_col = pcol; ++lb_count;
-        }
-        tc_fence_after();
-        const uint64_t a_desc = kmajor_sw64_desc(smem_u32(smem + L::kTOff + pb * L::kTBytes));
-        const uint64_t b_desc = kmajor_sw64_desc(smem_u32(smem + L::kLbOff + static_cast<int>((lb_count - 1u) & 1u) * L::kLbBytes));
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(pb * PBN);
-        tc_mma_f16_pair(d_tmem, a_desc, b_desc, idesc_lr, 1u);
-        tc_mma_f16_pair(d_tmem, a_desc + 2, b_desc + 2, idesc_lr, 1u);
-        commit_both(&lr_done[pb]);
-        return true;
-      };
       PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance(), ++it) {
@@ -300,24 +302,11 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * PBN);
 #pragma unroll 1
         for (int kb = 0; kb < num_kb; ++kb) {
-          {
-            const long long c1 = p.timing ? clock64() : 0;
-            uint64_t t0 = 0; uint32_t polls = 0; bool got = false;
-            while (true) {
-              if (mbar_try_wait(&full_bar[stage], phase)) { got = true; break; }
-              if (HAS_LR && pending >= 0 && mbar_test_wait(&ylr_ready[pending & 1], static_cast<uint32_t>(pending >> 1) & 1u)) {
-                if (!issue_lowrank(pending, pending_col)) break;
-                pending = -1;
-              }
-              if ((++polls & 255u) == 0) {
-                if (*abort_flag != 0) break;
-                const uint64_t now = global_timer_ns();
-                if (t0 == 0) t0 = now; else if (now - t0 > kWaitBudgetNs) break;
-              }
-            }
-            if (!got) { report_timeout(p.status, 2, 1); *abort_flag = 1; ok = false; break; }
-            if (p.timing) tm_full += clock64() - c1;
+          const long long c1 = p.timing ? clock64() : 0;
+          if (!wait_or_abort(&full_bar[stage], phase, abort_flag)) {
+            report_timeout(p.status, 2, 1); *abort_flag = 1; ok = false; break;
           }
+          if (p.timing) tm_full += clock64() - c1;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
           const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
@@ -331,27 +320,58 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         }
         if (!ok) break;
         commit_both(&tfull_bar[buf]);
-        if (HAS_LR) {
-          if (pending >= 0) {
-            if (!issue_lowrank(pending, pending_col)) { *abort_flag = 1; ok = false; break; }
+        if (trace && it < 1000) trace[it * 24 + 18] = static_cast<long long>(global_timer_ns());
+      }
+      if (p.timing) { p.timing[blockIdx.x * 16 + 0] = tm_tempty; p.timing[blockIdx.x * 16 + 1] = tm_full; }
+    }
+  } else if (HAS_LR && run && warp == kLrWarp && rank == 0) {
+    // ------------------------------------------------------------------ low-rank MMA issuer (leader CTA only)
+    // Per tile and column chunk: wait until all sixteen epilogue warps of the pair have written the scaled chunk back
+    // to tensor memory, add t @ lbT on top with two kind::f16 MMAs (K = 16 each), publish "chunk complete" to both CTAs.
+    if (elect_one()) {
+      constexpr uint32_t idesc_lr = idesc_f16(2 * BM, kLrChunkN, std::is_same<OutT, __nv_bfloat16>::value);
+      int it = 0, lb_col = -1; uint32_t lb_count = 0; bool ok = true;
+      long long tm_det[2] = {0, 0};
+      auto commit_both = [&](uint64_t* bar) { tc_commit_pair(smem_u32(bar)); tc_commit_pair(peer_addr(bar)); };
+      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
+#pragma unroll 1
+      for (; w.valid() && ok; w.advance(), ++it) {
+        const int pb = it & 1;
+        const uint32_t par = static_cast<uint32_t>(it >> 1) & 1u;
+#pragma unroll 1
+        for (int chunk = 0; chunk < kLrChunks; ++chunk) {
+          if (!wait_or_abort(&ylr_ready[pb * kLrChunks + chunk], par, abort_flag)) { report_timeout(p.status, 4, 3); ok = false; break; }
+          if (trace && it < 1000 && chunk == 0) trace[it * 24 + 16] = static_cast<long long>(global_timer_ns());
+          if (chunk == 0) {
+            if (!wait_or_abort(&t_full[pb], par, abort_flag)) { report_timeout(p.status, 4, 4); ok = false; break; }
+            if (w.ntile != lb_col) {          // first tile of a column: its lbT buffer is (column ordinal) & 1
+              if (!wait_or_abort(&lb_full[lb_count & 1u], (lb_count >> 1) & 1u, abort_flag)) { report_timeout(p.status, 4, 5); ok = false; break; }
+              lb_col = w.ntile; ++lb_count;
+            }
           }
-          pending = it; pending_col = w.ntile;
+          tc_fence_after();
+          if (trace && it < 1000 && chunk == 0) trace[it * 24 + 17] = static_cast<long long>(global_timer_ns());
+          const uint64_t a_desc = kmajor_sw64_desc(smem_u32(smem + L::kTOff + pb * L::kTBytes));
+          const uint64_t b_desc = kmajor_sw64_desc(smem_u32(smem + L::kLbOff + static_cast<int>((lb_count - 1u) & 1u) * L::kLbBytes +
+                                                            chunk * kLbChunkRows * kRowBytesLr));
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(pb * PBN + chunk * kLrChunkN);
+          tc_mma_f16_pair(d_tmem, a_desc, b_desc, idesc_lr, 1u);
+          tc_mma_f16_pair(d_tmem, a_desc + 2, b_desc + 2, idesc_lr, 1u);
+          commit_both(&lr_done[pb * kLrChunks + chunk]);
+          if (p.timing) { const long long now = clock64(); tm_det[chunk] += now - stamp[pb * kLrChunks + chunk]; stamp[4 + pb * kLrChunks + chunk] = now; }
         }
       }
-      if (HAS_LR && ok && pending >= 0) {
-        if (!issue_lowrank(pending, pending_col)) *abort_flag = 1;
-      }
-      if (p.timing) { p.timing[blockIdx.x * 8 + 0] = tm_tempty; p.timing[blockIdx.x * 8 + 1] = tm_full; }
+      if (!ok) *abort_flag = 1;
+      if (p.timing) { p.timing[blockIdx.x * 16 + 8] = tm_det[0]; p.timing[blockIdx.x * 16 + 9] = tm_det[1]; }
     }
-  } else if (run && warp >= 2) {
+  } else if (run && warp >= 2 && warp < 2 + kNumEpiWarps) {
     // ------------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
     const int etid = threadIdx.x - 64;
     const int g = lane >> 2, q = lane & 3;
-    constexpr int HALF_N = PBN / 2;
     constexpr int UNIT_N = 64;
-    constexpr int kChunks = HALF_N / UNIT_N;
+    static_assert(kLrChunkN == 2 * UNIT_N, "two column halves of 64 per chunk");
     OutT* out = static_cast<OutT*>(p.out);
     float* scol_s = reinterpret_cast<float*>(smem + L::kScolOff);
     float* bias_s = reinterpret_cast<float*>(smem + L::kBiasOff);
@@ -359,7 +379,16 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     bool aborted = false;
     int it = 0;
     int aux_n0 = -1;
-    long long te_tfull = 0, te_p1 = 0, te_lr = 0, te_p2 = 0, te_aux = 0;
+    long long te_tfull = 0, te_p1 = 0, te_lr = 0, te_p2 = 0, te_aux = 0, te_exec[2] = {0, 0};
+    float srow_next[2][2];
+    auto load_srow = [&](int r0, float (&dst)[2][2]) {
+#pragma unroll
+      for (int mb = 0; mb < 2; ++mb) {
+        const int rA = r0 + quarter * 32 + mb * 16 + g;
+        dst[mb][0] = rA < p.M ? p.s_row[rA] : 0.0f;
+        dst[mb][1] = rA + 8 < p.M ? p.s_row[rA + 8] : 0.0f;
+      }
+    };
     PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
 #pragma unroll 1
     for (; w.valid(); w.advance(), ++it) {
@@ -381,13 +410,11 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         }
         epi_bar_sync();
       }
+      // row scales of this tile: fetched while the previous tile was being stored (first tile: here)
       float srow[2][2];
+      if (it == 0) load_srow(row0, srow_next);
 #pragma unroll
-      for (int mb = 0; mb < 2; ++mb) {
-        const int rA = row0 + quarter * 32 + mb * 16 + g;
-        srow[mb][0] = rA < row_end ? p.s_row[rA] : 0.0f;
-        srow[mb][1] = rA + 8 < row_end ? p.s_row[rA + 8] : 0.0f;
-      }
+      for (int mb = 0; mb < 2; ++mb) { srow[mb][0] = srow_next[mb][0]; srow[mb][1] = srow_next[mb][1]; }
 
       const long long e1 = p.timing ? clock64() : 0;
       if (!aborted) {
@@ -396,19 +423,26 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       }
       if (aborted) continue;
       tc_fence_after();
+      if (trace && it < 1000 && warp == 2 && lane == 0) trace[it * 24 + 20 + rank] = static_cast<long long>(global_timer_ns());
       const long long e2 = p.timing ? clock64() : 0;
       long long e3 = e2, e4 = e2;
+      {
+        PairWalker wn = w; wn.advance();
+        if (wn.valid()) load_srow(wn.mt * 2 * BM + static_cast<int>(rank) * BM, srow_next);
+      }
 
-      const uint32_t t_acc = tmem_base + static_cast<uint32_t>(buf * PBN + half * HALF_N);
+      // Column assignment: chunk ch of the tile is columns [ch * 128, +128); the warps of half 0 take its first 64
+      // columns, those of half 1 the other 64, so that one low-rank MMA pair per chunk serves all sixteen warps.
+      const uint32_t t_acc = tmem_base + static_cast<uint32_t>(buf * PBN + half * UNIT_N);
       auto unit_addr = [&](int ch, int mb) {
-        return t_acc + (static_cast<uint32_t>(quarter * 32 + mb * 16) << 16) + static_cast<uint32_t>(ch * UNIT_N);
+        return t_acc + (static_cast<uint32_t>(quarter * 32 + mb * 16) << 16) + static_cast<uint32_t>(ch * kLrChunkN);
       };
       uint32_t va[32], vb[32];
 
       // scale one 16 x 64 block: int32 -> fp32 * (s_row * s_col), in place in the registers
       auto scale_unit = [&](uint32_t (&v)[32], int ch, int mb) {
-        const int col_unit = half * HALF_N + ch * UNIT_N;
-        const float srA = srow[mb][0], srB = srow[mb][1];
+        const int col_unit = ch * kLrChunkN + half * UNIT_N;
+        const float2 srA = make_float2(srow[mb][0], srow[mb][0]), srB = make_float2(srow[mb][1], srow[mb][1]);
 #pragma unroll
         for (int nb = 0; nb < 8; ++nb) {
           const int cl = col_unit + nb * 8 + 2 * q;
@@ -417,15 +451,17 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
             const int rA = row0 + quarter * 32 + mb * 16 + g;
             dump_acc_pair(p.dbg_acc, p.N, rA, rA + 8, n0 + cl, row_end, v[4 * nb + 0], v[4 * nb + 1], v[4 * nb + 2], v[4 * nb + 3]);
           }
-          v[4 * nb + 0] = __float_as_uint(__fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 0])), __fmul_rn(srA, sc.x)));
-          v[4 * nb + 1] = __float_as_uint(__fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 1])), __fmul_rn(srA, sc.y)));
-          v[4 * nb + 2] = __float_as_uint(__fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 2])), __fmul_rn(srB, sc.x)));
-          v[4 * nb + 3] = __float_as_uint(__fmul_rn(int_to_float_rn(static_cast<int32_t>(v[4 * nb + 3])), __fmul_rn(srB, sc.y)));
+          const float2 yA = __fmul2_rn(int2_to_float2_rn(static_cast<int32_t>(v[4 * nb + 0]), static_cast<int32_t>(v[4 * nb + 1])),
+                                       __fmul2_rn(srA, sc));
+          const float2 yB = __fmul2_rn(int2_to_float2_rn(static_cast<int32_t>(v[4 * nb + 2]), static_cast<int32_t>(v[4 * nb + 3])),
+                                       __fmul2_rn(srB, sc));
+          v[4 * nb + 0] = __float_as_uint(yA.x); v[4 * nb + 1] = __float_as_uint(yA.y);
+          v[4 * nb + 2] = __float_as_uint(yB.x); v[4 * nb + 3] = __float_as_uint(yB.y);
         }
       };
       // + bias, round, transpose inside quads, store one 16 x 64 block of fp32 values
       auto store_unit = [&](const uint32_t (&v)[32], int ch, int mb) {
-        const int col_unit = half * HALF_N + ch * UNIT_N;
+        const int col_unit = ch * kLrChunkN + half * UNIT_N;
         const int rA = row0 + quarter * 32 + mb * 16 + g;
         const int rB = rA + 8;
 #pragma unroll
@@ -435,8 +471,10 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           for (int j = 0; j < 4; ++j) {
             const int nb = grp * 4 + j;
             const float2 bi = *reinterpret_cast<const float2*>(bias_s + col_unit + nb * 8 + 2 * q);
-            wA[j] = pack2(__fadd_rn(__uint_as_float(v[4 * nb + 0]), bi.x), __fadd_rn(__uint_as_float(v[4 * nb + 1]), bi.y), OutT{});
-            wB[j] = pack2(__fadd_rn(__uint_as_float(v[4 * nb + 2]), bi.x), __fadd_rn(__uint_as_float(v[4 * nb + 3]), bi.y), OutT{});
+            const float2 yA = __fadd2_rn(make_float2(__uint_as_float(v[4 * nb + 0]), __uint_as_float(v[4 * nb + 1])), bi);
+            const float2 yB = __fadd2_rn(make_float2(__uint_as_float(v[4 * nb + 2]), __uint_as_float(v[4 * nb + 3])), bi);
+            wA[j] = pack2(yA.x, yA.y, OutT{});
+            wB[j] = pack2(yB.x, yB.y, OutT{});
           }
           const int col_grp = n0 + col_unit + grp * 32;
           if (vec_store && col_grp + 32 <= p.N) {
@@ -453,51 +491,69 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         }
       };
 
+      long long lr_wait = 0;
       if constexpr (HAS_LR) {
-        // pass 1: scaled accumulator back to tensor memory, then the MMA thread adds t @ lb on top
+        // pass 1, chunk by chunk: scaled accumulator back to tensor memory; the MMA thread adds t @ lb on top of a
+        // chunk as soon as all sixteen warps have written it, while the warps scale the next chunk
         tmem_ld_16x256b_x8(unit_addr(0, 0), va);
 #pragma unroll 1
-        for (int ch = 0; ch < kChunks; ++ch) {
-          tc_wait_ld(); wait_st();
+        for (int ch = 0; ch < kLrChunks; ++ch) {
+          tc_wait_ld();
           tmem_ld_16x256b_x8(unit_addr(ch, 1), vb);
           scale_unit(va, ch, 0);
           tmem_st_x8(unit_addr(ch, 0), va);
-          tc_wait_ld(); wait_st();
-          if (ch + 1 < kChunks) tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+          tc_wait_ld();
           scale_unit(vb, ch, 1);
           tmem_st_x8(unit_addr(ch, 1), vb);
+          wait_st();
+          if (ch + 1 < kLrChunks) tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+          tc_fence_before();
+          __syncwarp();
+          if (p.timing && warp == 2 && lane == 0) stamp[buf * kLrChunks + ch] = clock64();
+          if (trace && it < 1000 && ch == 0 && lane == 0) trace[it * 24 + rank * 8 + (warp - 2)] = static_cast<long long>(global_timer_ns());
+          if (lane == 0) mbar_arrive_cluster(leader_addr(&ylr_ready[buf * kLrChunks + ch]));
         }
-        wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(leader_addr(&ylr_ready[buf]));
         if (p.timing) e3 = clock64();
-        const bool landed = wait_or_abort(&lr_done[buf], par, abort_flag);
-        if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 6); *abort_flag = 1; aborted = true; continue; }
-        tc_fence_after();
-        if (p.timing) e4 = clock64();
       }
       // final pass: (scale when there is no low-rank term,) + bias, round, store
+      auto chunk_ready = [&](int ch) -> bool {     // low-rank term of chunk ch has landed in tensor memory
+        if constexpr (HAS_LR) {
+          const long long c0 = p.timing ? clock64() : 0;
+          const bool landed = wait_or_abort(&lr_done[buf * kLrChunks + ch], par, abort_flag);
+          if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 6); *abort_flag = 1; return false; }
+          tc_fence_after();
+          if (trace && it < 1000 && ch == 0 && warp == 2 && lane == 0) trace[it * 24 + (rank ? 22 : 19)] = static_cast<long long>(global_timer_ns());
+          if (p.timing) { const long long now = clock64(); lr_wait += now - c0; te_exec[ch] += now - stamp[4 + buf * kLrChunks + ch]; }
+        }
+        return true;
+      };
+      if (!chunk_ready(0)) { aborted = true; continue; }
       tmem_ld_16x256b_x8(unit_addr(0, 0), va);
 #pragma unroll 1
-      for (int ch = 0; ch < kChunks; ++ch) {
+      for (int ch = 0; ch < kLrChunks; ++ch) {
         tc_wait_ld();
         tmem_ld_16x256b_x8(unit_addr(ch, 1), vb);
         if constexpr (!HAS_LR) scale_unit(va, ch, 0);
         store_unit(va, ch, 0);
         tc_wait_ld();
-        if (ch + 1 < kChunks) tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+        if (ch + 1 < kLrChunks) {
+          if (!chunk_ready(ch + 1)) { aborted = true; break; }
+          tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+        }
         if constexpr (!HAS_LR) scale_unit(vb, ch, 1);
         store_unit(vb, ch, 1);
       }
+      if (aborted) continue;
+      e4 = e3 + lr_wait;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_addr(&tempty_bar[buf]));
       if (p.timing) { te_aux += e1 - e0; te_tfull += e2 - e1; te_p1 += e3 - e2; te_lr += e4 - e3; te_p2 += clock64() - e4; }
     }
     if (p.timing && warp == 2 && lane == 0) {
-      p.timing[blockIdx.x * 8 + 2] = te_aux; p.timing[blockIdx.x * 8 + 3] = te_tfull; p.timing[blockIdx.x * 8 + 4] = te_p1;
-      p.timing[blockIdx.x * 8 + 5] = te_lr; p.timing[blockIdx.x * 8 + 6] = te_p2; p.timing[blockIdx.x * 8 + 7] = it;
+      p.timing[blockIdx.x * 16 + 2] = te_aux; p.timing[blockIdx.x * 16 + 3] = te_tfull; p.timing[blockIdx.x * 16 + 4] = te_p1;
+      p.timing[blockIdx.x * 16 + 5] = te_lr; p.timing[blockIdx.x * 16 + 6] = te_p2; p.timing[blockIdx.x * 16 + 7] = it;
+      p.timing[blockIdx.x * 16 + 10] = te_exec[0]; p.timing[blockIdx.x * 16 + 11] = te_exec[1];
     }
   }
 
@@ -525,7 +581,7 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMa
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.blockDim = dim3(kPairThreads, 1, 1);
   cfg.dynamicSmemBytes = PairSmem::kTotal;
   cfg.stream = st;
   cfg.attrs = attr; cfg.numAttrs = 1;
@@ -563,8 +619,9 @@ int make_lr_map64(CUtensorMap* map, const void* base, int64_t rows, int64_t ld, 
 }  // namespace
 
 int launch_gemm_pair(bool bf16, bool dbg, const void* xq, int64_t ldx, const void* w, int64_t ldw, const void* t,
-                     int64_t ldt, const void* lb_t, int64_t M, int64_t N, int64_t K, const GemmParams& p,
+                     int64_t ldt, const void* lb_t, int64_t M, int64_t N, int64_t K, const GemmParams& p_in,
                      cudaStream_t st) {
+  const GemmParams& p = p_in;
   CUtensorMap tmA, tmW, tmT, tmLbT;
   int rc = make_tile_map(&tmA, xq, M, K, ldx, BM);
   if (rc != PQ_OK) return rc;
@@ -574,7 +631,7 @@ int launch_gemm_pair(bool bf16, bool dbg, const void* xq, int64_t ldx, const voi
   if (has_lr) {
     rc = make_lr_map64(&tmT, t, M, ldt, BM, bf16);
     if (rc != PQ_OK) return rc;
-    rc = make_lr_map64(&tmLbT, lb_t, N, kLR, kHalfB, bf16);
+    rc = make_lr_map64(&tmLbT, lb_t, N, kLR, kLbChunkRows, bf16);
     if (rc != PQ_OK) return rc;
   } else {
     tmT = tmA; tmLbT = tmA;
