@@ -313,7 +313,7 @@ def main_ours(args):
     # DRAM traffic of the GEMM launches of one step: bytes per row from the committed ncu summary (captured at
     # 8192 rows), scaled by the rows of a full launch
     traffic = None
-    tp = ROOT / "profiles" / "gemm_fused_flux4k_rows8192_full.md"
+    tp = ROOT / "profiles" / "gemm_fused_pair_flux4k_rows8192_full.md"
     if tp.exists():
         per_row = {}
         for ln in tp.read_text().splitlines():
@@ -331,7 +331,7 @@ def main_ours(args):
                    "parallelism": f"row-sharded x{world}, weights replicated", "allgather": bool(args.allgather and world > 1),
                    "l2": "inputs (2.4 GB) and outputs (3.2 GB) exceed L2; no flush needed"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOPS", "frac": achieved / peak,
-                     "traffic": traffic, "kernel": "pq_int8_gemm_fused_kernel (both launches of a step)",
+                     "traffic": traffic, "kernel": "pq_int8_gemm_fused_pair_kernel (both launches of a step)",
                      "peak_basis": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json (INT8 issues at twice the bf16 rate)",
                      "frac_of_datasheet_4500": achieved / DATASHEET_INT8_TOPS,
                      "ops_per_launch": [2.0 * rows * K * N for _n, K, N in LAYERS]},

@@ -533,12 +533,15 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
                  ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + 256) : nullptr;
   p.sched_pm = p.sched_pn = p.sched_m_steps = p.sched_n_rounds = 1;
 
-  // CTA-pair kernel: one weight set, 256-column tiles, enough 256-row tiles to occupy the SM pairs, and the
-  // K-major low-rank factor when there is a low-rank term
-  if (options().gemm_pair != 0 && m_split == M && bn == 256 && (!has_lr || lb_t != nullptr) &&
-      ((M + 255) / 256) * ((N + 255) / 256) >= (options().gemm_pair == 2 ? 1 : sm_count() / 2)) {
-    return launch_gemm_pair(out_dtype == PQ_DTYPE_BF16, dbg_acc != nullptr, xq, ldx, w0, ldw, has_lr ? t : nullptr, ldt,
-                            has_lr ? lb_t : nullptr, M, N, K, p, static_cast<cudaStream_t>(stream));
+  // CTA-pair kernel: 256-column tiles, enough 256-row tiles to occupy the SM pairs, and the K-major low-rank
+  // factor when there is a low-rank term
+  {
+    const int64_t pair_rows = (m_split + 255) / 256 + (M - m_split + 255) / 256;
+    if (options().gemm_pair != 0 && bn == 256 && (!has_lr || lb_t != nullptr) &&
+        pair_rows * ((N + 255) / 256) >= (options().gemm_pair == 2 ? 1 : sm_count() / 2)) {
+      return launch_gemm_pair(out_dtype == PQ_DTYPE_BF16, dbg_acc != nullptr, xq, ldx, w0, w1, ldw, has_lr ? t : nullptr, ldt,
+                              has_lr ? lb_t : nullptr, M, N, K, p, static_cast<cudaStream_t>(stream));
+    }
   }
 
   CUtensorMap tmA, tmW0, tmW1;

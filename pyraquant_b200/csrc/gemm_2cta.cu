@@ -154,10 +154,21 @@ struct PairWalker {
   __device__ __forceinline__ void advance() { mt += pm; if (mt >= mt_total) { mt = bm; ntile += pn; } }
 };
 
+// Rows of a pair tile.  Row tiles [0, mt0) cover rows [0, m_split) with weight set 0, the rest cover [m_split, M) with
+// weight set 1; a tile never straddles the split (its tail rows are masked at row_end).
+struct PairCoord { int row0, row_end, set; };
+__device__ __forceinline__ PairCoord pair_coord(int mt, int mt0, const GemmParams& p, uint32_t rank) {
+  PairCoord c;
+  if (mt < mt0) { c.set = 0; c.row0 = mt * 2 * BM; c.row_end = p.m_split; }
+  else { c.set = 1; c.row0 = p.m_split + (mt - mt0) * 2 * BM; c.row_end = p.M; }
+  c.row0 += static_cast<int>(rank) * BM;
+  return c;
+}
+
 template <typename OutT, bool HAS_LR, bool DBG>
 __global__ void __launch_bounds__(kPairThreads, 1)
 pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
-                               const __grid_constant__ CUtensorMap tmT, const __grid_constant__ CUtensorMap tmLbT,
+                               const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmT, const __grid_constant__ CUtensorMap tmLbT,
                                const GemmParams p) {
   using L = PairSmem;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -178,7 +189,8 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   const uint32_t rank = cluster_cta_rank();          // 0 = leader (issues the MMAs), 1 = peer
   const bool aligned_ok = (smem_u32(smem) & 1023u) == 0;
 
-  const int mt_total = (p.M + 2 * BM - 1) / (2 * BM);   // pair tiles of 256 rows
+  const int mt0 = (p.m_split + 2 * BM - 1) / (2 * BM);   // pair tiles of 256 rows: first tier, then second tier
+  const int mt_total = mt0 + (p.M - p.m_split + 2 * BM - 1) / (2 * BM);
   const int nt = (p.N + PBN - 1) / PBN;
   const int num_kb = (p.K + BK - 1) / BK;
   constexpr uint32_t kTmemCols = 2 * PBN;
@@ -187,7 +199,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   long long* trace = (p.timing != nullptr && pair == 0) ? p.timing + 8192 : nullptr;
 
   if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmW1);
     if (HAS_LR) { tma_prefetch_desc(&tmT); tma_prefetch_desc(&tmLbT); }
     for (int s = 0; s < PSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) {
@@ -223,7 +235,8 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance(), ++it) {
-        const int row0 = w.mt * 2 * BM + static_cast<int>(rank) * BM;       // this CTA's 128 rows
+        const PairCoord c = pair_coord(w.mt, mt0, p, rank);
+        const int row0 = c.row0;                                            // this CTA's 128 rows
         const int n0 = w.ntile * PBN;
         const int nhalf0 = n0 + static_cast<int>(rank) * kHalfB;            // this CTA's half of the weight tile
         const int buf = it & 1;
@@ -252,7 +265,8 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           const uint32_t fb = leader_addr(&full_bar[stage]);
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
           tma_load_2d_pair(a_s, &tmA, fb, kb * BK, row0);
-          tma_load_2d_pair(a_s + L::kABytes, &tmW, fb, kb * BK, nhalf0);
+          if (c.set == 0) tma_load_2d_pair(a_s + L::kABytes, &tmW, fb, kb * BK, nhalf0);
+          else tma_load_2d_pair(a_s + L::kABytes, &tmW1, fb, kb * BK, nhalf0);
           ++issued;
           if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
         }
@@ -378,41 +392,44 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     const bool vec_store = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     bool aborted = false;
     int it = 0;
-    int aux_n0 = -1;
+    int aux_n0 = -1, aux_set = -1;
     long long te_tfull = 0, te_p1 = 0, te_lr = 0, te_p2 = 0, te_aux = 0, te_exec[2] = {0, 0};
     float srow_next[2][2];
-    auto load_srow = [&](int r0, float (&dst)[2][2]) {
+    auto load_srow = [&](const PairCoord& pc, float (&dst)[2][2]) {
 #pragma unroll
       for (int mb = 0; mb < 2; ++mb) {
-        const int rA = r0 + quarter * 32 + mb * 16 + g;
-        dst[mb][0] = rA < p.M ? p.s_row[rA] : 0.0f;
-        dst[mb][1] = rA + 8 < p.M ? p.s_row[rA + 8] : 0.0f;
+        const int rA = pc.row0 + quarter * 32 + mb * 16 + g;
+        dst[mb][0] = rA < pc.row_end ? p.s_row[rA] : 0.0f;
+        dst[mb][1] = rA + 8 < pc.row_end ? p.s_row[rA + 8] : 0.0f;
       }
     };
     PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
 #pragma unroll 1
     for (; w.valid(); w.advance(), ++it) {
-      const int row0 = w.mt * 2 * BM + static_cast<int>(rank) * BM;
+      const PairCoord c = pair_coord(w.mt, mt0, p, rank);
+      const int row0 = c.row0;
       const int n0 = w.ntile * PBN;
-      const int row_end = p.M;
+      const int row_end = c.row_end;
       const int buf = it & 1;
       const uint32_t par = static_cast<uint32_t>(it >> 1) & 1u;
 
       const long long e0 = p.timing ? clock64() : 0;
-      if (n0 != aux_n0) {
-        aux_n0 = n0;
+      if (n0 != aux_n0 || c.set != aux_set) {
+        aux_n0 = n0; aux_set = c.set;
+        const float* scol_g = p.s_col[0];
+        if (c.set != 0) scol_g = p.s_col[1];
         epi_bar_sync();
 #pragma unroll 1
         for (int i = etid; i < PBN; i += kNumEpiWarps * 32) {
           const int col = n0 + i;
-          scol_s[i] = col < p.N ? p.s_col[0][col] : 0.0f;
+          scol_s[i] = col < p.N ? scol_g[col] : 0.0f;
           bias_s[i] = (p.has_bias && col < p.N) ? p.bias[col] : 0.0f;
         }
         epi_bar_sync();
       }
       // row scales of this tile: fetched while the previous tile was being stored (first tile: here)
       float srow[2][2];
-      if (it == 0) load_srow(row0, srow_next);
+      if (it == 0) load_srow(c, srow_next);
 #pragma unroll
       for (int mb = 0; mb < 2; ++mb) { srow[mb][0] = srow_next[mb][0]; srow[mb][1] = srow_next[mb][1]; }
 
@@ -428,7 +445,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       long long e3 = e2, e4 = e2;
       {
         PairWalker wn = w; wn.advance();
-        if (wn.valid()) load_srow(wn.mt * 2 * BM + static_cast<int>(rank) * BM, srow_next);
+        if (wn.valid()) load_srow(pair_coord(wn.mt, mt0, p, rank), srow_next);
       }
 
       // Column assignment: chunk ch of the tile is columns [ch * 128, +128); the warps of half 0 take its first 64
@@ -570,8 +587,8 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
 }
 
 template <typename OutT, bool HAS_LR, bool DBG>
-int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmT, const CUtensorMap& tmLbT,
-                GemmParams p, int mt_pairs, int ntl, cudaStream_t st) {
+int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmW1, const CUtensorMap& tmT,
+                const CUtensorMap& tmLbT, GemmParams p, int mt_pairs, int ntl, cudaStream_t st) {
   auto kern = pq_int8_gemm_fused_pair_kernel<OutT, HAS_LR, DBG>;
   static int max_pairs[64] = {0};
   int dev = 0;
@@ -598,7 +615,7 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMa
   if (pairs_cap < 1) pairs_cap = 1;
   choose_cta_grid(mt_pairs, ntl, pairs_cap, &p.sched_pm, &p.sched_pn);
   cfg.gridDim = dim3(2 * p.sched_pm * p.sched_pn, 1, 1);
-  PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmT, tmLbT, p));
+  PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmW1, tmT, tmLbT, p));
   return PQ_OK;
 }
 
@@ -618,15 +635,20 @@ int make_lr_map64(CUtensorMap* map, const void* base, int64_t rows, int64_t ld, 
 
 }  // namespace
 
-int launch_gemm_pair(bool bf16, bool dbg, const void* xq, int64_t ldx, const void* w, int64_t ldw, const void* t,
-                     int64_t ldt, const void* lb_t, int64_t M, int64_t N, int64_t K, const GemmParams& p_in,
+int launch_gemm_pair(bool bf16, bool dbg, const void* xq, int64_t ldx, const void* w, const void* w1, int64_t ldw,
+                     const void* t, int64_t ldt, const void* lb_t, int64_t M, int64_t N, int64_t K, const GemmParams& p,
                      cudaStream_t st) {
-  const GemmParams& p = p_in;
-  CUtensorMap tmA, tmW, tmT, tmLbT;
+  CUtensorMap tmA, tmW, tmW1, tmT, tmLbT;
   int rc = make_tile_map(&tmA, xq, M, K, ldx, BM);
   if (rc != PQ_OK) return rc;
   rc = make_tile_map(&tmW, w, N, K, ldw, kHalfB);
   if (rc != PQ_OK) return rc;
+  if (p.m_split < p.M) {
+    rc = make_tile_map(&tmW1, w1, N, K, ldw, kHalfB);
+    if (rc != PQ_OK) return rc;
+  } else {
+    tmW1 = tmW;
+  }
   const bool has_lr = t != nullptr;
   if (has_lr) {
     rc = make_lr_map64(&tmT, t, M, ldt, BM, bf16);
@@ -636,18 +658,18 @@ int launch_gemm_pair(bool bf16, bool dbg, const void* xq, int64_t ldx, const voi
   } else {
     tmT = tmA; tmLbT = tmA;
   }
-  const int mt_pairs = static_cast<int>((M + 2 * BM - 1) / (2 * BM));
+  const int mt_pairs = (p.m_split + 2 * BM - 1) / (2 * BM) + (p.M - p.m_split + 2 * BM - 1) / (2 * BM);
   const int ntl = static_cast<int>((N + PBN - 1) / PBN);
   if (bf16) {
-    if (has_lr) return dbg ? launch_pair<__nv_bfloat16, true, true>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st)
-                           : launch_pair<__nv_bfloat16, true, false>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st);
-    return dbg ? launch_pair<__nv_bfloat16, false, true>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st)
-               : launch_pair<__nv_bfloat16, false, false>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st);
+    if (has_lr) return dbg ? launch_pair<__nv_bfloat16, true, true>(tmA, tmW, tmW1, tmT, tmLbT, p, mt_pairs, ntl, st)
+                           : launch_pair<__nv_bfloat16, true, false>(tmA, tmW, tmW1, tmT, tmLbT, p, mt_pairs, ntl, st);
+    return dbg ? launch_pair<__nv_bfloat16, false, true>(tmA, tmW, tmW1, tmT, tmLbT, p, mt_pairs, ntl, st)
+               : launch_pair<__nv_bfloat16, false, false>(tmA, tmW, tmW1, tmT, tmLbT, p, mt_pairs, ntl, st);
   }
-  if (has_lr) return dbg ? launch_pair<__half, true, true>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st)
-                         : launch_pair<__half, true, false>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st);
-  return dbg ? launch_pair<__half, false, true>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st)
-             : launch_pair<__half, false, false>(tmA, tmW, tmT, tmLbT, p, mt_pairs, ntl, st);
+  if (has_lr) return dbg ? launch_pair<__half, true, true>(tmA, tmW, tmW1, tmT, tmLbT, p, mt_pairs, ntl, st)
+                         : launch_pair<__half, true, false>(tmA, tmW, tmW1, tmT, tmLbT, p, mt_pairs, ntl, st);
+  return dbg ? launch_pair<__half, false, true>(tmA, tmW, tmW1, tmT, tmLbT, p, mt_pairs, ntl, st)
+             : launch_pair<__half, false, false>(tmA, tmW, tmW1, tmT, tmLbT, p, mt_pairs, ntl, st);
 }
 
 }  // namespace pq

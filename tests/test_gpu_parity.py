@@ -277,6 +277,15 @@ def test_gemm_grouped_two_tiers(cuda_dev):
         if mh < M:
             ref[mh:] = oracle.exact_dequant_f64(oracle.int_mm(xq[mh:], w4), sr[mh:], s4, b, t[mh:], lb)
         assert max_rel_err(y, ref) <= TOL, mh
+        # the same call on the CTA-pair kernel (K-major low-rank factor given, kernel forced on): tiles of 256 rows
+        # per tier, split rows not aligned to anything
+        _lib.set_option("gemm_pair", 2)
+        try:
+            y2 = int8_exec.int8_gemm_grouped(xq.to(d), sr.to(d), w8.to(d), s8.to(d), w4.to(d), s4.to(d), b.to(d),
+                                             t.to(d), lb.to(d), mh, torch.bfloat16, lb.t().contiguous().to(d)).cpu()
+        finally:
+            _lib.set_option("gemm_pair", 1)
+        assert max_rel_err(y2, ref) <= TOL, mh
 
 
 def test_dequant_epilogue_and_linear_2d(cuda_dev):
