@@ -21,7 +21,7 @@ Added entry points (not in the reference module): ``quant_rows_g32``, ``gather_q
 from __future__ import annotations
 
 import time
-from typing import Callable, Dict, Optional, Tuple
+from typing import Callable, Dict, Optional, Sequence, Tuple
 
 import torch
 import torch.nn as nn
@@ -164,6 +164,77 @@ def nested4_codes(weight_int8: torch.Tensor, w_scale: torch.Tensor) -> Tuple[tor
     return c.contiguous(), (w_scale.float() * (127.0 / 7.0)).contiguous()
 
 
+class SharedInputGroup:
+    """Sibling ``Int8Linear`` layers that are called one after the other on the SAME input tensor (FLUX: to_q / to_k /
+    to_v, add_*_proj, and proj_mlp next to the attention projections of a single-stream block) share one per-token
+    quantisation and one down-projection ``x @ [A_1 | A_2 | ...]`` instead of one each.  The first member called on
+    an input does both and keeps the results; the others recognise the input (same storage, shape, strides and
+    version counter) and reuse them.  Results are bit-identical to the ungrouped layers except for the
+    down-projection, whose cuBLAS kernel may differ with the width (same caveat as between any two GEMM shapes).
+    The cache keeps the last input and its codes alive until the next input arrives or ``clear()`` is called."""
+
+    def __init__(self, layers: Sequence["Int8Linear"]):
+        layers = list(layers)
+        assert len(layers) >= 2 and all(isinstance(m, Int8Linear) for m in layers)
+        K = layers[0].in_features
+        assert all(m.in_features == K for m in layers), "members must have the same in_features"
+        self.layers = layers
+        self._key = None
+        self._val = None
+        self._A_cat = None
+        self._A_slots: Dict[int, int] = {}
+        for m in layers:
+            m.__dict__["_shared_input"] = self
+
+    def clear(self) -> None:
+        self._key = None
+        self._val = None
+
+    def _a_cat(self, dtype: torch.dtype, device: torch.device) -> Optional[torch.Tensor]:
+        c = self._A_cat
+        if c is None or c.dtype != dtype or c.device != device:
+            mats, self._A_slots, off = [], {}, 0
+            for m in self.layers:
+                if m.lr_A is not None and m.lr_A.shape[1] == 32 and m.lr_A.dtype == dtype:
+                    self._A_slots[id(m)] = off
+                    mats.append(m.lr_A.to(device))
+                    off += 32
+            c = torch.cat(mats, dim=1).contiguous() if mats else torch.empty((0, 0), dtype=dtype, device=device)
+            self._A_cat = c
+        return c if c.numel() else None
+
+    def prepare(self, x2: torch.Tensor):
+        """(codes, row scales, T) for x2; T [M, 32 * members with a rank-32 branch] or None."""
+        key = (x2.data_ptr(), tuple(x2.shape), tuple(x2.stride()), x2.dtype, x2._version, x2.device)
+        if key != self._key:
+            a_cat = self._a_cat(x2.dtype, x2.device)
+            T = (x2 @ a_cat) if a_cat is not None else None
+            xq, sx = ops._quant_rows_impl(x2)
+            self._key, self._val = key, (x2, xq, sx, T)          # x2 kept so that its storage cannot be recycled
+        _x, xq, sx, T = self._val
+        return xq, sx, T
+
+    def t_of(self, member: "Int8Linear", T: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        off = self._A_slots.get(id(member))
+        if T is None or off is None:
+            return None
+        return T[:, off:off + 32]                                # row stride 32 * members: the kernel takes strided t
+
+
+def share_input_quantisation(layers: Sequence["Int8Linear"]) -> SharedInputGroup:
+    """Groups converted layers that are always called on the same input; see ``SharedInputGroup``."""
+    return SharedInputGroup(layers)
+
+
+# Sibling layers of the FLUX blocks that read the same tensor (flux/transformer_flux.py:135-145, 727-729, 821-823),
+# as paths relative to a common parent module.
+FLUX_SHARED_INPUT_GROUPS = (
+    ("proj_mlp", "attn.to_q", "attn.to_k", "attn.to_v"),
+    ("to_q", "to_k", "to_v"),
+    ("add_q_proj", "add_k_proj", "add_v_proj"),
+)
+
+
 class Int8Linear(nn.Module):
     """INT8 stand-in for ``nn.Linear``: per-channel INT8 weights held as buffers, per-token dynamic INT8
     activations, optional rank-r low-rank branch executed for real (down-projection as a small GEMM,
@@ -254,10 +325,27 @@ class Int8Linear(nn.Module):
             ops._lib.check(rc, f"Int8Linear(M={M}, N={N}, K={K})")
         return out
 
+    def _shared_forward(self, x2: torch.Tensor):
+        """Forward through the group's shared quantisation / down-projection; None when the input does not qualify."""
+        grp = self.__dict__.get("_shared_input")
+        M, K = x2.shape
+        if (grp is None or M == 0 or not x2.is_cuda or x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16
+                or K % 32 or x2.dtype not in ops._DT or torch.compiler.is_compiling()):
+            return None
+        if self.lr_A is not None and not self._fusable_lowrank(x2):
+            return None
+        xq, sx, T = grp.prepare(x2)
+        t = grp.t_of(self, T) if self.lr_A is not None else None
+        if t is not None:
+            return int8_gemm_lr(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B, x2.dtype, self._lr_Bt())
+        return int8_gemm_fused(xq, sx, self.weight_int8, self.w_scale, self.bias, x2.dtype)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
-        y = self._lean_forward(x2)
+        y = self._shared_forward(x2)
+        if y is None:
+            y = self._lean_forward(x2)
         if y is not None:
             return y.reshape(*shape[:-1], self.out_features)
         if x2.stride(1) != 1:
@@ -368,10 +456,38 @@ def is_bf16_whitelisted(name: str) -> bool:
     return len(parts) >= 2 and parts[-1] == "linear" and parts[-2].startswith("norm")
 
 
+def group_shared_inputs(model: nn.Module, groups: Sequence[Sequence[str]] = FLUX_SHARED_INPUT_GROUPS) -> int:
+    """For every module of ``model`` under which all relative paths of a group name converted ``Int8Linear`` layers,
+    ties those layers into a ``SharedInputGroup`` (a layer joins at most one group: the first that matches, so list
+    the widest group first).  Returns the number of groups made."""
+    made = 0
+    taken = set()
+    for _name, parent in model.named_modules():
+        for paths in groups:
+            members = []
+            for rel in paths:
+                try:
+                    m = parent.get_submodule(rel)
+                except AttributeError:
+                    m = None
+                if not isinstance(m, Int8Linear) or id(m) in taken:
+                    members = []
+                    break
+                members.append(m)
+            if len(members) >= 2 and len({m.in_features for m in members}) == 1:
+                SharedInputGroup(members)
+                taken.update(id(m) for m in members)
+                made += 1
+    return made
+
+
 def convert_linears_to_int8(model: nn.Module, device: Optional[str] = "cuda",
-                            whitelist: Callable[[str], bool] = is_bf16_whitelisted) -> Dict[str, object]:
+                            whitelist: Callable[[str], bool] = is_bf16_whitelisted,
+                            shared_input_groups: Optional[Sequence[Sequence[str]]] = None) -> Dict[str, object]:
     """Swaps every non-whitelisted ``nn.Linear`` for ``Int8Linear`` in place and returns the same
-    statistics dictionary as the reference (:444-445)."""
+    statistics dictionary as the reference (:444-445).  ``shared_input_groups`` (not in the reference; e.g.
+    ``FLUX_SHARED_INPUT_GROUPS``) additionally ties sibling layers that read the same tensor into one quantisation
+    and one down-projection per input; the count is reported as ``n_shared_input_groups``."""
     dev = torch.device(device) if device is not None else None
     stats = {"n_int8_linear": 0, "n_bf16_linear_kept": 0, "params_int8": 0, "params_bf16_linear_kept": 0,
              "bf16_kept_names": []}
@@ -390,6 +506,8 @@ def convert_linears_to_int8(model: nn.Module, device: Optional[str] = "cuda",
         torch.cuda.synchronize()
     stats["int8_weight_gib"] = stats["params_int8"] / 2**30
     stats["bf16_equiv_gib"] = stats["params_int8"] * 2 / 2**30
+    if shared_input_groups is not None:
+        stats["n_shared_input_groups"] = group_shared_inputs(model, shared_input_groups)
     return stats
 
 

@@ -288,6 +288,55 @@ def test_gemm_grouped_two_tiers(cuda_dev):
         assert max_rel_err(y2, ref) <= TOL, mh
 
 
+def test_shared_input_group(cuda_dev, monkeypatch):
+    """Sibling layers on one input: one quantisation and one down-projection for the group, outputs identical to
+    the same layers run alone on the same codes and the same slice of the shared down-projection."""
+    g = torch.Generator().manual_seed(33)
+    K, Ns, M = 512, (256, 512, 1024, 264), 700
+    layers = []
+    for i, N in enumerate(Ns):
+        lin = nn.Linear(K, N, bias=(i != 1)).to(torch.bfloat16)
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(N, K, generator=g) * 0.02)
+        lr = None if i == 2 else ((torch.randn(K, 32, generator=g) * 0.02).to(torch.bfloat16),
+                                  (torch.randn(32, N, generator=g) * 0.02).to(torch.bfloat16))
+        layers.append(int8_exec.Int8Linear(lin, device=cuda_dev, lowrank=lr))
+    x = (torch.randn(2, M // 2, K, generator=g)).to(torch.bfloat16).to(cuda_dev)
+    alone = [m(x) for m in layers]
+    grp = int8_exec.share_input_quantisation(layers)
+    calls = {"n": 0}
+    real = ops._quant_rows_impl
+
+    def counting(x2):
+        calls["n"] += 1
+        return real(x2)
+    monkeypatch.setattr(ops, "_quant_rows_impl", counting)
+    together = [m(x) for m in layers]
+    assert calls["n"] == 1
+    x2 = x.reshape(-1, K)
+    xq, sx = real(x2)
+    T = x2 @ torch.cat([m.lr_A for m in layers if m.lr_A is not None], dim=1)
+    off = 0
+    for m, ya, yt in zip(layers, alone, together):
+        assert yt.shape == ya.shape == (2, M // 2, m.out_features)
+        if m.lr_A is None:
+            assert torch.equal(yt, ya)
+            continue
+        exp = int8_exec.int8_gemm_lr(xq, sx, m.weight_int8, m.w_scale, m.bias, T[:, off:off + 32], m.lr_B, torch.bfloat16)
+        off += 32
+        assert torch.equal(yt.reshape(M, -1), exp)
+        assert max_rel_err(yt.float().cpu(), ya.double().cpu()) <= TOL      # down-projection may round differently
+    # a modified input (same storage) is quantised again; so is a new tensor
+    x.mul_(0.5)
+    _ = layers[0](x)
+    assert calls["n"] == 2
+    _ = layers[1](x)
+    assert calls["n"] == 2
+    _ = layers[1](x.clone())
+    assert calls["n"] == 3
+    grp.clear()
+
+
 def test_dequant_epilogue_and_linear_2d(cuda_dev):
     L = oracle.make_layer(5, 300, 512, 256, lowrank=False)
     wq, ws = oracle.quant_weight(L["w"])

@@ -191,3 +191,45 @@ def test_nested4_codes_match_oracle():
     c, s4 = int8_exec.nested4_codes(q8, s8)
     co, so = oracle.nested4_from_int8(q8, s8)
     assert torch.equal(c, co) and torch.equal(s4, so)
+
+
+def test_group_shared_inputs_on_flux_like_blocks():
+    """Sibling layers that read the same tensor are tied into groups by relative path; a layer joins one group only."""
+    import torch.nn as nn
+    from pyraquant_b200 import int8_exec
+
+    class Attn(nn.Module):
+        def __init__(self, ctx):
+            super().__init__()
+            self.to_q = nn.Linear(64, 64); self.to_k = nn.Linear(64, 64); self.to_v = nn.Linear(64, 64)
+            if ctx:
+                self.add_q_proj = nn.Linear(64, 64); self.add_k_proj = nn.Linear(64, 64); self.add_v_proj = nn.Linear(64, 64)
+
+    class Single(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.proj_mlp = nn.Linear(64, 256); self.attn = Attn(False); self.proj_out = nn.Linear(320, 64)
+
+    class Double(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.attn = Attn(True)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.single = nn.ModuleList([Single(), Single()]); self.dual = nn.ModuleList([Double()])
+
+    net = Net()
+    stats = int8_exec.convert_linears_to_int8(net, device=None, whitelist=lambda n: False,
+                                              shared_input_groups=int8_exec.FLUX_SHARED_INPUT_GROUPS)
+    # 2 single blocks (proj_mlp + q/k/v) + 1 double block (q/k/v and add_q/k/v)
+    assert stats["n_shared_input_groups"] == 4
+    g = net.single[0].proj_mlp.__dict__["_shared_input"]
+    assert [m for m in g.layers] == [net.single[0].proj_mlp, net.single[0].attn.to_q, net.single[0].attn.to_k,
+                                     net.single[0].attn.to_v]
+    assert "_shared_input" not in net.single[0].proj_out.__dict__
+    assert net.dual[0].attn.to_q.__dict__["_shared_input"] is not net.dual[0].attn.add_q_proj.__dict__["_shared_input"]
+    # the reference's statistics keys are untouched when the option is not used
+    stats2 = int8_exec.convert_linears_to_int8(Net(), device=None, whitelist=lambda n: False)
+    assert "n_shared_input_groups" not in stats2
