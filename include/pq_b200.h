@@ -119,6 +119,24 @@ int pq_int8_gemm(const int8_t* xq, int64_t ldx, const float* s_row,
                  int64_t M, int64_t N, int64_t K,
                  void* workspace, size_t ws_bytes, int32_t* dbg_acc, void* stream);
 
+/* pq_int8_gemm with a variant epilogue (no counterpart in the reference, whose callers run these as separate
+ * elementwise kernels after the Linear).  `epilogue` is a combination of
+ *   PQ_EPI_ACCUMULATE  out = round(out + round(y)): the second half of a Linear split along its inputs
+ *                      (SplitInLinear.forward, pyraquant/external_quant.py:191-192) adds onto the first half's output;
+ *   PQ_EPI_GELU_TANH   out = round(gelu_tanh(round(y))): the tanh-form GELU that follows proj_mlp
+ *                      (flux/transformer_flux.py:135), tanh by the hardware approximation;
+ * (activation first when both are set).  y is the pq_int8_gemm result before rounding, round() rounds to out_dtype.
+ * Needs the CTA-pair kernel: lb_t given when t is, N % 32 == 0, ldo % 8 == 0, out 16-byte aligned; otherwise
+ * PQ_ERR_UNSUPPORTED and nothing is launched.  epilogue == 0 is pq_int8_gemm. */
+#define PQ_EPI_ACCUMULATE 1
+#define PQ_EPI_GELU_TANH 2
+int pq_int8_gemm_ex(const int8_t* xq, int64_t ldx, const float* s_row,
+                    const int8_t* w, int64_t ldw, const float* s_col, const float* bias,
+                    const void* t, int64_t ldt, const void* lb, int64_t ldb, const void* lb_t, int R, int lr_dtype,
+                    void* out, int out_dtype, int64_t ldo,
+                    int64_t M, int64_t N, int64_t K, int epilogue,
+                    void* workspace, size_t ws_bytes, void* stream);
+
 /* Routed two-tier GEMM (the per-leaf precision routing of flux/run_flux.py:117-123 collapsed to a
  * hard choice at the Linear): rows [0, M_hi) use weight set 0 (the INT8 codes), rows [M_hi, M)
  * use weight set 1 (the codes re-rounded to the nested 4-bit grid,

@@ -64,6 +64,11 @@ __device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
                : "l"(p));
   return v;
 }
+__device__ __forceinline__ uint4 ld_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_v2(void* p, uint32_t a, uint32_t b) {
   asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
 }

@@ -494,8 +494,9 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
                 const int8_t* w1, const float* sc1, int64_t ldw, const float* bias, const void* t, int64_t ldt,
                 const void* lb, int64_t ldb, const void* lb_t, int R, int lr_dtype, void* out, int out_dtype,
                 int64_t ldo, int64_t m_split, int64_t M, int64_t N, int64_t K, void* workspace, size_t ws_bytes,
-                int32_t* dbg_acc, void* stream) {
+                int32_t* dbg_acc, void* stream, int epi_flags = 0) {
   if (M < 0 || N <= 0 || K <= 0 || m_split < 0 || m_split > M) return PQ_ERR_SHAPE;
+  if (epi_flags & ~(PQ_EPI_ACCUMULATE | PQ_EPI_GELU_TANH)) return PQ_ERR_UNSUPPORTED;
   if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return PQ_ERR_SHAPE;
   if (out_dtype != PQ_DTYPE_BF16 && out_dtype != PQ_DTYPE_FP16) return PQ_ERR_DTYPE;
   if (M == 0) return PQ_OK;
@@ -529,6 +530,7 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
   p.m_split = static_cast<int>(m_split);
   p.has_bias = bias != nullptr ? 1 : 0;
+  p.epi_flags = epi_flags;
   p.timing = (options().gemm_debug_timing != 0 && workspace != nullptr && ws_bytes >= 256 + 4096 * 64)
                  ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + 256) : nullptr;
   p.sched_pm = p.sched_pn = p.sched_m_steps = p.sched_n_rounds = 1;
@@ -537,7 +539,14 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
   // factor when there is a low-rank term
   {
     const int64_t pair_rows = (m_split + 255) / 256 + (M - m_split + 255) / 256;
-    if (options().gemm_pair != 0 && bn == 256 && (!has_lr || lb_t != nullptr) &&
+    const bool pair_legal = (!has_lr || lb_t != nullptr);
+    if (epi_flags != 0) {
+      // the epilogue variants exist in the CTA-pair kernel's vector store path only
+      if (!pair_legal || N % 32 != 0 || ldo % 8 != 0 || !aligned_to(out, 16)) return PQ_ERR_UNSUPPORTED;
+      return launch_gemm_pair(out_dtype == PQ_DTYPE_BF16, dbg_acc != nullptr, xq, ldx, w0, w1, ldw, has_lr ? t : nullptr, ldt,
+                              has_lr ? lb_t : nullptr, M, N, K, p, static_cast<cudaStream_t>(stream));
+    }
+    if (options().gemm_pair != 0 && bn == 256 && pair_legal &&
         pair_rows * ((N + 255) / 256) >= (options().gemm_pair == 2 ? 1 : sm_count() / 2)) {
       return launch_gemm_pair(out_dtype == PQ_DTYPE_BF16, dbg_acc != nullptr, xq, ldx, w0, w1, ldw, has_lr ? t : nullptr, ldt,
                               has_lr ? lb_t : nullptr, M, N, K, p, static_cast<cudaStream_t>(stream));
@@ -587,6 +596,15 @@ extern "C" int pq_int8_gemm(const int8_t* xq, int64_t ldx, const float* s_row, c
                             void* stream) {
   return gemm_common(xq, ldx, s_row, w, s_col, nullptr, nullptr, ldw, bias, t, ldt, lb, ldb, lb_t, R, lr_dtype, out,
                      out_dtype, ldo, M, M, N, K, workspace, ws_bytes, dbg_acc, stream);
+}
+
+extern "C" int pq_int8_gemm_ex(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t* w, int64_t ldw,
+                               const float* s_col, const float* bias, const void* t, int64_t ldt, const void* lb,
+                               int64_t ldb, const void* lb_t, int R, int lr_dtype, void* out, int out_dtype, int64_t ldo,
+                               int64_t M, int64_t N, int64_t K, int epilogue, void* workspace, size_t ws_bytes,
+                               void* stream) {
+  return gemm_common(xq, ldx, s_row, w, s_col, nullptr, nullptr, ldw, bias, t, ldt, lb, ldb, lb_t, R, lr_dtype, out,
+                     out_dtype, ldo, M, M, N, K, workspace, ws_bytes, nullptr, stream, epilogue);
 }
 
 extern "C" int pq_int8_gemm_grouped(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t* w_hi,

@@ -488,19 +488,42 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           for (int j = 0; j < 4; ++j) {
             const int nb = grp * 4 + j;
             const float2 bi = *reinterpret_cast<const float2*>(bias_s + col_unit + nb * 8 + 2 * q);
-            const float2 yA = __fadd2_rn(make_float2(__uint_as_float(v[4 * nb + 0]), __uint_as_float(v[4 * nb + 1])), bi);
-            const float2 yB = __fadd2_rn(make_float2(__uint_as_float(v[4 * nb + 2]), __uint_as_float(v[4 * nb + 3])), bi);
-            wA[j] = pack2(yA.x, yA.y, OutT{});
-            wB[j] = pack2(yB.x, yB.y, OutT{});
+            if constexpr (HAS_LR) {
+              const float2 yA = __fadd2_rn(make_float2(__uint_as_float(v[4 * nb + 0]), __uint_as_float(v[4 * nb + 1])), bi);
+              const float2 yB = __fadd2_rn(make_float2(__uint_as_float(v[4 * nb + 2]), __uint_as_float(v[4 * nb + 3])), bi);
+              wA[j] = pack2(yA.x, yA.y, OutT{});
+              wB[j] = pack2(yB.x, yB.y, OutT{});
+            } else {
+              // scalar additions: right behind the packed multiplication of scale_unit a packed addition gets
+              // contracted into a fused multiply-add, which would round differently from product-then-sum
+              wA[j] = pack2(__fadd_rn(__uint_as_float(v[4 * nb + 0]), bi.x), __fadd_rn(__uint_as_float(v[4 * nb + 1]), bi.y), OutT{});
+              wB[j] = pack2(__fadd_rn(__uint_as_float(v[4 * nb + 2]), bi.x), __fadd_rn(__uint_as_float(v[4 * nb + 3]), bi.y), OutT{});
+            }
           }
           const int col_grp = n0 + col_unit + grp * 32;
+          if (p.epi_flags & PQ_EPI_GELU_TANH) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { wA[j] = gelu_word<OutT>(wA[j]); wB[j] = gelu_word<OutT>(wB[j]); }
+          }
           if (vec_store && col_grp + 32 <= p.N) {
             quad_transpose(wA, q);
             quad_transpose(wB, q);
-            if (rA < row_end)
-              st_v4(out + static_cast<int64_t>(rA) * p.ldo + col_grp + q * 8, make_uint4(wA[0], wA[1], wA[2], wA[3]));
-            if (rB < row_end)
-              st_v4(out + static_cast<int64_t>(rB) * p.ldo + col_grp + q * 8, make_uint4(wB[0], wB[1], wB[2], wB[3]));
+            OutT* pA = out + static_cast<int64_t>(rA) * p.ldo + col_grp + q * 8;
+            OutT* pB = out + static_cast<int64_t>(rB) * p.ldo + col_grp + q * 8;
+            if (p.epi_flags & PQ_EPI_ACCUMULATE) {          // out += y: the sum of two rounded tensors, rounded once
+              if (rA < row_end) {
+                const uint4 o = ld_v4(pA);
+                wA[0] = add_word<OutT>(wA[0], o.x); wA[1] = add_word<OutT>(wA[1], o.y);
+                wA[2] = add_word<OutT>(wA[2], o.z); wA[3] = add_word<OutT>(wA[3], o.w);
+              }
+              if (rB < row_end) {
+                const uint4 o = ld_v4(pB);
+                wB[0] = add_word<OutT>(wB[0], o.x); wB[1] = add_word<OutT>(wB[1], o.y);
+                wB[2] = add_word<OutT>(wB[2], o.z); wB[3] = add_word<OutT>(wB[3], o.w);
+              }
+            }
+            if (rA < row_end) st_v4(pA, make_uint4(wA[0], wA[1], wA[2], wA[3]));
+            if (rB < row_end) st_v4(pB, make_uint4(wB[0], wB[1], wB[2], wB[3]));
           } else {
             store_pairs_slow(p.out, p.ldo, rA, rB, col_grp + 2 * q, row_end, p.N, make_uint4(wA[0], wA[1], wA[2], wA[3]),
                              make_uint4(wB[0], wB[1], wB[2], wB[3]));

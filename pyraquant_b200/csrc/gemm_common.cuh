@@ -23,8 +23,27 @@ struct GemmParams {
   int sched_m_steps;        // ceil(row tiles / sched_pm)
   int sched_n_rounds;       // ceil(column tiles / sched_pn)
   int has_bias;
+  int epi_flags;            // PQ_EPI_* bits (CTA-pair kernel only)
   long long* timing;        // experiments: per-CTA cycle counters [grid][8] (NULL in normal use)
 };
+
+// out = act(y) or out += y variants of the epilogue, on values already rounded to the output type (what separate
+// elementwise kernels after the Linear would see).
+__device__ __forceinline__ float gelu_tanh_f32(float x) {
+  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), tanh by the hardware approximation (relative error ~2^-11)
+  const float inner = 0.7978845608028654f * fmaf(0.044715f * x * x, x, x);
+  float th;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(inner));
+  return 0.5f * x * (1.0f + th);
+}
+template <typename OutT>
+__device__ __forceinline__ uint32_t gelu_word(uint32_t w) {
+  return pack2(gelu_tanh_f32(lo_f32(w, OutT{})), gelu_tanh_f32(hi_f32(w, OutT{})), OutT{});
+}
+template <typename OutT>
+__device__ __forceinline__ uint32_t add_word(uint32_t w, uint32_t prev) {
+  return pack2(lo_f32(w, OutT{}) + lo_f32(prev, OutT{}), hi_f32(w, OutT{}) + hi_f32(prev, OutT{}), OutT{});
+}
 
 struct TileCoord {
   int row0, row_end, n0, set;

@@ -340,6 +340,46 @@ class Int8Linear(nn.Module):
             return int8_gemm_lr(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B, x2.dtype, self._lr_Bt())
         return int8_gemm_fused(xq, sx, self.weight_int8, self.w_scale, self.bias, x2.dtype)
 
+    def forward_ex(self, x: torch.Tensor, epilogue: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``gelu_tanh(self(x))`` (``ops.EPI_GELU_TANH``) or ``out += self(x)`` (``ops.EPI_ACCUMULATE``, in place, returns
+        ``out``), with the extra step done in the GEMM epilogue when the shapes allow it and by the separate torch
+        kernels the reference's callers use otherwise.  The activation sees the Linear's output rounded to the
+        activation dtype, the sum is the sum of two rounded tensors: the values match the unfused sequence (the
+        GELU up to the hardware tanh approximation)."""
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        M, K = x2.shape
+        N = self.out_features
+        out2 = out.reshape(-1, N) if out is not None else None
+        assert not (epilogue & ops.EPI_ACCUMULATE) or (out2 is not None and out2.shape[0] == M and out2.dtype == x2.dtype)
+        lr = self.lr_A is not None
+        fused = (epilogue != 0 and M > 0 and x2.is_cuda and x2.dtype in ops._DT and K % 16 == 0
+                 and not torch.compiler.is_compiling() and (not lr or self._fusable_lowrank(x2))
+                 and (out2 is None or (out2.stride(1) == 1 and out2.data_ptr() == out.data_ptr()))
+                 and ops.epilogue_supported(N, out2.stride(0) if out2 is not None else N,
+                                            out2.data_ptr() if out2 is not None else 0, lr))
+        if not fused:
+            y = self.forward(x)
+            if epilogue & ops.EPI_GELU_TANH:
+                y = F.gelu(y, approximate="tanh")
+            if epilogue & ops.EPI_ACCUMULATE:
+                out.add_(y.reshape(out.shape))
+                return out
+            return y
+        grp = self.__dict__.get("_shared_input")
+        if grp is not None and x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0 and K % 32 == 0:
+            xq, sx, T = grp.prepare(x2)
+            t = grp.t_of(self, T) if lr else None
+        else:
+            t = (x2 @ self.lr_A) if lr else None
+            xq, sx = quant_rows(x2)
+        y2 = ops._gemm_impl(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B if lr else None, x2.dtype,
+                            lb_t=self._lr_Bt() if lr else None, epilogue=epilogue,
+                            out=out2 if (epilogue & ops.EPI_ACCUMULATE) else None)
+        if epilogue & ops.EPI_ACCUMULATE:
+            return out
+        return y2.reshape(*shape[:-1], N)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
@@ -367,6 +407,42 @@ class Int8Linear(nn.Module):
     def extra_repr(self) -> str:
         return (f"in={self.in_features}, out={self.out_features}, int8 per-channel W / per-token A, "
                 f"sm_100a tcgen05 kernel")
+
+
+class SplitInInt8Linear(nn.Module):
+    """A Linear split along its inputs, ``y = L0(x[..., :in0]) + L1(x[..., in0:])`` (the reference's ``SplitInLinear``,
+    pyraquant/external_quant.py:174-192, after conversion of its two halves): each half keeps its own per-token
+    quantisation and low-rank branch, and the second half's GEMM adds onto the first half's output in its epilogue
+    instead of a separate elementwise sum."""
+
+    def __init__(self, l0: "Int8Linear", l1: "Int8Linear", in0: Optional[int] = None):
+        super().__init__()
+        assert isinstance(l0, Int8Linear) and isinstance(l1, Int8Linear) and l0.out_features == l1.out_features
+        self.linears = nn.ModuleList([l0, l1])
+        self.in0 = int(l0.in_features if in0 is None else in0)
+        assert self.in0 == l0.in_features
+        self.in_features = l0.in_features + l1.in_features
+        self.out_features = l0.out_features
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.linears[0](x[..., : self.in0])
+        return self.linears[1].forward_ex(x[..., self.in0:], ops.EPI_ACCUMULATE, out=y)
+
+
+def fuse_split_inputs(model: nn.Module) -> int:
+    """Replaces every module that has the reference ``SplitInLinear`` layout (``linears`` = two converted halves and
+    ``in0``) by ``SplitInInt8Linear``.  Returns the number replaced."""
+    n = 0
+    for name, m in list(model.named_modules()):
+        halves = getattr(m, "linears", None)
+        if (isinstance(m, SplitInInt8Linear) or not isinstance(halves, nn.ModuleList) or len(halves) != 2
+                or not hasattr(m, "in0") or not all(isinstance(h, Int8Linear) for h in halves)):
+            continue
+        parent_name, _, attr = name.rpartition(".")
+        parent = model.get_submodule(parent_name) if parent_name else model
+        setattr(parent, attr, SplitInInt8Linear(halves[0], halves[1], int(m.in0)))
+        n += 1
+    return n
 
 
 def _quantize_weight_g32(w: torch.Tensor, group: int = 32) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -483,11 +559,13 @@ def group_shared_inputs(model: nn.Module, groups: Sequence[Sequence[str]] = FLUX
 
 def convert_linears_to_int8(model: nn.Module, device: Optional[str] = "cuda",
                             whitelist: Callable[[str], bool] = is_bf16_whitelisted,
-                            shared_input_groups: Optional[Sequence[Sequence[str]]] = None) -> Dict[str, object]:
+                            shared_input_groups: Optional[Sequence[Sequence[str]]] = None,
+                            fuse_split: bool = False) -> Dict[str, object]:
     """Swaps every non-whitelisted ``nn.Linear`` for ``Int8Linear`` in place and returns the same
     statistics dictionary as the reference (:444-445).  ``shared_input_groups`` (not in the reference; e.g.
     ``FLUX_SHARED_INPUT_GROUPS``) additionally ties sibling layers that read the same tensor into one quantisation
-    and one down-projection per input; the count is reported as ``n_shared_input_groups``."""
+    and one down-projection per input; the count is reported as ``n_shared_input_groups``.  ``fuse_split`` (not in the
+    reference) replaces converted ``SplitInLinear`` modules by ``SplitInInt8Linear`` (``n_split_fused``)."""
     dev = torch.device(device) if device is not None else None
     stats = {"n_int8_linear": 0, "n_bf16_linear_kept": 0, "params_int8": 0, "params_bf16_linear_kept": 0,
              "bf16_kept_names": []}
@@ -508,6 +586,8 @@ def convert_linears_to_int8(model: nn.Module, device: Optional[str] = "cuda",
     stats["bf16_equiv_gib"] = stats["params_int8"] * 2 / 2**30
     if shared_input_groups is not None:
         stats["n_shared_input_groups"] = group_shared_inputs(model, shared_input_groups)
+    if fuse_split:
+        stats["n_split_fused"] = fuse_split_inputs(model)
     return stats
 
 

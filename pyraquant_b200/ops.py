@@ -19,6 +19,9 @@ Tensor = torch.Tensor
 _DT = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16}
 # rank-32 term of the fused GEMM: tcgen05 tensor cores (True) or warp-level mma.sync in the epilogue (False)
 LOWRANK_ON_TENSOR_CORES = True
+# epilogue variants of pq_int8_gemm_ex
+EPI_ACCUMULATE = 1      # out += y (both rounded to the output type first)
+EPI_GELU_TANH = 2       # out = gelu_tanh(y rounded to the output type)
 _status_words: Dict[int, Tensor] = {}
 
 
@@ -156,10 +159,16 @@ def _gather_rows_impl(canvas: Tensor, row_idx: Tensor) -> Tensor:
 
 
 # ------------------------------------------------------------------------------------------------ GEMM
+def epilogue_supported(N: int, out_stride0: int, out_ptr: int, has_lowrank: bool, rank: int = 32) -> bool:
+    """Whether pq_int8_gemm_ex takes this problem (its variants live in the CTA-pair kernel's vector stores)."""
+    return N % 32 == 0 and out_stride0 % 8 == 0 and out_ptr % 16 == 0 and (not has_lowrank or rank == 32)
+
+
 def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias: Optional[Tensor],
                t: Optional[Tensor], lb: Optional[Tensor], out_dtype: torch.dtype,
                dbg_acc: Optional[Tensor] = None, w_lo: Optional[Tensor] = None, s_lo: Optional[Tensor] = None,
-               m_hi: Optional[int] = None, lb_t: Optional[Tensor] = None) -> Tensor:
+               m_hi: Optional[int] = None, lb_t: Optional[Tensor] = None, epilogue: int = 0,
+               out: Optional[Tensor] = None) -> Tensor:
     assert xq.is_cuda and xq.dtype == torch.int8 and xq.dim() == 2 and xq.stride(1) == 1
     assert w_int8.dtype == torch.int8 and w_int8.dim() == 2 and w_int8.stride(1) == 1
     M, K = xq.shape
@@ -175,7 +184,11 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
         xq = xq.contiguous()
     if w_int8.stride(0) % 16 != 0 or w_int8.data_ptr() % 16 != 0:
         w_int8 = w_int8.contiguous()
-    out = torch.empty((M, N), dtype=out_dtype, device=xq.device)
+    if out is None:
+        assert not (epilogue & EPI_ACCUMULATE), "accumulation needs the tensor to add onto"
+        out = torch.empty((M, N), dtype=out_dtype, device=xq.device)
+    else:
+        assert out.shape == (M, N) and out.dtype == out_dtype and out.stride(1) == 1 and out.device == xq.device
     R = 0
     ldt = ldb = 0
     if t is not None:
@@ -195,18 +208,25 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
     ws = status_word(xq.device)
     lib = _LIB()
     ldx = xq.stride(0) if M > 1 else max(K, xq.stride(0))
+    ldo = out.stride(0) if M > 1 else max(N, out.stride(0))
     with _on_device(xq):
-        if w_lo is None:
+        if epilogue:
+            assert w_lo is None and dbg_acc is None
+            rc = lib.pq_int8_gemm_ex(xq.data_ptr(), ldx, s_row.data_ptr(), w_int8.data_ptr(), w_int8.stride(0),
+                                     w_scale.data_ptr(), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, _ptr(lb_t), R,
+                                     _dt(out_dtype), out.data_ptr(), _dt(out_dtype), ldo,
+                                     M, N, K, int(epilogue), ws.data_ptr(), ws.numel() * 4, _stream(xq))
+        elif w_lo is None:
             rc = lib.pq_int8_gemm(xq.data_ptr(), ldx, s_row.data_ptr(), w_int8.data_ptr(), w_int8.stride(0),
                                   w_scale.data_ptr(), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, _ptr(lb_t), R,
-                                  _dt(out_dtype), out.data_ptr(), _dt(out_dtype), N, M, N, K, ws.data_ptr(), ws.numel() * 4,
+                                  _dt(out_dtype), out.data_ptr(), _dt(out_dtype), ldo, M, N, K, ws.data_ptr(), ws.numel() * 4,
                                   _ptr(dbg_acc), _stream(xq))
         else:
             assert w_lo.shape == w_int8.shape and w_lo.stride() == w_int8.stride() and s_lo is not None
             rc = lib.pq_int8_gemm_grouped(xq.data_ptr(), ldx, s_row.data_ptr(), w_int8.data_ptr(),
                                           w_scale.data_ptr(), w_lo.data_ptr(), s_lo.contiguous().data_ptr(),
                                           w_int8.stride(0), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, _ptr(lb_t), R,
-                                          _dt(out_dtype), out.data_ptr(), _dt(out_dtype), N, int(m_hi), M, N, K,
+                                          _dt(out_dtype), out.data_ptr(), _dt(out_dtype), ldo, int(m_hi), M, N, K,
                                           ws.data_ptr(), ws.numel() * 4, _stream(xq))
     if rc:
         _lib.check(rc, f"pq_int8_gemm(M={M}, N={N}, K={K})")

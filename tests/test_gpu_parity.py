@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from conftest import from_bf16_bits
 from oracle import oracle
@@ -221,6 +222,28 @@ def test_gemm_cta_pair_kernel(cuda_dev, M, N, K, dtype):
         _lib.set_option("gemm_pair", 1); _lib.set_option("gemm_max_ctas", 0)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_production_kernels_bit_equal_without_lowrank(cuda_dev, dtype):
+    """The non-debug instantiations (what users run) against the fp32 restatement, no low-rank term: identical bits
+    from every kernel variant."""
+    g = torch.Generator().manual_seed(77)
+    M, N, K = 900, 768, 384
+    xq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
+    wq = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8)
+    sr = torch.rand(M, generator=g) * 0.05 + 0.001
+    sc = torch.rand(N, generator=g) * 0.002 + 0.0001
+    b = torch.randn(N, generator=g) * 0.01
+    y32 = oracle.epilogue(oracle.int_mm(xq, wq), sr, sc, b, None, None, dtype)
+    d = cuda_dev
+    for pair, bn in ((0, 256), (0, 128), (2, 0)):
+        _lib.set_option("gemm_pair", pair); _lib.set_option("gemm_block_n", bn)
+        try:
+            y = int8_exec.int8_gemm_fused(xq.to(d), sr.to(d), wq.to(d), sc.to(d), b.to(d), dtype)
+        finally:
+            _lib.set_option("gemm_pair", 1); _lib.set_option("gemm_block_n", 0)
+        assert torch.equal(y.cpu(), y32), (pair, bn)
+
+
 def test_gemm_cfg0_layer(cuda_dev):
     """BASELINE config 0: M=4608, K=N=3072, rank-32 branch and bias, through Int8Linear.forward."""
     L = oracle.make_layer(0, 4608, 3072, 3072)
@@ -335,6 +358,57 @@ def test_shared_input_group(cuda_dev, monkeypatch):
     _ = layers[1](x.clone())
     assert calls["n"] == 3
     grp.clear()
+
+
+def _toy_layer(cuda_dev, g, K, N, lowrank=True, bias=True, dtype=torch.bfloat16):
+    lin = nn.Linear(K, N, bias=bias).to(dtype)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(N, K, generator=g) * 0.05)
+        if bias:
+            lin.bias.copy_(torch.randn(N, generator=g) * 0.1)
+    lr = ((torch.randn(K, 32, generator=g) * 0.05).to(dtype), (torch.randn(32, N, generator=g) * 0.05).to(dtype)) if lowrank else None
+    return int8_exec.Int8Linear(lin, device=cuda_dev, lowrank=lr)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("N,lowrank", [(768, True), (512, False), (264, True)])
+def test_epilogue_variants(cuda_dev, dtype, N, lowrank):
+    """GELU(tanh) and accumulate-into-output in the GEMM epilogue against the separate torch kernels on the layer's own
+    output: the sum bit for bit; the activation within two units in the last place of the output type (hardware tanh).
+    N = 264 is a shape the fused variants do not take: same results through the unfused sequence."""
+    g = torch.Generator().manual_seed(N + (1 if lowrank else 0))
+    K, M = 512, 700
+    layer = _toy_layer(cuda_dev, g, K, N, lowrank=lowrank, dtype=dtype)
+    x = (torch.randn(M, K, generator=g) * 1.5).to(dtype).to(cuda_dev)
+    y = layer(x)
+    ref_act = F.gelu(y, approximate="tanh")
+    got_act = layer.forward_ex(x, ops.EPI_GELU_TANH)
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    err = (got_act.float() - ref_act.float()).abs()
+    assert bool((err <= 2 * ulp * ref_act.float().abs() + 2e-3).all()), err.max().item()
+    base = (torch.randn(M, N, generator=g)).to(dtype).to(cuda_dev)
+    ref_sum = base + y
+    out = base.clone()
+    r = layer.forward_ex(x, ops.EPI_ACCUMULATE, out=out)
+    assert r is out and torch.equal(out, ref_sum)
+    both = base.clone()
+    layer.forward_ex(x, ops.EPI_ACCUMULATE | ops.EPI_GELU_TANH, out=both)
+    err = (both.float() - (base + ref_act).float()).abs()
+    assert bool((err <= 4 * ulp * (base + ref_act).float().abs() + 4e-3).all()), err.max().item()
+
+
+def test_split_input_linear(cuda_dev):
+    """y = L0(x[..., :in0]) + L1(x[..., in0:]) with the sum in the second GEMM's epilogue: identical to the two layers
+    and a torch add (pyraquant/external_quant.py:191-192), 3-D input, strided halves."""
+    g = torch.Generator().manual_seed(5)
+    in0, in1, N = 256, 768, 512
+    l0 = _toy_layer(cuda_dev, g, in0, N, lowrank=True, bias=False)
+    l1 = _toy_layer(cuda_dev, g, in1, N, lowrank=True, bias=True)
+    x = torch.randn(3, 333, in0 + in1, generator=g).to(torch.bfloat16).to(cuda_dev)
+    ref = l0(x[..., :in0]) + l1(x[..., in0:])
+    m = int8_exec.SplitInInt8Linear(l0, l1)
+    y = m(x)
+    assert y.shape == ref.shape and torch.equal(y, ref)
 
 
 def test_dequant_epilogue_and_linear_2d(cuda_dev):

@@ -233,3 +233,28 @@ def test_group_shared_inputs_on_flux_like_blocks():
     # the reference's statistics keys are untouched when the option is not used
     stats2 = int8_exec.convert_linears_to_int8(Net(), device=None, whitelist=lambda n: False)
     assert "n_shared_input_groups" not in stats2
+
+
+def test_fuse_split_inputs_replaces_reference_layout():
+    import torch.nn as nn
+    from pyraquant_b200 import int8_exec
+
+    class SplitInLinear(nn.Module):          # the layout of pyraquant/external_quant.py:174-192
+        def __init__(self, in0, in1, out):
+            super().__init__()
+            self.linears = nn.ModuleList([nn.Linear(in0, out, bias=False), nn.Linear(in1, out)]); self.in0 = in0
+
+        def forward(self, x):
+            return self.linears[0](x[..., : self.in0]) + self.linears[1](x[..., self.in0:])
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.proj_out = SplitInLinear(64, 128, 32); self.other = nn.Linear(32, 32)
+
+    net = nn.Sequential(Block(), Block())
+    stats = int8_exec.convert_linears_to_int8(net, device=None, whitelist=lambda n: False, fuse_split=True)
+    assert stats["n_int8_linear"] == 6 and stats["n_split_fused"] == 2
+    m = net[0].proj_out
+    assert isinstance(m, int8_exec.SplitInInt8Linear) and m.in0 == 64 and m.in_features == 192 and m.out_features == 32
+    assert isinstance(net[0].other, int8_exec.Int8Linear)
