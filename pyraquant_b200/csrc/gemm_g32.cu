@@ -1,8 +1,9 @@
 // Group-32 W8A8 GEMM for sm_100a:
 //   out[m,n] = sum_g s_a[m,g] * s_w[g,n] * (sum_{k in group g} xq[m,k] * w[n,k])  (+ bias[n])
 // A group is 32 consecutive K = exactly one tcgen05.mma kind::i8 instruction, so every instruction starts a
-// fresh int32 accumulator (exact per-group partial sum) in one of four tensor-memory slots; the epilogue warps
-// drain each slot and fold it into fp32 running sums in registers with one packed fused multiply-add per pair of
+// fresh int32 accumulator (exact per-group partial sum) in one of four tensor-memory slots (the four groups of
+// a 128-byte stage are issued back to back and handed over with one barrier); the epilogue warps drain each slot
+// and fold it into fp32 running sums in registers with one packed fused multiply-add per pair of
 // outputs: sum = fma(float(partial), s_a * s_w, sum).
 // The scale work (one multiply and one add per output element and group) is what bounds this kernel, not the
 // tensor pipe.  Roles and barriers mirror the per-channel GEMM: warp 0 TMA producer (operand stages plus a ring
@@ -18,7 +19,7 @@ constexpr int GBN = 128;                 // columns per tile = one tensor-memory
 constexpr int kSlots = 4;
 constexpr int kG32Stages = 4;
 constexpr int kGroupsPerStage = BK / 32;  // 4
-constexpr int kG32EpiWarps = 8;
+constexpr int kG32EpiWarps = 8;          // two per tensor-memory lane quarter: 64 columns of the tile each
 constexpr int kG32Threads = 64 + 32 * kG32EpiWarps;
 
 struct G32Params {
@@ -126,7 +127,7 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc_i8(BM, GBN);
       int stage = 0; uint32_t phase = 0; bool ok = true;
-      uint32_t gc = 0;                                // groups issued so far: slot = gc % 4, use = gc / 4
+      uint32_t gc = 0;                                // stages issued so far
       TileWalker w; w.init(p.sched_pm, p.sched_pn, mt_total, nt);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance()) {
@@ -139,17 +140,18 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
           const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
           const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + L::kABytes);
-#pragma unroll 1
-          for (int g = 0; g < kGroupsPerStage; ++g, ++gc) {
-            const uint32_t slot = gc & (kSlots - 1), use = gc / kSlots;
-            if (!wait_or_abort(&slot_empty[slot], (use & 1u) ^ 1u, abort_flag)) {
-              report_timeout(p.status, 2, 2); *abort_flag = 1; ok = false; break;
-            }
-            tc_fence_after();
-            tc_mma_i8(tmem_base + slot * GBN, a_desc + static_cast<uint64_t>(2 * g), b_desc + static_cast<uint64_t>(2 * g),
-                      idesc, 0u);
-            tc_commit(&slot_full[slot]);
+          // the four groups of a stage go to the four slots back to back; one "slots free" wait and one "slots
+          // written" commit per stage (every barrier operation costs this thread a few hundred cycles)
+          if (!wait_or_abort(&slot_empty[0], (gc & 1u) ^ 1u, abort_flag)) {
+            report_timeout(p.status, 2, 2); *abort_flag = 1; ok = false; break;
           }
+          tc_fence_after();
+#pragma unroll
+          for (int g = 0; g < kGroupsPerStage; ++g)
+            tc_mma_i8(tmem_base + g * GBN, a_desc + static_cast<uint64_t>(2 * g), b_desc + static_cast<uint64_t>(2 * g),
+                      idesc, 0u);
+          tc_commit(&slot_full[0]);
+          ++gc;
           if (ok) tc_commit(&empty_bar[stage]);
           if (++stage == kG32Stages) { stage = 0; phase ^= 1u; }
         }
@@ -184,51 +186,58 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           const bool landed = wait_or_abort(&sfull_bar[stage], phase, abort_flag);
           if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 4); *abort_flag = 1; aborted = true; }
         }
-        // row scales of this thread's four rows for the four groups of the stage
-        float4 sa4[2][2];
-#pragma unroll
-        for (int mb = 0; mb < 2; ++mb) {
-          const int r = quarter * 32 + mb * 16 + g4;
-          sa4[mb][0] = aborted ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(sa_s + r * 4);
-          sa4[mb][1] = aborted ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(sa_s + (r + 8) * 4);
+        if (!aborted) {
+          const bool landed = wait_or_abort(&slot_full[0], gc & 1u, abort_flag);
+          if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 3); *abort_flag = 1; aborted = true; }
+        }
+        ++gc;
+        if (!aborted) tc_fence_after();
+        uint32_t va[32], vb[32];
+        if (!aborted) {
+          const uint32_t t0_acc = tmem_base + half * 64;
+          tmem_ld_16x256b_x8(t0_acc + (static_cast<uint32_t>(quarter * 32) << 16), va);
         }
 #pragma unroll 1
-        for (int g = 0; g < kGroupsPerStage; ++g, ++gc) {
-          const uint32_t slot = gc & (kSlots - 1), use = gc / kSlots;
-          if (!aborted) {
-            const bool landed = wait_or_abort(&slot_full[slot], use & 1u, abort_flag);
-            if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 3); *abort_flag = 1; aborted = true; }
-          }
+        for (int g = 0; g < kGroupsPerStage; ++g) {
           if (aborted) continue;
-          tc_fence_after();
-          uint32_t va[32], vb[32];
-          const uint32_t t_acc = tmem_base + slot * GBN + half * 64;
-          tmem_ld_16x256b_x8(t_acc + (static_cast<uint32_t>(quarter * 32) << 16), va);
-          tmem_ld_16x256b_x8(t_acc + (static_cast<uint32_t>(quarter * 32 + 16) << 16), vb);
-          tc_wait_ld();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&slot_empty[slot]);      // the slot can be refilled while we do the arithmetic
-          const float saA0 = g == 0 ? sa4[0][0].x : g == 1 ? sa4[0][0].y : g == 2 ? sa4[0][0].z : sa4[0][0].w;
-          const float saB0 = g == 0 ? sa4[0][1].x : g == 1 ? sa4[0][1].y : g == 2 ? sa4[0][1].z : sa4[0][1].w;
-          const float saA1 = g == 0 ? sa4[1][0].x : g == 1 ? sa4[1][0].y : g == 2 ? sa4[1][0].z : sa4[1][0].w;
-          const float saB1 = g == 0 ? sa4[1][1].x : g == 1 ? sa4[1][1].y : g == 2 ? sa4[1][1].z : sa4[1][1].w;
-          const float2 kMagic2 = make_float2(12582912.0f, 12582912.0f);
+          const uint32_t t_acc = tmem_base + g * GBN + half * 64;
+          const float2 kNegMagic2 = make_float2(-12582912.0f, -12582912.0f);
+          // |partial| <= 32 * 127^2 < 2^22: adding the bit pattern of 1.5 * 2^23 converts exactly
+          auto cvt2 = [&](uint32_t a, uint32_t b) {
+            return __fadd2_rn(make_float2(__int_as_float(0x4B400000 + static_cast<int32_t>(a)),
+                                          __int_as_float(0x4B400000 + static_cast<int32_t>(b))), kNegMagic2);
+          };
           const float* swg = sw_s + g * GBN + half * 64 + 2 * q;
+          // row scales of this thread's four rows for this group (shared memory tile [128 rows][4 groups])
+          const float* sag = sa_s + (quarter * 32 + g4) * kGroupsPerStage + g;
+          tc_wait_ld();                                                       // rows 0..15 of group g are in va
+          tmem_ld_16x256b_x8(t_acc + (static_cast<uint32_t>(quarter * 32 + 16) << 16), vb);
+          {
+            const float saA = sag[0], saB = sag[8 * kGroupsPerStage];
 #pragma unroll
-          for (int nb = 0; nb < 8; ++nb) {
-            const float2 sw2 = *reinterpret_cast<const float2*>(swg + nb * 8);
-            // |partial| <= 32 * 127^2 < 2^22: adding the bit pattern of 1.5 * 2^23 converts exactly
-            auto cvt2 = [&](uint32_t a, uint32_t b) {
-              float2 f = make_float2(__int_as_float(0x4B400000 + static_cast<int32_t>(a)),
-                                     __int_as_float(0x4B400000 + static_cast<int32_t>(b)));
-              return __fadd2_rn(f, make_float2(-kMagic2.x, -kMagic2.y));
-            };
-            // same arithmetic as the CPU restatement: running sum = fma(partial, s_a * s_w, running sum)
-            y[0][nb][0] = __ffma2_rn(cvt2(va[4 * nb + 0], va[4 * nb + 1]), __fmul2_rn(make_float2(saA0, saA0), sw2), y[0][nb][0]);
-            y[0][nb][1] = __ffma2_rn(cvt2(va[4 * nb + 2], va[4 * nb + 3]), __fmul2_rn(make_float2(saB0, saB0), sw2), y[0][nb][1]);
-            y[1][nb][0] = __ffma2_rn(cvt2(vb[4 * nb + 0], vb[4 * nb + 1]), __fmul2_rn(make_float2(saA1, saA1), sw2), y[1][nb][0]);
-            y[1][nb][1] = __ffma2_rn(cvt2(vb[4 * nb + 2], vb[4 * nb + 3]), __fmul2_rn(make_float2(saB1, saB1), sw2), y[1][nb][1]);
+            for (int nb = 0; nb < 8; ++nb) {
+              const float2 sw2 = *reinterpret_cast<const float2*>(swg + nb * 8);
+              // same arithmetic as the CPU restatement: running sum = fma(partial, s_a * s_w, running sum)
+              y[0][nb][0] = __ffma2_rn(cvt2(va[4 * nb + 0], va[4 * nb + 1]), __fmul2_rn(make_float2(saA, saA), sw2), y[0][nb][0]);
+              y[0][nb][1] = __ffma2_rn(cvt2(va[4 * nb + 2], va[4 * nb + 3]), __fmul2_rn(make_float2(saB, saB), sw2), y[0][nb][1]);
+            }
+          }
+          tc_wait_ld();                                                       // rows 16..31 of group g are in vb
+          if (g + 1 < kGroupsPerStage) {
+            tmem_ld_16x256b_x8(t_acc + GBN + (static_cast<uint32_t>(quarter * 32) << 16), va);
+          } else {
+            tc_fence_before();                                                // all four slots are in registers:
+            __syncwarp();                                                     // the MMA thread may refill them
+            if (lane == 0) mbar_arrive(&slot_empty[0]);
+          }
+          {
+            const float saA = sag[16 * kGroupsPerStage], saB = sag[24 * kGroupsPerStage];
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb) {
+              const float2 sw2 = *reinterpret_cast<const float2*>(swg + nb * 8);
+              y[1][nb][0] = __ffma2_rn(cvt2(vb[4 * nb + 0], vb[4 * nb + 1]), __fmul2_rn(make_float2(saA, saA), sw2), y[1][nb][0]);
+              y[1][nb][1] = __ffma2_rn(cvt2(vb[4 * nb + 2], vb[4 * nb + 3]), __fmul2_rn(make_float2(saB, saB), sw2), y[1][nb][1]);
+            }
           }
         }
         // scales of this stage consumed
