@@ -15,40 +15,39 @@ namespace {
 
 constexpr int kThreads = 256;
 
-template <typename T> __device__ __forceinline__ uint32_t abs2_max(uint32_t acc, uint32_t w);
-template <> __device__ __forceinline__ uint32_t abs2_max<__nv_bfloat16>(uint32_t acc, uint32_t w) {
-  __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&acc);
-  __nv_bfloat162 b = __habs2(*reinterpret_cast<__nv_bfloat162*>(&w));
-  __nv_bfloat162 r = __hmax2(a, b);
-  return *reinterpret_cast<uint32_t*>(&r);
-}
-template <> __device__ __forceinline__ uint32_t abs2_max<__half>(uint32_t acc, uint32_t w) {
-  __half2 a = *reinterpret_cast<__half2*>(&acc);
-  __half2 b = __habs2(*reinterpret_cast<__half2*>(&w));
-  __half2 r = __hmax2(a, b);
-  return *reinterpret_cast<uint32_t*>(&r);
+// Running maximum of |x| over packed 16-bit floats, kept as two packed magnitudes.  Clearing the sign bits leaves
+// non-negative bf16 / fp16 bit patterns, whose order as unsigned 16-bit integers is their order as numbers, so the
+// maximum is an integer one: two masked words and the running value per three-input halfword maximum.  (The
+// floating-point packed abs / max instructions of these types issue on the slow special-function pipe.)
+template <typename T>
+__device__ __forceinline__ uint32_t absmax_chunk(uint32_t acc, const uint4& v) {
+  constexpr uint32_t kMag = 0x7FFF7FFFu;
+  acc = __vimax3_u16x2(acc, v.x & kMag, v.y & kMag);
+  acc = __vimax3_u16x2(acc, v.z & kMag, v.w & kMag);
+  return acc;
 }
 
 // Quantisation of one 16-byte chunk (8 elements) to 8 int8 codes (two 32-bit words).
 //
 // Exact contract: code = round_half_even(fl(x / scale)) with the IEEE quotient.  Fast path without a division:
-// with inv = fl(1/scale), both x * inv * (1 - 2^-18) and x * inv * (1 + 2^-18) are rounded to the nearest integer by
+// with inv = fl(1/scale), both x * inv * (1 - 2^-21) and x * inv * (1 + 2^-21) are rounded to the nearest integer by
 // a fused multiply-add with 1.5 * 2^23 (one rounding, integer left in the low mantissa bits).  The IEEE quotient
-// lies between the two products (its relative error and that of inv are below 2^-23), and rounding is monotonic,
-// so whenever both give the same integer it is the exact answer.  If any of the 8 elements disagrees (a quotient
-// within ~2^-17 relative of a rounding boundary, about one chunk in a thousand) the chunk is redone with real
-// divisions.  Codes never leave [-127, 127] because |x| <= absmax.  No conversion instructions are used: those run
+// lies between the two products: it, inv and the two scaled reciprocals each carry a relative rounding error of at
+// most 2^-24, so a margin of 1.5 * 2^-23 would do and 2^-21 is 2.7 times that.  Rounding is monotonic, so whenever
+// both products give the same integer it is the exact answer.  If any of the 8 elements disagrees (a quotient
+// within ~2^-20 relative of a rounding boundary) the chunk is redone with real divisions; the margin is kept
+// small because one such element sends its whole warp through the slow path.  Codes never leave [-127, 127] because |x| <= absmax.  No conversion instructions are used: those run
 // on a slow pipe and made the first version of this kernel issue-bound.
 struct QuantScale {
   float scale;       // absmax / 127 (or the 1e-8 floor / 127)
-  float2 inv_lo;     // (1/scale) * (1 - 2^-18), twice
-  float2 inv_hi;     // (1/scale) * (1 + 2^-18), twice
+  float2 inv_lo;     // (1/scale) * (1 - 2^-21), twice
+  float2 inv_hi;     // (1/scale) * (1 + 2^-21), twice
 };
 __device__ __forceinline__ QuantScale make_quant_scale(float amax) {
   QuantScale qs;
   qs.scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
   const float inv = __fdiv_rn(1.0f, qs.scale);
-  const float lo = inv * (1.0f - 3.814697265625e-6f), hi = inv * (1.0f + 3.814697265625e-6f);
+  const float lo = inv * (1.0f - 4.76837158203125e-7f), hi = inv * (1.0f + 4.76837158203125e-7f);   // 1 -+ 2^-21
   qs.inv_lo = make_float2(lo, lo);
   qs.inv_hi = make_float2(hi, hi);
   return qs;
@@ -134,8 +133,7 @@ pq_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, const int32_t* __rest
     uint32_t acc = 0u;
 #pragma unroll
     for (int j = 0; j < CPT; ++j) {
-      acc = abs2_max<T>(acc, v[j].x); acc = abs2_max<T>(acc, v[j].y);
-      acc = abs2_max<T>(acc, v[j].z); acc = abs2_max<T>(acc, v[j].w);
+      acc = absmax_chunk<T>(acc, v[j]);
     }
     float amax = amax_of_packed<T>(acc);
     constexpr int W = TPR < 32 ? TPR : 32;
@@ -170,8 +168,7 @@ pq_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, const int32_t* __rest
 #pragma unroll
     for (int j = 0; j < CPT; ++j) {
       uint32_t acc = 0u;
-      acc = abs2_max<T>(acc, v[j].x); acc = abs2_max<T>(acc, v[j].y);
-      acc = abs2_max<T>(acc, v[j].z); acc = abs2_max<T>(acc, v[j].w);
+      acc = absmax_chunk<T>(acc, v[j]);
       float amax = amax_of_packed<T>(acc);
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
@@ -204,8 +201,7 @@ pq_quant_rows_kernel_long(const T* __restrict__ x, int64_t ldx, const int32_t* _
   if (have_src) {
     for (int c = threadIdx.x; c < nchunk; c += kThreads) {
       uint4 v = xrow[c];
-      acc = abs2_max<T>(acc, v.x); acc = abs2_max<T>(acc, v.y);
-      acc = abs2_max<T>(acc, v.z); acc = abs2_max<T>(acc, v.w);
+      acc = absmax_chunk<T>(acc, v);
     }
   }
   float amax = amax_of_packed<T>(acc);
