@@ -269,7 +269,8 @@ def main_ours(args):
     # ---- end to end through host buffers (pinned), copies inside the timed region
     e2e = None
     if not args.no_e2e:
-        chunk = 8192
+        # about eight chunks per rank so that the three pipeline stages overlap at every GPU count
+        chunk = min(8192, max(1024, ((rows + 7) // 8 + 255) // 256 * 256))
         pipes = [HostRowPipeline(m, K, torch.bfloat16, dev, chunk) for (_n, K, _N), m in zip(LAYERS, mods)]
         hx = [torch.empty((rows, K), dtype=torch.bfloat16).pin_memory() for _n, K, _N in LAYERS]
         hy = [torch.empty((rows, N), dtype=torch.bfloat16).pin_memory() for _n, _K, N in LAYERS]
