@@ -59,13 +59,21 @@ __device__ __forceinline__ float2 unpack2(uint32_t w) {
   return make_float2(lo_f32(w, tag), hi_f32(w, tag));
 }
 
-__device__ __noinline__ void quant_chunk_exact(const float (&f)[8], float scale, uint32_t& lo, uint32_t& hi) {
+// The rare exact path: real divisions, in line (a call in the hot loop costs more in register shuffling around
+// it than these instructions cost in size; an array argument even put a stack frame and its stores on the hot path).
+template <typename T>
+__device__ __forceinline__ void quant_chunk_exact(const uint4& v, float scale, uint32_t& lo, uint32_t& hi) {
   const float kMagic = 12582912.0f;
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
   uint32_t c[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) c[i] = static_cast<uint32_t>(__float_as_int(__fdiv_rn(f[i], scale) + kMagic)) & 0xFFu;
-  lo = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
-  hi = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = unpack2<T>(w[i]);
+    c[2 * i] = __float_as_uint(__fdiv_rn(f.x, scale) + kMagic);
+    c[2 * i + 1] = __float_as_uint(__fdiv_rn(f.y, scale) + kMagic);
+  }
+  lo = __byte_perm(__byte_perm(c[0], c[1], 0x0040), __byte_perm(c[2], c[3], 0x0040), 0x5410);
+  hi = __byte_perm(__byte_perm(c[4], c[5], 0x0040), __byte_perm(c[6], c[7], 0x0040), 0x5410);
 }
 
 template <typename T>
@@ -82,16 +90,10 @@ __device__ __forceinline__ void quant_chunk(const uint4& v, const QuantScale& qs
     m[2 * i] = __float_as_uint(a.x); m[2 * i + 1] = __float_as_uint(a.y);
     differ |= (m[2 * i] ^ __float_as_uint(b.x)) | (m[2 * i + 1] ^ __float_as_uint(b.y));
   }
-  if (differ != 0u) {
-    float f[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { const float2 t = unpack2<T>(w[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
-    quant_chunk_exact(f, qs.scale, lo, hi);
-    return;
-  }
   // low bytes of the eight integers -> two words
   lo = __byte_perm(__byte_perm(m[0], m[1], 0x0040), __byte_perm(m[2], m[3], 0x0040), 0x5410);
   hi = __byte_perm(__byte_perm(m[4], m[5], 0x0040), __byte_perm(m[6], m[7], 0x0040), 0x5410);
+  if (differ != 0u) quant_chunk_exact<T>(v, qs.scale, lo, hi);
 }
 
 template <typename T>
@@ -276,12 +278,23 @@ int dispatch(const void* x, int64_t ldx, const int32_t* row_idx, int64_t src_row
   const int nchunk = K >> 3;
   // team size (threads per row) and chunks per thread: the row must fit the team's registers
   const int force = options().quant_tpr;
+  if (force == 32 && nchunk <= 32 * 8) return launch_one<T, GATHER, GROUP32, 32, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (force == 32 && nchunk <= 32 * 12) return launch_one<T, GATHER, GROUP32, 32, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (force == 64 && nchunk <= 64 * 8) return launch_one<T, GATHER, GROUP32, 64, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (force == 64 && nchunk <= 64 * 12) return launch_one<T, GATHER, GROUP32, 64, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (force == 128 && nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (force == 256 && nchunk <= 256 * 8) return launch_one<T, GATHER, GROUP32, 256, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (nchunk <= 32 * 2) return launch_one<T, GATHER, GROUP32, 32, 2>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (nchunk <= 32 * 4) return launch_one<T, GATHER, GROUP32, 32, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if constexpr (!GROUP32) {
+    // per-row scales: a single warp per row up to 3072 elements (no shared-memory hop, the per-row work is spread over
+    // up to 96 elements per thread: a quarter fewer instructions than four warps per row), measured best per rung
+    if (nchunk <= 32 * 8) return launch_one<T, GATHER, GROUP32, 32, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+    if (nchunk <= 32 * 12) return launch_one<T, GATHER, GROUP32, 32, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+    if (nchunk <= 64 * 8) return launch_one<T, GATHER, GROUP32, 64, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+    if (nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+    if (nchunk <= 64 * 12) return launch_one<T, GATHER, GROUP32, 64, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  }
   if (nchunk <= 64 * 4) return launch_one<T, GATHER, GROUP32, 64, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (nchunk <= 128 * 3) return launch_one<T, GATHER, GROUP32, 128, 3>(x, ldx, row_idx, src_rows, q, s, M, K, st);
   if (nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st);
