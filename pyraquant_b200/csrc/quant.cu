@@ -81,19 +81,24 @@ __device__ __forceinline__ void quant_chunk(const uint4& v, const QuantScale& qs
   const float2 kMagic2 = make_float2(12582912.0f, 12582912.0f);
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
   uint32_t m[8];
-  uint32_t differ = 0u;
+  // Disagreement test on the fp32 pipe (the integer pipe, half as wide, is the busiest one in this kernel): a - b
+  // is a small exact integer, the squares are summed exactly, and the sum is zero only if every pair agrees.
+  float2 dsq = make_float2(0.0f, 0.0f);
+  const float2 kMinusOne2 = make_float2(-1.0f, -1.0f);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const float2 f = unpack2<T>(w[i]);
     const float2 a = __ffma2_rn(f, qs.inv_lo, kMagic2);
     const float2 b = __ffma2_rn(f, qs.inv_hi, kMagic2);
     m[2 * i] = __float_as_uint(a.x); m[2 * i + 1] = __float_as_uint(a.y);
-    differ |= (m[2 * i] ^ __float_as_uint(b.x)) | (m[2 * i + 1] ^ __float_as_uint(b.y));
+    const float2 d = __ffma2_rn(b, kMinusOne2, a);
+    dsq = __ffma2_rn(d, d, dsq);
   }
+  const bool differ = (dsq.x + dsq.y) != 0.0f;
   // low bytes of the eight integers -> two words
   lo = __byte_perm(__byte_perm(m[0], m[1], 0x0040), __byte_perm(m[2], m[3], 0x0040), 0x5410);
   hi = __byte_perm(__byte_perm(m[4], m[5], 0x0040), __byte_perm(m[6], m[7], 0x0040), 0x5410);
-  if (differ != 0u) quant_chunk_exact<T>(v, qs.scale, lo, hi);
+  if (differ) quant_chunk_exact<T>(v, qs.scale, lo, hi);
 }
 
 template <typename T>
