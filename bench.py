@@ -134,6 +134,53 @@ def make_cpu_layers(rows: int):
     return out
 
 
+def measure_issue_ceiling(dev, sustain_s: float = 3.0):
+    """Measured ceiling of the INT8 tensor pipe on this GPU: one CTA per SM issues tcgen05.mma kind::i8 128x256x32 back
+    to back on operands that stay in shared memory (no global traffic at all).  Reported: a short burst on an idle GPU,
+    and the rate over the last quarter of `sustain_s` seconds of back-to-back launches, once with constant operands
+    (the pipe's rate at the clock the GPU can hold with little switching activity) and once with pseudo-random operands
+    (tensor-core power is data dependent: with random bytes the power cap alone pulls the clock down)."""
+    import torch
+    from pyraquant_b200 import _lib, ops
+    lib = _lib.load()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    cycles = torch.zeros(sms, dtype=torch.int64, device=dev)
+    ws = ops.status_word(dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ops_per_iter = 4 * 2.0 * 128 * 256 * 32 * sms
+
+    def launch(iters):
+        rc = lib.pq_i8_mma_issue_loop(sms, iters, cycles.data_ptr(), ws.data_ptr(), ws.numel() * 4, stream)
+        _lib.check(rc, "pq_i8_mma_issue_loop")
+
+    def sustained(sign):
+        it_long = 200000
+        t_end = time.time() + sustain_s
+        marks = []
+        while time.time() < t_end:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); launch(sign * it_long); b.record()
+            marks.append((a, b))
+            torch.cuda.synchronize(dev)
+        tail = marks[-max(1, len(marks) // 4):]
+        return ops_per_iter * it_long * len(tail) / (sum(a.elapsed_time(b) for a, b in tail) * 1e-3) / 1e12
+
+    launch(2000)
+    torch.cuda.synchronize(dev)
+    time.sleep(0.5)                                    # let the clocks recover from whatever ran before
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    it_burst = 20000
+    e0.record(); launch(it_burst); e1.record()
+    torch.cuda.synchronize(dev)
+    burst = ops_per_iter * it_burst / (e0.elapsed_time(e1) * 1e-3) / 1e12
+    cyc_per_mma = float(cycles.double().mean().item()) / (4.0 * it_burst)
+    s_const = sustained(1)
+    s_rand = sustained(-1)                             # negative iteration count = pseudo-random operand bytes
+    ops.check_device_status(dev)
+    return {"burst_tops": burst, "sustained_tops": s_const, "sustained_random_operands_tops": s_rand,
+            "cycles_per_mma_128x256x32": cyc_per_mma, "sustain_seconds": sustain_s, "ctas": sms}
+
+
 def run_cpu_baseline(sample_rows: int, reps: int):
     torch.set_num_threads(os.cpu_count() or 1)
     layers = make_cpu_layers(sample_rows)
@@ -342,6 +389,11 @@ def main_ours(args):
     }
     if e2e is not None:
         line["e2e"] = e2e
+    if world == 1 and not args.no_ceiling and not args.no_cpu:       # diagnostic runs (--no-cpu) skip it too
+        ceil = measure_issue_ceiling(dev)
+        line["roofline"]["int8_issue_ceiling"] = ceil
+        line["roofline"]["frac_of_issue_ceiling_sustained"] = achieved / ceil["sustained_tops"]
+        line["roofline"]["frac_of_issue_ceiling_random_operands"] = achieved / ceil["sustained_random_operands_tops"]
     if world == 1 and not args.no_cpu:
         cb, _t = run_cpu_baseline(args.cpu_sample_rows, 3)
         line["cpu_baseline"] = cb
@@ -363,6 +415,7 @@ if __name__ == "__main__":
                     help="total token rows (default: the 4K stage's 66048); smaller values are for profiler captures only")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-ceiling", action="store_true", help="skip the tensor-pipe issue-loop ceiling measurement")
     args = ap.parse_args()
     M_TOTAL = int(args.rows)
     if args.impl == "reference":

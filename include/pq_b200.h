@@ -211,7 +211,9 @@ int pq_read_status_word(void* workspace, int32_t* raw, int clear, void* stream);
 
 /* Tensor-pipe ceiling probe: every CTA issues `iters` tcgen05.mma kind::i8 128x256x32 instructions
  * on shared-memory operands with no global traffic and writes elapsed clock cycles per CTA to
- * cycles[ctas] (int64).  Used by the benchmark for the measured INT8 ceiling. */
+ * cycles[ctas] (int64).  The operands are all ones; a negative `iters` runs |iters| iterations on pseudo-random
+ * operand bytes instead (tensor-core power, and with it the clock the GPU holds, depends on the data).  Used by the
+ * benchmark for the measured INT8 ceiling. */
 int pq_i8_mma_issue_loop(int ctas, int iters, long long* cycles, void* workspace, size_t ws_bytes,
                          void* stream);
 

@@ -375,8 +375,20 @@ pq_i8_mma_issue_loop_kernel(int iters, long long* cycles, int32_t* status) {
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem + kA + kB);
   uint32_t* holder = reinterpret_cast<uint32_t*>(smem + kA + kB + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kA + kB + 24);
-  for (int i = threadIdx.x; i < (kA + kB) / 16; i += blockDim.x)
-    reinterpret_cast<uint4*>(smem)[i] = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+  // operands: all ones (iters >= 0), or pseudo-random bytes (iters < 0: data-dependent power of the tensor cores)
+  const bool random_fill = iters < 0;
+  if (random_fill) iters = -iters;
+  for (int i = threadIdx.x; i < (kA + kB) / 16; i += blockDim.x) {
+    uint4 v = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+    if (random_fill) {
+      uint32_t h = (static_cast<uint32_t>(i) * 4u + blockIdx.x * 7919u) * 2654435761u;
+      v.x = h ^ (h >> 15); h = h * 2246822519u + 3266489917u;
+      v.y = h ^ (h >> 13); h = h * 2246822519u + 3266489917u;
+      v.z = h ^ (h >> 16); h = h * 2246822519u + 3266489917u;
+      v.w = h ^ (h >> 14);
+    }
+    reinterpret_cast<uint4*>(smem)[i] = v;
+  }
   if (threadIdx.x == 0) { mbar_init(bar, 1); *abort_flag = 0; fence_mbar_init(); }
   fence_proxy_async_smem();
   if (threadIdx.x < 32) { tmem_alloc(holder, 256); tmem_relinquish(); }
@@ -619,7 +631,7 @@ extern "C" int pq_int8_gemm_grouped(const int8_t* xq, int64_t ldx, const float* 
 
 extern "C" int pq_i8_mma_issue_loop(int ctas, int iters, long long* cycles, void* workspace, size_t ws_bytes,
                                     void* stream) {
-  if (ctas <= 0 || iters <= 0 || ctas > 4096 || iters > (1 << 24)) return PQ_ERR_SHAPE;
+  if (ctas <= 0 || iters == 0 || ctas > 4096 || iters > (1 << 24) || iters < -(1 << 24)) return PQ_ERR_SHAPE;
   if (cycles == nullptr) return PQ_ERR_NULL;
   if (workspace != nullptr && ws_bytes < PQ_GEMM_WORKSPACE_BYTES) return PQ_ERR_WORKSPACE;
   constexpr int kSmem = BM * BK + 256 * BK + 64 + 1024;
