@@ -19,8 +19,14 @@ constexpr int GBN = 128;                 // columns per tile = one tensor-memory
 constexpr int kSlots = 4;
 constexpr int kG32Stages = 4;
 constexpr int kGroupsPerStage = BK / 32;  // 4
-constexpr int kG32EpiWarps = 8;          // two per tensor-memory lane quarter: 64 columns of the tile each
+constexpr int kG32EpiWarps = 8;          // two per tensor-memory lane quarter (16 measured the same: not latency-bound)
+constexpr int kColW = GBN / (kG32EpiWarps / 4);   // columns of the tile per epilogue warp (64)
+constexpr int kNB = kColW / 8;           // 8-column blocks per warp
 constexpr int kG32Threads = 64 + 32 * kG32EpiWarps;
+
+// 16 lanes x (8 x NB) columns of tensor memory -> 4 x NB registers per thread
+__device__ __forceinline__ void tmem_ld_cols(uint32_t addr, uint32_t (&v)[32]) { tmem_ld_16x256b_x8(addr, v); }
+__device__ __forceinline__ void tmem_ld_cols(uint32_t addr, uint32_t (&v)[16]) { tmem_ld_16x256b_x4(addr, v); }
 
 struct G32Params {
   const float* bias;
@@ -158,9 +164,10 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // ------------------------------------------------------------------ epilogue (warps 2..)
     const int quarter = warp & 3;              // tensor-memory lanes [32*quarter, +32)
-    const int half = (warp - 2) >> 2;          // columns [64*half, +64) of the tile
+    const int colg = (warp - 2) >> 2;          // columns [kColW*colg, +kColW) of the tile
+    auto ld_cols = [](uint32_t addr, uint32_t (&v)[4 * kNB]) { tmem_ld_cols(addr, v); };
     const int g4 = lane >> 2, q = lane & 3;
     OutT* out = static_cast<OutT*>(p.out);
     const bool vec_store = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
@@ -172,11 +179,11 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     for (; w.valid(); w.advance()) {
       const int row0 = w.mt * BM, n0 = w.ntile * GBN;
       // y[mb][nb][0] = (row g4, cols 2q, 2q+1), y[mb][nb][1] = (row g4 + 8, same cols) of n8 block nb, 16-row block mb
-      float2 y[2][8][2];
+      float2 y[2][kNB][2];
 #pragma unroll
       for (int mb = 0; mb < 2; ++mb)
 #pragma unroll
-        for (int nb = 0; nb < 8; ++nb) { y[mb][nb][0] = make_float2(0.f, 0.f); y[mb][nb][1] = make_float2(0.f, 0.f); }
+        for (int nb = 0; nb < kNB; ++nb) { y[mb][nb][0] = make_float2(0.f, 0.f); y[mb][nb][1] = make_float2(0.f, 0.f); }
 
 #pragma unroll 1
       for (int kb = 0; kb < num_kb; ++kb) {
@@ -192,30 +199,30 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
         ++gc;
         if (!aborted) tc_fence_after();
-        uint32_t va[32], vb[32];
+        uint32_t va[4 * kNB], vb[4 * kNB];
         if (!aborted) {
-          const uint32_t t0_acc = tmem_base + half * 64;
-          tmem_ld_16x256b_x8(t0_acc + (static_cast<uint32_t>(quarter * 32) << 16), va);
+          const uint32_t t0_acc = tmem_base + colg * kColW;
+          ld_cols(t0_acc + (static_cast<uint32_t>(quarter * 32) << 16), va);
         }
 #pragma unroll 1
         for (int g = 0; g < kGroupsPerStage; ++g) {
           if (aborted) continue;
-          const uint32_t t_acc = tmem_base + g * GBN + half * 64;
+          const uint32_t t_acc = tmem_base + g * GBN + colg * kColW;
           const float2 kNegMagic2 = make_float2(-12582912.0f, -12582912.0f);
           // |partial| <= 32 * 127^2 < 2^22: adding the bit pattern of 1.5 * 2^23 converts exactly
           auto cvt2 = [&](uint32_t a, uint32_t b) {
             return __fadd2_rn(make_float2(__int_as_float(0x4B400000 + static_cast<int32_t>(a)),
                                           __int_as_float(0x4B400000 + static_cast<int32_t>(b))), kNegMagic2);
           };
-          const float* swg = sw_s + g * GBN + half * 64 + 2 * q;
+          const float* swg = sw_s + g * GBN + colg * kColW + 2 * q;
           // row scales of this thread's four rows for this group (shared memory tile [128 rows][4 groups])
           const float* sag = sa_s + (quarter * 32 + g4) * kGroupsPerStage + g;
           tc_wait_ld();                                                       // rows 0..15 of group g are in va
-          tmem_ld_16x256b_x8(t_acc + (static_cast<uint32_t>(quarter * 32 + 16) << 16), vb);
+          ld_cols(t_acc + (static_cast<uint32_t>(quarter * 32 + 16) << 16), vb);
           {
             const float saA = sag[0], saB = sag[8 * kGroupsPerStage];
 #pragma unroll
-            for (int nb = 0; nb < 8; ++nb) {
+            for (int nb = 0; nb < kNB; ++nb) {
               const float2 sw2 = *reinterpret_cast<const float2*>(swg + nb * 8);
               // same arithmetic as the CPU restatement: running sum = fma(partial, s_a * s_w, running sum)
               y[0][nb][0] = __ffma2_rn(cvt2(va[4 * nb + 0], va[4 * nb + 1]), __fmul2_rn(make_float2(saA, saA), sw2), y[0][nb][0]);
@@ -224,7 +231,7 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           }
           tc_wait_ld();                                                       // rows 16..31 of group g are in vb
           if (g + 1 < kGroupsPerStage) {
-            tmem_ld_16x256b_x8(t_acc + GBN + (static_cast<uint32_t>(quarter * 32) << 16), va);
+            ld_cols(t_acc + GBN + (static_cast<uint32_t>(quarter * 32) << 16), va);
           } else {
             tc_fence_before();                                                // all four slots are in registers:
             __syncwarp();                                                     // the MMA thread may refill them
@@ -233,7 +240,7 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           {
             const float saA = sag[16 * kGroupsPerStage], saB = sag[24 * kGroupsPerStage];
 #pragma unroll
-            for (int nb = 0; nb < 8; ++nb) {
+            for (int nb = 0; nb < kNB; ++nb) {
               const float2 sw2 = *reinterpret_cast<const float2*>(swg + nb * 8);
               y[1][nb][0] = __ffma2_rn(cvt2(vb[4 * nb + 0], vb[4 * nb + 1]), __fmul2_rn(make_float2(saA, saA), sw2), y[1][nb][0]);
               y[1][nb][1] = __ffma2_rn(cvt2(vb[4 * nb + 2], vb[4 * nb + 3]), __fmul2_rn(make_float2(saB, saB), sw2), y[1][nb][1]);
@@ -253,12 +260,12 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const int rA = row0 + quarter * 32 + mb * 16 + g4;
         const int rB = rA + 8;
 #pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
+        for (int grp = 0; grp < kColW / 32; ++grp) {
           uint32_t wA[4], wB[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int nb = grp * 4 + j;
-            const int col = n0 + half * 64 + nb * 8 + 2 * q;
+            const int col = n0 + colg * kColW + nb * 8 + 2 * q;
             float2 b2 = make_float2(0.f, 0.f);
             if (p.has_bias && col + 1 < p.N) b2 = *reinterpret_cast<const float2*>(p.bias + col);
             else if (p.has_bias && col < p.N) b2.x = p.bias[col];
@@ -266,7 +273,7 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             wA[j] = pack2(a.x, a.y, OutT{});
             wB[j] = pack2(b.x, b.y, OutT{});
           }
-          const int col_grp = n0 + half * 64 + grp * 32;
+          const int col_grp = n0 + colg * kColW + grp * 32;
           if (vec_store && col_grp + 32 <= p.N) {
             quad_transpose(wA, q);
             quad_transpose(wB, q);
