@@ -403,6 +403,117 @@ def main_ours(args):
         dist.destroy_process_group()
 
 
+def main_other(args) -> None:
+    """Secondary workloads (one GPU, one JSON line each, not the contract line): the other configurations of the path
+    measured with the same hygiene -- interleaved repetitions, CUDA events, median per item.
+
+    flux2k    FLUX double-block linear set at the 2K stage (M = 16896, four layers, rank 32 + bias)
+    sdxl_g32  SDXL 4K-stage linears, group-32 scales on both operands (six shapes, fp16)
+    routed4k  routed nested-precision FLUX MLP at the 4K stage: gather + quantise from the canvas, two-tier GEMMs
+              3072 -> 12288 -> 3072, feathered scatter back (16x16-token leaves, ~30 % active, halo 2)"""
+    import numpy as np
+    import torch.nn as nn
+    from pyraquant_b200 import int8_exec, ops, routing
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def interleaved(items, reps):
+        """items: list of (name, fn); returns {name: median microseconds} with the repetitions interleaved."""
+        for _n, fn in items:
+            fn(); fn()
+        ev = {n: [] for n, _ in items}
+        torch.cuda.synchronize()
+        for _ in range(reps):
+            for n, fn in items:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); fn(); b.record()
+                ev[n].append((a, b))
+        torch.cuda.synchronize()
+        return {n: statistics.median(a.elapsed_time(b) for a, b in v) * 1e3 for n, v in ev.items()}
+
+    def act(M, K, dtype):
+        x = torch.randn(M, K, generator=g, device=dev)
+        ch = torch.randperm(K, generator=g, device=dev)[: max(1, round(K * 0.005))]
+        x[:, ch] *= 20.0
+        return x.to(dtype)
+
+    def layer(K, N, dtype, routed=False):
+        lin = nn.Linear(K, N, bias=True, device=dev, dtype=dtype)
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(N, K, generator=g, device=dev) * 0.02)
+            lin.bias.copy_(torch.randn(N, generator=g, device=dev) * 0.01)
+        A = (torch.randn(K, RANK, generator=g, device=dev) * 0.02).to(dtype)
+        B = (torch.randn(RANK, N, generator=g, device=dev) * 0.02).to(dtype)
+        cls = int8_exec.Int8LinearRouted if routed else int8_exec.Int8Linear
+        return cls(lin, device=dev, lowrank=(A, B))
+
+    reps = max(5, args.steps)
+    out = {"workload": args.workload, "n_gpus": 1, "unit_time": "us (median of interleaved repetitions)", "reps": reps,
+           "data": "synthetic", "items": []}
+    if args.workload == "flux2k":
+        M = 16384 + 512
+        for K, N in ((3072, 9216), (3072, 3072), (3072, 12288), (12288, 3072)):
+            m = layer(K, N, torch.bfloat16)
+            x = act(M, K, torch.bfloat16)
+            xq, sx = int8_exec.quant_rows(x)
+            t = x @ m.lr_A
+            r = interleaved([("forward", lambda: m(x)), ("quant", lambda: int8_exec.quant_rows(x)),
+                             ("gemm", lambda: int8_exec.int8_gemm_lr(xq, sx, m.weight_int8, m.w_scale, m.bias, t, m.lr_B,
+                                                                     torch.bfloat16, m._lr_Bt()))], reps)
+            opsn = 2.0 * M * K * N
+            out["items"].append({"layer": f"{K}->{N}", "rows": M, "forward_us": r["forward"], "forward_tops": opsn / r["forward"] / 1e6,
+                                 "gemm_us": r["gemm"], "gemm_tops": opsn / r["gemm"] / 1e6, "quant_us": r["quant"],
+                                 "quant_gbs": (3.0 * M * K + 4 * M) / r["quant"] / 1e3})
+            del m, x, xq, sx, t
+    elif args.workload == "sdxl_g32":
+        for M, K, N in ((65536, 640, 640), (65536, 640, 5120), (65536, 2560, 640), (16384, 1280, 1280), (16384, 1280, 10240),
+                        (16384, 5120, 1280)):
+            lin = nn.Linear(K, N, bias=True, device=dev, dtype=torch.float16)
+            with torch.no_grad():
+                lin.weight.copy_(torch.randn(N, K, generator=g, device=dev) * 0.02)
+            m = int8_exec.Int8LinearG32(lin, device=dev)
+            x = torch.randn(M, K, generator=g, device=dev).to(torch.float16)
+            r = interleaved([("forward", lambda: m(x)), ("quant", lambda: int8_exec.quant_rows_g32(x))], reps)
+            opsn = 2.0 * M * K * N
+            out["items"].append({"layer": f"{K}->{N}", "rows": M, "forward_us": r["forward"], "forward_tops": opsn / r["forward"] / 1e6,
+                                 "quant_g32_us": r["quant"], "quant_g32_gbs": (3.0 * M * K + 4.0 * M * K / 32) / r["quant"] / 1e3,
+                                 "gemm_g32_us": r["forward"] - r["quant"],
+                                 "gemm_g32_tops": opsn / max(r["forward"] - r["quant"], 1e-3) / 1e6})
+            del m, x, lin
+    else:
+        H = W = 256
+        C, F = 3072, 12288
+        rng = np.random.default_rng(4)
+        sel = (rng.random((16, 16)) < 0.3).astype(np.float32)
+        hi = routing.inner_split_median(rng.random((16, 16)), sel, 1.0)
+        plan = routing.build_route_plan((H, W), routing.leaf_run_boxes(sel, 32), 2,
+                                        token_tier_hi=routing.leaf_tier_to_token_map(hi, (H, W)))
+        d = plan.to(dev)
+        M, mh = plan.n_rows, plan.m_hi
+        canvas = act(H * W, C, torch.bfloat16)
+        up, down = layer(C, F, torch.bfloat16, routed=True), layer(F, C, torch.bfloat16, routed=True)
+        hmid = up.forward_gathered(canvas, d["row_idx"], mh)
+        y = down.forward_rows(hmid, mh)
+        r = interleaved([("gather_quant", lambda: routing.gather_quant_rows(canvas, plan)),
+                         ("up", lambda: up.forward_gathered(canvas, d["row_idx"], mh)),
+                         ("down", lambda: down.forward_rows(hmid, mh)),
+                         ("scatter", lambda: routing.scatter_rows_(y, plan, canvas))], reps)
+        nt, nnz = int(plan.tokens.shape[0]), int(plan.src.shape[0])
+        out.update({"rows_gathered": M, "rows_hi": mh, "touched_tokens": nt, "canvas": [H * W, C]})
+        out["items"] = [
+            {"item": "gather+quantise", "us": r["gather_quant"], "gbs": (3.0 * M * C + 8.0 * M) / r["gather_quant"] / 1e3},
+            {"item": f"routed Linear {C}->{F} (gather, quantise, down-projection, two-tier GEMM)", "us": r["up"],
+             "tops": 2.0 * M * C * F / r["up"] / 1e6},
+            {"item": f"routed Linear {F}->{C} (quantise, down-projection, two-tier GEMM)", "us": r["down"],
+             "tops": 2.0 * M * C * F / r["down"] / 1e6},
+            {"item": "feathered scatter", "us": r["scatter"], "gbs": 2.0 * C * (nnz + 2 * nt) / r["scatter"] / 1e3}]
+    ops.check_device_status(dev)
+    out["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "int8_proxy_tops": 2.0 * float(peaks["bf16_sustained"]), "source": peaks["source"]}
+    print(json.dumps(out))
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -416,9 +527,14 @@ if __name__ == "__main__":
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-ceiling", action="store_true", help="skip the tensor-pipe issue-loop ceiling measurement")
+    ap.add_argument("--workload", choices=("flux4k", "flux2k", "sdxl_g32", "routed4k"), default="flux4k",
+                    help="flux4k (default) is the benchmark contract; the others print one JSON line of per-item "
+                         "measurements for the remaining configurations of the path (one GPU)")
     args = ap.parse_args()
     M_TOTAL = int(args.rows)
-    if args.impl == "reference":
+    if args.workload != "flux4k":
+        main_other(args)
+    elif args.impl == "reference":
         main_reference(args)
     else:
         main_ours(args)
