@@ -45,8 +45,16 @@ struct QuantScale {
 };
 __device__ __forceinline__ QuantScale make_quant_scale(float amax) {
   QuantScale qs;
-  qs.scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
-  const float inv = __fdiv_rn(1.0f, qs.scale);
+  // absmax / 127, correctly rounded, without the generic division routine: quotient estimate with the rounded
+  // reciprocal, exact residual, one correction.  absmax is a bf16 or fp16 value (or the 1e-8 floor): the sequence
+  // was checked against the IEEE quotient for every such value on the host and is checked again for all of them
+  // on the device by the tests.
+  const float a = fmaxf(amax, 1e-8f);
+  const float r127 = 0.007874015718698502f;           // RN(1/127)
+  const float q0 = __fmul_rn(a, r127);
+  const float rem = __fmaf_rn(-q0, 127.0f, a);
+  qs.scale = __fmaf_rn(rem, r127, q0);
+  const float inv = __frcp_rn(qs.scale);               // correctly rounded reciprocal = IEEE 1 / scale
   const float lo = inv * (1.0f - 4.76837158203125e-7f), hi = inv * (1.0f + 4.76837158203125e-7f);   // 1 -+ 2^-21
   qs.inv_lo = make_float2(lo, lo);
   qs.inv_hi = make_float2(hi, hi);

@@ -54,6 +54,24 @@ def test_quant_rows_bit_exact(cuda_dev, M, K, dtype):
     assert torch.equal(q.cpu(), qo)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_quant_scales_for_every_absmax(cuda_dev, dtype):
+    """Every positive finite value of the activation type as a row's absmax: the scale equals the IEEE quotient
+    absmax / 127 bit for bit (the kernel computes it with a multiply-and-correct sequence), and so do the group scales."""
+    top = 0x7F80 if dtype == torch.bfloat16 else 0x7C00
+    bits = torch.arange(1, top, dtype=torch.int32).to(torch.int16)
+    vals = bits.view(dtype)
+    M = vals.numel()
+    x = torch.zeros(M, 32, dtype=dtype)
+    x[:, 5] = vals
+    x[::2, 17] = -vals[::2]
+    _q, s = int8_exec.quant_rows(x.to(cuda_dev))
+    want = vals.float().clamp_min(1e-8) / torch.full((M,), 127.0)
+    assert torch.equal(s.cpu(), want)
+    _q, sg = int8_exec.quant_rows_g32(x.to(cuda_dev))
+    assert torch.equal(sg.cpu()[:, 0], want)
+
+
 def test_quant_rows_cfg0_full(cuda_dev):
     L = oracle.make_layer(0, 4608, 3072, 8, lowrank=False, bias=False)
     q, s = int8_exec.quant_rows(L["x"].to(cuda_dev))
