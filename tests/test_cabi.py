@@ -81,6 +81,24 @@ def test_gemm_argument_checks():
     assert gemm(N=0) == 2
 
 
+def test_gemm_ex_argument_checks():
+    """The epilogue variants are refused, before anything is launched, for shapes their store path does not cover."""
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(4096)
+    p16 = (ctypes.addressof(buf) + 15) & ~15
+
+    def ex(N=64, ldo=64, epi=1, out=p16, M=8, K=64):
+        return lib.pq_int8_gemm_ex(p16, 64, p16, p16, 64, p16, None, None, 0, None, 0, None, 0, 0, out, 0, ldo, M, N, K,
+                                   epi, None, 0, None)
+
+    assert ex(M=0) == 0
+    assert ex(epi=8) == 7                            # unknown flag
+    assert ex(N=40, ldo=40) == 7                     # N % 32
+    assert ex(ldo=68) == 7                           # ldo % 8
+    assert ex(out=p16 + 4) == 7                      # out not 16-byte aligned
+    assert ex(K=40) == 3                             # the plain GEMM's checks still come first
+
+
 def test_scatter_and_gather_argument_checks():
     lib = _lib.load()
     buf = ctypes.create_string_buffer(4096)
