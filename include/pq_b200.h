@@ -167,6 +167,13 @@ int pq_int8_gemm_g32(const int8_t* xq, int64_t ldx, const float* s_a,
                      int64_t M, int64_t N, int64_t K,
                      void* workspace, size_t ws_bytes, void* stream);
 
+/* Low-tier weights at rest in 4 bits: expands packed nested-4-bit codes (pyraquant/quantizers_weight.py:182-199;
+ * the reference keeps this tier for storage/BOPs accounting only, deploy/run_flux_latency.py:16-18) to the int8
+ * operand the GEMMs read.  Byte b of row n holds element 2b in its low nibble and element 2b+1 in its high nibble,
+ * two's complement.  packed [N, K/2] row stride ldp bytes, out [N, K] row stride ldo; K % 32 == 0, ldp % 16 == 0,
+ * ldo % 16 == 0, 16-byte aligned bases.  No counterpart in the reference. */
+int pq_unpack_int4(const uint8_t* packed, int64_t ldp, int8_t* out, int64_t ldo, int64_t N, int64_t K, void* stream);
+
 /* Feathered scatter of routed rows back over the cached canvas, in place: the pull form of
  * fuse_patch_predictions (flux/routing.py:328-379).  For canvas token j with contributor list
  * e in [ptr[j], ptr[j+1]):  local = sum_e beta[e] * y[src[e], :], bsum = sum_e beta[e] (both

@@ -489,16 +489,40 @@ class Int8LinearG32(nn.Module):
         return f"in={self.in_features}, out={self.out_features}, int8 group-32 W / per-token group-32 A"
 
 
+_LO_SCRATCH: Dict[Tuple[int, int], torch.Tensor] = {}      # (device index, bytes) -> shared expansion buffer
+
+
 class Int8LinearRouted(Int8Linear):
     """Two-tier routed Linear: rows gathered from a token canvas, the first ``m_hi`` rows run against
-    the INT8 codes, the rest against the nested 4-bit grid derived from them (``nested4_codes``)."""
+    the INT8 codes, the rest against the nested 4-bit grid derived from them (``nested4_codes``).
+
+    ``pack_lo=True`` keeps the low tier at rest as packed nibbles (``weight_lo_packed`` uint8 [N, K/2], half the
+    bytes of ``weight_lo``) and expands it into a per-device scratch buffer shared by all layers of the same size
+    right before each forward (one small HBM-bound kernel): the reference's storage-only W4 tier made real."""
 
     def __init__(self, lin: nn.Linear, device: Optional[torch.device] = None,
-                 lowrank: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+                 lowrank: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, pack_lo: bool = False):
         super().__init__(lin, device=device, lowrank=lowrank)
         c4, s4 = nested4_codes(self.weight_int8, self.w_scale)
-        self.register_buffer("weight_lo", c4)
+        self.pack_lo = bool(pack_lo)
+        if self.pack_lo:
+            assert self.in_features % 32 == 0, "packed low tier needs in_features % 32 == 0"
+            self.register_buffer("weight_lo_packed", ops.pack_int4(c4))
+        else:
+            self.register_buffer("weight_lo", c4)
         self.register_buffer("w_scale_lo", s4)
+
+    def _lo_codes(self) -> torch.Tensor:
+        """The low tier as int8 [N, K]: the buffer itself, or the packed nibbles expanded into the shared scratch."""
+        if not self.pack_lo:
+            return self.weight_lo
+        p = self.weight_lo_packed
+        key = (p.device.index if p.device.index is not None else torch.cuda.current_device(), p.numel() * 2)
+        buf = _LO_SCRATCH.get(key)
+        if buf is None:
+            buf = torch.empty(p.numel() * 2, dtype=torch.int8, device=p.device)
+            _LO_SCRATCH[key] = buf
+        return ops.unpack_int4(p, buf.view(self.out_features, self.in_features))
 
     def forward_rows(self, x2: torch.Tensor, m_hi: int) -> torch.Tensor:
         """x2 [M,K] already gathered and ordered hi-tier rows first."""
@@ -507,7 +531,7 @@ class Int8LinearRouted(Int8Linear):
             t = x2.to(self.lr_A.dtype) @ self.lr_A
             lb = self.lr_B; lbt = self._lr_Bt()
         xq, sx = quant_rows(x2)
-        return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self.weight_lo, self.w_scale_lo,
+        return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self._lo_codes(), self.w_scale_lo,
                                  self.bias, t, lb, m_hi, x2.dtype, lbt)
 
     def forward_gathered(self, canvas: torch.Tensor, row_idx: torch.Tensor, m_hi: int) -> torch.Tensor:
@@ -518,7 +542,7 @@ class Int8LinearRouted(Int8Linear):
             xg = torch.ops.pq_b200.gather_rows(canvas, row_idx)
             t = xg @ self.lr_A
             lb = self.lr_B; lbt = self._lr_Bt()
-        return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self.weight_lo, self.w_scale_lo,
+        return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self._lo_codes(), self.w_scale_lo,
                                  self.bias, t, lb, m_hi, canvas.dtype, lbt)
 
 

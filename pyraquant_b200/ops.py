@@ -158,6 +158,30 @@ def _gather_rows_impl(canvas: Tensor, row_idx: Tensor) -> Tensor:
     return out
 
 
+# ------------------------------------------------------------------------------------------------ 4-bit storage
+def pack_int4(codes: Tensor) -> Tensor:
+    """int8 codes in [-8, 7], shape [N, K] with K even -> uint8 [N, K/2]: element 2b in the low nibble of byte b,
+    element 2b+1 in the high nibble (two's complement).  Plain tensor arithmetic: done once per layer, on any device."""
+    assert codes.dtype == torch.int8 and codes.dim() == 2 and codes.shape[1] % 2 == 0
+    assert int(codes.min()) >= -8 and int(codes.max()) <= 7, "codes do not fit four bits"
+    u = codes.to(torch.int16) & 0xF
+    return (u[:, 0::2] | (u[:, 1::2] << 4)).to(torch.uint8).contiguous()
+
+
+def unpack_int4(packed: Tensor, out: Optional[Tensor] = None) -> Tensor:
+    """uint8 [N, K/2] packed nibbles -> int8 [N, K] on the device (pq_unpack_int4)."""
+    assert packed.is_cuda and packed.dtype == torch.uint8 and packed.dim() == 2 and packed.is_contiguous()
+    N, K = packed.shape[0], packed.shape[1] * 2
+    assert K % 32 == 0, f"K={K} must be a multiple of 32"
+    if out is None:
+        out = torch.empty((N, K), dtype=torch.int8, device=packed.device)
+    assert out.shape == (N, K) and out.dtype == torch.int8 and out.is_contiguous() and out.device == packed.device
+    with _on_device(packed):
+        rc = _LIB().pq_unpack_int4(packed.data_ptr(), K // 2, out.data_ptr(), K, N, K, _stream(packed))
+    _lib.check(rc, f"pq_unpack_int4(N={N}, K={K})")
+    return out
+
+
 # ------------------------------------------------------------------------------------------------ GEMM
 def epilogue_supported(N: int, out_stride0: int, out_ptr: int, has_lowrank: bool, rank: int = 32) -> bool:
     """Whether pq_int8_gemm_ex takes this problem (its variants live in the CTA-pair kernel's vector stores)."""

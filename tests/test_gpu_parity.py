@@ -457,6 +457,30 @@ def test_forward_is_cuda_graph_capturable(cuda_dev):
     ops.check_device_status(cuda_dev)
 
 
+def test_packed_low_tier(cuda_dev):
+    """Four-bit storage of the low tier: pack -> device expansion returns the codes bit for bit (every nibble value
+    at every position of a byte), and the routed Linear built with packed storage gives the same output as the one
+    that keeps int8 codes."""
+    g = torch.Generator().manual_seed(12)
+    codes = torch.randint(-8, 8, (37, 96), generator=g, dtype=torch.int8)
+    codes[0, :16] = torch.arange(-8, 8, dtype=torch.int8)
+    codes[1, :32] = torch.arange(-8, 8, dtype=torch.int8).repeat_interleave(2)
+    packed = ops.pack_int4(codes)
+    assert packed.shape == (37, 48) and packed.dtype == torch.uint8
+    assert torch.equal(ops.unpack_int4(packed.to(cuda_dev)).cpu(), codes)
+    K, N, M = 512, 768, 600
+    lin = nn.Linear(K, N, bias=True).to(torch.bfloat16)
+    A = (torch.randn(K, 32, generator=g) * 0.02).to(torch.bfloat16)
+    B = (torch.randn(32, N, generator=g) * 0.02).to(torch.bfloat16)
+    plain = int8_exec.Int8LinearRouted(lin, device=cuda_dev, lowrank=(A, B))
+    small = int8_exec.Int8LinearRouted(lin, device=cuda_dev, lowrank=(A, B), pack_lo=True)
+    assert small.weight_lo_packed.numel() * 2 == plain.weight_lo.numel() and not hasattr(small, "weight_lo")
+    assert torch.equal(ops.unpack_int4(small.weight_lo_packed), plain.weight_lo)
+    x = rand_act(M, K, torch.bfloat16, 13).to(cuda_dev)
+    for m_hi in (0, 250, M):
+        assert torch.equal(small.forward_rows(x, m_hi), plain.forward_rows(x, m_hi))
+
+
 def test_dequant_epilogue_and_linear_2d(cuda_dev):
     L = oracle.make_layer(5, 300, 512, 256, lowrank=False)
     wq, ws = oracle.quant_weight(L["w"])

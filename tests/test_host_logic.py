@@ -258,3 +258,14 @@ def test_fuse_split_inputs_replaces_reference_layout():
     m = net[0].proj_out
     assert isinstance(m, int8_exec.SplitInInt8Linear) and m.in0 == 64 and m.in_features == 192 and m.out_features == 32
     assert isinstance(net[0].other, int8_exec.Int8Linear)
+
+
+def test_pack_int4_layout():
+    """Element 2b in the low nibble of byte b, element 2b+1 in the high nibble, two's complement; out-of-range codes refused."""
+    import pytest
+    from pyraquant_b200 import ops
+    c = torch.tensor([[-8, 7, 0, -1, 3, -4, 1, 2]], dtype=torch.int8)
+    p = ops.pack_int4(c)
+    assert p.tolist() == [[0x78, 0xF0, 0xC3, 0x21]]
+    with pytest.raises(AssertionError):
+        ops.pack_int4(torch.tensor([[8, 0]], dtype=torch.int8))
