@@ -408,6 +408,7 @@ def main_other(args) -> None:
     measured with the same hygiene -- interleaved repetitions, CUDA events, median per item.
 
     flux2k    FLUX double-block linear set at the 2K stage (M = 16896, four layers, rank 32 + bias)
+    sdxl_pc   SDXL 4K-stage linears as the reference deploys them: per-channel / per-token scales, fp16 (six shapes)
     sdxl_g32  SDXL 4K-stage linears, group-32 scales on both operands (six shapes, fp16)
     routed4k  routed nested-precision FLUX MLP at the 4K stage: gather + quantise from the canvas, two-tier GEMMs
               3072 -> 12288 -> 3072, feathered scatter back (16x16-token leaves, ~30 % active, halo 2)"""
@@ -467,6 +468,25 @@ def main_other(args) -> None:
                                  "gemm_us": r["gemm"], "gemm_tops": opsn / r["gemm"] / 1e6, "quant_us": r["quant"],
                                  "quant_gbs": (3.0 * M * K + 4 * M) / r["quant"] / 1e3})
             del m, x, xq, sx, t
+    elif args.workload == "sdxl_pc":
+        # the reference's SDXL deployment arm: per-channel weights, per-token activations, fp16, no low-rank branch
+        # (deploy/run_sdxl_latency.py:214-224, shapes :280)
+        for M, K, N in ((65536, 640, 640), (65536, 640, 5120), (65536, 2560, 640), (16384, 1280, 1280), (16384, 1280, 10240),
+                        (16384, 5120, 1280)):
+            lin = nn.Linear(K, N, bias=True, device=dev, dtype=torch.float16)
+            with torch.no_grad():
+                lin.weight.copy_(torch.randn(N, K, generator=g, device=dev) * 0.02)
+            m = int8_exec.Int8Linear(lin, device=dev)
+            x = torch.randn(M, K, generator=g, device=dev).to(torch.float16)
+            xq, sx = int8_exec.quant_rows(x)
+            r = interleaved([("forward", lambda: m(x)), ("quant", lambda: int8_exec.quant_rows(x)),
+                             ("gemm", lambda: int8_exec.int8_gemm_fused(xq, sx, m.weight_int8, m.w_scale, m.bias, torch.float16)),
+                             ("fp16", lambda: torch.nn.functional.linear(x, lin.weight, lin.bias))], reps)
+            opsn = 2.0 * M * K * N
+            out["items"].append({"layer": f"{K}->{N}", "rows": M, "forward_us": r["forward"], "forward_tops": opsn / r["forward"] / 1e6,
+                                 "gemm_us": r["gemm"], "gemm_tops": opsn / r["gemm"] / 1e6, "quant_us": r["quant"],
+                                 "quant_gbs": (3.0 * M * K + 4 * M) / r["quant"] / 1e3, "torch_fp16_linear_us": r["fp16"]})
+            del m, x, lin, xq, sx
     elif args.workload == "sdxl_g32":
         for M, K, N in ((65536, 640, 640), (65536, 640, 5120), (65536, 2560, 640), (16384, 1280, 1280), (16384, 1280, 10240),
                         (16384, 5120, 1280)):
@@ -527,7 +547,7 @@ if __name__ == "__main__":
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-ceiling", action="store_true", help="skip the tensor-pipe issue-loop ceiling measurement")
-    ap.add_argument("--workload", choices=("flux4k", "flux2k", "sdxl_g32", "routed4k"), default="flux4k",
+    ap.add_argument("--workload", choices=("flux4k", "flux2k", "sdxl_pc", "sdxl_g32", "routed4k"), default="flux4k",
                     help="flux4k (default) is the benchmark contract; the others print one JSON line of per-item "
                          "measurements for the remaining configurations of the path (one GPU)")
     args = ap.parse_args()
