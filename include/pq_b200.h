@@ -167,6 +167,14 @@ int pq_int8_gemm_g32(const int8_t* xq, int64_t ldx, const float* s_a,
                      int64_t M, int64_t N, int64_t K,
                      void* workspace, size_t ws_bytes, void* stream);
 
+/* Down-projection of the rank-32 branch: t[m, 0:32] = round(sum_k x[m,k] * A[k, 0:32]), fp32 accumulation on the
+ * tensor cores, result rounded to `dtype`.  Replaces `x2.to(lr_A.dtype) @ lr_A` (deploy/int8_exec.py:390), a torch
+ * matmul in the reference; same value up to fp32 summation order.  A is passed transposed: a_t [32, K] with row
+ * stride lda (K-contiguous).  x [M, K] row stride ldx, t [M, 32] row stride ldt, all in `dtype`; K % 8 == 0,
+ * ldx % 8 == 0, lda % 8 == 0, ldt % 8 == 0, 16-byte aligned bases.  workspace as for pq_int8_gemm (status word). */
+int pq_lowrank_down(const void* x, int dtype, int64_t ldx, const void* a_t, int64_t lda, void* t, int64_t ldt,
+                    int64_t M, int64_t K, void* workspace, size_t ws_bytes, void* stream);
+
 /* Low-tier weights at rest in 4 bits: expands packed nested-4-bit codes (pyraquant/quantizers_weight.py:182-199;
  * the reference keeps this tier for storage/BOPs accounting only, deploy/run_flux_latency.py:16-18) to the int8
  * operand the GEMMs read.  Byte b of row n holds element 2b in its low nibble and element 2b+1 in its high nibble,

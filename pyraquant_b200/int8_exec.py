@@ -279,6 +279,21 @@ class Int8Linear(nn.Module):
             self._lr_Bt_cache = c
         return c
 
+    def _lr_At(self) -> torch.Tensor:
+        """K-major copy of lr_A ([32, K]) for the native down-projection kernel, made once (not part of the state)."""
+        c = getattr(self, "_lr_At_cache", None)
+        if c is None or c.device != self.lr_A.device or c.dtype != self.lr_A.dtype or c.shape[1] != self.lr_A.shape[0]:
+            c = self.lr_A.t().contiguous()
+            self._lr_At_cache = c
+        return c
+
+    def _down(self, x2: torch.Tensor) -> torch.Tensor:
+        """t = x2 @ lr_A rounded to the activation dtype (reference :390): the native streaming kernel for rank 32
+        on inputs it takes as they are, torch's matmul otherwise."""
+        if self.lr_A.shape[1] == 32 and self.lr_A.dtype == x2.dtype and ops.lowrank_down_ok(x2):
+            return ops.lowrank_down(x2, self._lr_At())
+        return x2.to(self.lr_A.dtype) @ self.lr_A
+
     def _fusable_lowrank(self, x2: torch.Tensor) -> bool:
         return (self.lr_A is not None and self.lr_A.shape[1] == 32 and x2.shape[1] % 32 == 0
                 and self.lr_A.dtype == x2.dtype and self.out_features % 8 == 0)
@@ -309,7 +324,7 @@ class Int8Linear(nn.Module):
         t_ptr = None
         ldt = 0
         if lr:
-            t = x2 @ self.lr_A                                  # [M, 32], torch's bf16/fp16 GEMM as in the reference
+            t = self._down(x2)                                  # [M, 32]
             t_ptr, ldt = t.data_ptr(), t.stride(0)
         q = torch.empty((M, K), dtype=torch.int8, device=dev)
         sx = torch.empty((M,), dtype=torch.float32, device=dev)
@@ -371,7 +386,7 @@ class Int8Linear(nn.Module):
             xq, sx, T = grp.prepare(x2)
             t = grp.t_of(self, T) if lr else None
         else:
-            t = (x2 @ self.lr_A) if lr else None
+            t = self._down(x2) if lr else None
             xq, sx = quant_rows(x2)
         y2 = ops._gemm_impl(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B if lr else None, x2.dtype,
                             lb_t=self._lr_Bt() if lr else None, epilogue=epilogue,
@@ -391,7 +406,7 @@ class Int8Linear(nn.Module):
         if x2.stride(1) != 1:
             x2 = x2.contiguous()
         if self._fusable_lowrank(x2):
-            t = x2.to(self.lr_A.dtype) @ self.lr_A                 # [M, r], rounded to the activation dtype
+            t = self._down(x2)                                     # [M, r], rounded to the activation dtype
             xq, sx = quant_rows(x2)
             y = int8_gemm_lr(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B, x2.dtype, self._lr_Bt())
             return y.reshape(*shape[:-1], self.out_features)
@@ -528,7 +543,7 @@ class Int8LinearRouted(Int8Linear):
         """x2 [M,K] already gathered and ordered hi-tier rows first."""
         t = lb = lbt = None
         if self._fusable_lowrank(x2):
-            t = x2.to(self.lr_A.dtype) @ self.lr_A
+            t = self._down(x2)
             lb = self.lr_B; lbt = self._lr_Bt()
         xq, sx = quant_rows(x2)
         return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self._lo_codes(), self.w_scale_lo,
@@ -540,7 +555,7 @@ class Int8LinearRouted(Int8Linear):
         xq, sx = gather_quant_rows(canvas, row_idx)
         if self.lr_A is not None and self.lr_A.shape[1] == 32 and self.lr_A.dtype == canvas.dtype:
             xg = torch.ops.pq_b200.gather_rows(canvas, row_idx)
-            t = xg @ self.lr_A
+            t = self._down(xg)
             lb = self.lr_B; lbt = self._lr_Bt()
         return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self._lo_codes(), self.w_scale_lo,
                                  self.bias, t, lb, m_hi, canvas.dtype, lbt)

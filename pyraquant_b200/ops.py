@@ -158,6 +158,37 @@ def _gather_rows_impl(canvas: Tensor, row_idx: Tensor) -> Tensor:
     return out
 
 
+# ------------------------------------------------------------------------------------------------ low-rank down-projection
+# True: t = x @ lr_A runs on this library's streaming tcgen05 kernel; False: torch's matmul, as the reference does
+LOWRANK_DOWN_NATIVE = True
+# below this many rows the 64-row tiles do not fill the SMs evenly and torch's split-K matmul is faster (measured:
+# 66048 rows 349 -> 308 us at K = 15360, 76 -> 70 us at K = 3072; 16896 rows 66 -> 74 us, 26 -> 35 us)
+LOWRANK_DOWN_MIN_ROWS = 32768
+
+
+def lowrank_down(x2: Tensor, a_t: Tensor) -> Tensor:
+    """t [M, 32] = x2 [M, K] @ A [K, 32] with A given transposed (a_t [32, K] contiguous), fp32 accumulation, rounded to
+    the activation dtype (pq_lowrank_down)."""
+    assert x2.is_cuda and x2.dim() == 2 and x2.stride(1) == 1 and x2.dtype in _DT
+    assert a_t.dtype == x2.dtype and a_t.shape == (32, x2.shape[1]) and a_t.is_contiguous() and a_t.device == x2.device
+    M, K = x2.shape
+    t = torch.empty((M, 32), dtype=x2.dtype, device=x2.device)
+    ws = status_word(x2.device)
+    ld = x2.stride(0) if M > 1 else max(K, x2.stride(0))
+    with _on_device(x2):
+        rc = _LIB().pq_lowrank_down(x2.data_ptr(), _dt(x2.dtype), ld, a_t.data_ptr(), K, t.data_ptr(), 32, M, K,
+                                    ws.data_ptr(), ws.numel() * 4, _stream(x2))
+    _lib.check(rc, f"pq_lowrank_down(M={M}, K={K})")
+    return t
+
+
+def lowrank_down_ok(x2: Tensor) -> bool:
+    """Shapes pq_lowrank_down takes without a copy and is the faster choice for."""
+    return (LOWRANK_DOWN_NATIVE and x2.is_cuda and x2.dtype in _DT and x2.dim() == 2 and x2.stride(1) == 1
+            and x2.shape[1] % 8 == 0 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0
+            and x2.shape[0] >= LOWRANK_DOWN_MIN_ROWS)
+
+
 # ------------------------------------------------------------------------------------------------ 4-bit storage
 def pack_int4(codes: Tensor) -> Tensor:
     """int8 codes in [-8, 7], shape [N, K] with K even -> uint8 [N, K/2]: element 2b in the low nibble of byte b,

@@ -481,6 +481,29 @@ def test_packed_low_tier(cuda_dev):
         assert torch.equal(small.forward_rows(x, m_hi), plain.forward_rows(x, m_hi))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K", [(1, 64), (63, 128), (64, 200), (129, 3072), (1000, 1288), (4608, 3072)])
+def test_lowrank_down_projection(cuda_dev, M, K, dtype):
+    """t = x @ A on the streaming tensor-core kernel against the fp64 product: within one unit in the last place of
+    the output type (fp32 accumulation order differs from any reference), identical to torch's own matmul almost
+    everywhere; row tails, K tails (K % 64 != 0), strided rows."""
+    g = torch.Generator().manual_seed(M + K)
+    xp = torch.randn(M, K + 8, generator=g).to(dtype)
+    x = xp[:, :K]
+    A = (torch.randn(K, 32, generator=g) * 0.05).to(dtype)
+    xd, Ad = xp.to(cuda_dev)[:, :K], A.to(cuda_dev)                   # row stride K + 8 on the device too
+    assert xd.stride(0) == K + 8 or M == 1
+    t = ops.lowrank_down(xd, Ad.t().contiguous()).cpu()
+    ref = x.double() @ A.double()
+    ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    err = (t.double() - ref).abs()
+    mag = x.double().abs() @ A.double().abs()                        # bound of the fp32 accumulation error
+    assert bool((err <= ulp * ref.abs() * 1.01 + 1e-6 * mag).all()), err.max().item()
+    t_torch = (xd @ Ad).cpu()
+    assert (t != t_torch).float().mean().item() < 0.02
+    ops.check_device_status(cuda_dev)
+
+
 def test_dequant_epilogue_and_linear_2d(cuda_dev):
     L = oracle.make_layer(5, 300, 512, 256, lowrank=False)
     wq, ws = oracle.quant_weight(L["w"])
