@@ -504,6 +504,30 @@ def test_lowrank_down_projection(cuda_dev, M, K, dtype):
     ops.check_device_status(cuda_dev)
 
 
+def test_int8linear_uses_native_down_projection_for_many_rows(cuda_dev, monkeypatch):
+    """From 32768 rows up Int8Linear.forward takes the library's own down-projection kernel: the output matches the
+    exact dequantised math built on that kernel's t, and the kernel really is the one called."""
+    g = torch.Generator().manual_seed(3)
+    M, K, N = ops.LOWRANK_DOWN_MIN_ROWS + 100, 256, 256
+    layer = _toy_layer(cuda_dev, g, K, N, lowrank=True)
+    x = (torch.randn(M, K, generator=g)).to(torch.bfloat16)
+    calls = {"n": 0}
+    real = ops.lowrank_down
+
+    def counting(x2, a_t):
+        calls["n"] += 1
+        return real(x2, a_t)
+    monkeypatch.setattr(ops, "lowrank_down", counting)
+    xd = x.to(cuda_dev)
+    y = layer(xd).cpu()
+    assert calls["n"] == 1
+    t = real(xd, layer._lr_At()).cpu()
+    xq, sx = oracle.quant_rows(x)
+    ref = oracle.exact_dequant_f64(oracle.int_mm(xq, layer.weight_int8.cpu()), sx, layer.w_scale.cpu(), layer.bias.cpu(),
+                                   t, layer.lr_B.cpu())
+    assert max_rel_err(y, ref) <= TOL
+
+
 def test_dequant_epilogue_and_linear_2d(cuda_dev):
     L = oracle.make_layer(5, 300, 512, 256, lowrank=False)
     wq, ws = oracle.quant_weight(L["w"])
