@@ -167,12 +167,14 @@ int pq_int8_gemm_g32(const int8_t* xq, int64_t ldx, const float* s_a,
                      int64_t M, int64_t N, int64_t K,
                      void* workspace, size_t ws_bytes, void* stream);
 
-/* Down-projection of the rank-32 branch: t[m, 0:32] = round(sum_k x[m,k] * A[k, 0:32]), fp32 accumulation on the
+/* Down-projection of the rank-32 branch: t[m, 0:R] = round(sum_k x[m,k] * A[k, 0:R]), fp32 accumulation on the
  * tensor cores, result rounded to `dtype`.  Replaces `x2.to(lr_A.dtype) @ lr_A` (deploy/int8_exec.py:390), a torch
- * matmul in the reference; same value up to fp32 summation order.  A is passed transposed: a_t [32, K] with row
- * stride lda (K-contiguous).  x [M, K] row stride ldx, t [M, 32] row stride ldt, all in `dtype`; K % 8 == 0,
- * ldx % 8 == 0, lda % 8 == 0, ldt % 8 == 0, 16-byte aligned bases.  workspace as for pq_int8_gemm (status word). */
-int pq_lowrank_down(const void* x, int dtype, int64_t ldx, const void* a_t, int64_t lda, void* t, int64_t ldt,
+ * matmul in the reference; same value up to fp32 summation order.  R = 32 for one layer; 64, 96 or 128 when the
+ * factors of layers that read the same input stand side by side (x is then read once for all of them).  A is passed
+ * transposed: a_t [R, K] with row stride lda (K-contiguous).  x [M, K] row stride ldx, t [M, R] row stride ldt, all
+ * in `dtype`; K % 8 == 0, ldx % 8 == 0, lda % 8 == 0, ldt % 8 == 0, 16-byte aligned bases.  workspace as for
+ * pq_int8_gemm (status word).  PQ_ERR_UNSUPPORTED for any other R. */
+int pq_lowrank_down(const void* x, int dtype, int64_t ldx, const void* a_t, int64_t lda, int R, void* t, int64_t ldt,
                     int64_t M, int64_t K, void* workspace, size_t ws_bytes, void* stream);
 
 /* Low-tier weights at rest in 4 bits: expands packed nested-4-bit codes (pyraquant/quantizers_weight.py:182-199;

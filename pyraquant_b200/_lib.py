@@ -47,7 +47,7 @@ SIGNATURES = {
                                      c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int,
                                      c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
                                      c_void_p, c_size_t, c_void_p]),
-    "pq_lowrank_down": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64,
+    "pq_lowrank_down": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int64, c_int64,
                                 c_void_p, c_size_t, c_void_p]),
     "pq_unpack_int4": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "pq_int8_gemm_g32": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,

@@ -17,16 +17,18 @@ constexpr int LM = 64;                 // rows of x per tile (tcgen05 M = 64)
 constexpr int LKE = 64;                // elements of K per TMA box (128 bytes of a 16-bit type: one swizzle row)
 constexpr int LBOX = 2;                // boxes per operand and stage: fewer barrier operations per byte for the two
                                        // single threads that drive the ring (they are latency-bound at low SM clocks)
-constexpr int LR = kLR;                // 32 output columns
-constexpr int LSTAGES = 6;
+constexpr int kLowMaxCols = 128;       // up to four rank-32 branches side by side (layers that share their input)
 constexpr int kLowThreads = 64 + 4 * 32;
 
+template <int NC>                      // NC output columns: 32, 64, 96 or 128
 struct LowSmem {
+  static constexpr int kStages = NC <= 32 ? 6 : (NC <= 64 ? 5 : 4);
   static constexpr int kXBytes = LM * LKE * 2;       // 8 KB per box
-  static constexpr int kABytes = LR * LKE * 2;       // 4 KB per box
+  static constexpr int kABytes = NC * LKE * 2;       // 4 .. 16 KB per box
   static constexpr int kStageBytes = LBOX * (kXBytes + kABytes);
-  static constexpr int kBarOff = LSTAGES * kStageBytes;
-  static constexpr int kNumBars = 2 * LSTAGES + 4;   // full[S], empty[S], tfull[2], tempty[2]
+  static constexpr int kBarOff = kStages * kStageBytes;
+  static constexpr int kNumBars = 2 * kStages + 4;   // full[S], empty[S], tfull[2], tempty[2]
+  static constexpr int kTmemCols = NC <= 32 ? 64 : (NC <= 64 ? 128 : 256);   // two accumulators, a power of two
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kDynamic = kMiscOff + 16 + 1024;
 };
@@ -43,11 +45,12 @@ __host__ __device__ constexpr uint32_t idesc_f16_f32acc(int M, int N, bool bf16)
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 
-template <typename T>
+template <typename T, int NC>
 __global__ void __launch_bounds__(kLowThreads, 1)
 pq_lowrank_down_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmA, T* __restrict__ t,
                        int64_t ldt, int M, int K, int32_t* status) {
-  using L = LowSmem;
+  using L = LowSmem<NC>;
+  constexpr int LSTAGES = L::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -61,7 +64,7 @@ pq_lowrank_down_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
   const int lane = threadIdx.x & 31;
   const int tiles = (M + LM - 1) / LM;
   const int num_kb = (K + LBOX * LKE - 1) / (LBOX * LKE);
-  constexpr uint32_t kTmemCols = 64;                 // two accumulators of 32 columns
+  constexpr uint32_t kTmemCols = L::kTmemCols;       // two accumulators of NC columns
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmX); tma_prefetch_desc(&tmA);
@@ -112,7 +115,7 @@ pq_lowrank_down_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      constexpr uint32_t idesc = idesc_f16_f32acc(LM, LR, std::is_same<T, __nv_bfloat16>::value);
+      constexpr uint32_t idesc = idesc_f16_f32acc(LM, NC, std::is_same<T, __nv_bfloat16>::value);
       int stage = 0; uint32_t phase = 0; int it = 0; bool ok = true;
 #pragma unroll 1
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
@@ -121,7 +124,7 @@ pq_lowrank_down_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
           report_timeout(status, 2, 2); *abort_flag = 1; ok = false; break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * LR);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * NC);
 #pragma unroll 1
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!wait_or_abort(&full_bar[stage], phase, abort_flag)) {
@@ -160,20 +163,25 @@ pq_lowrank_down_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
       }
       if (aborted) continue;
       tc_fence_after();
-      uint32_t v[32];
-      tmem_ld_32x32b_x32(tmem_base + static_cast<uint32_t>(buf * LR) + (static_cast<uint32_t>(quarter * 32) << 16), v);
-      tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
       const int row = tile * LM + quarter * 16 + lane;
-      if (lane < 16 && row < M) {
-        uint32_t w[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) w[j] = pack2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), T{});
-        T* dst = t + static_cast<int64_t>(row) * ldt;
+      for (int cg = 0; cg < NC / 32; ++cg) {           // 32 columns at a time
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + static_cast<uint32_t>(buf * NC + cg * 32) + (static_cast<uint32_t>(quarter * 32) << 16), v);
+        tc_wait_ld();
+        if (cg == NC / 32 - 1) {                       // the accumulator is in registers: the MMA thread may reuse it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        }
+        if (lane < 16 && row < M) {
+          uint32_t w[16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) st_v4(dst + 8 * j, make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
+          for (int j = 0; j < 16; ++j) w[j] = pack2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), T{});
+          T* dst = t + static_cast<int64_t>(row) * ldt + cg * 32;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) st_v4(dst + 8 * j, make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
+        }
       }
     }
   }
@@ -204,25 +212,38 @@ int make_map16(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int6
   return PQ_OK;
 }
 
-template <typename T>
+template <typename T, int NC>
 int launch_low(const CUtensorMap& tmX, const CUtensorMap& tmA, void* t, int64_t ldt, int64_t M, int64_t K, int32_t* status,
                cudaStream_t st) {
-  auto kern = pq_lowrank_down_kernel<T>;
+  auto kern = pq_lowrank_down_kernel<T, NC>;
+  using LS = LowSmem<NC>;
   static bool attr_set[64] = {false};
   int dev = 0;
   PQ_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return PQ_ERR_UNSUPPORTED;
   if (!attr_set[dev]) {
-    PQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LowSmem::kDynamic));
+    PQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LS::kDynamic));
     attr_set[dev] = true;
   }
   const int64_t tiles = (M + LM - 1) / LM;
   int64_t grid = sm_count();
   if (grid > tiles) grid = tiles;
-  kern<<<static_cast<unsigned>(grid), kLowThreads, LowSmem::kDynamic, st>>>(tmX, tmA, static_cast<T*>(t), ldt,
+  kern<<<static_cast<unsigned>(grid), kLowThreads, LS::kDynamic, st>>>(tmX, tmA, static_cast<T*>(t), ldt,
                                                                            static_cast<int>(M), static_cast<int>(K), status);
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
+}
+
+template <typename T>
+int launch_low_cols(int R, const CUtensorMap& tmX, const CUtensorMap& tmA, void* t, int64_t ldt, int64_t M, int64_t K,
+                    int32_t* status, cudaStream_t st) {
+  switch (R) {
+    case 32: return launch_low<T, 32>(tmX, tmA, t, ldt, M, K, status, st);
+    case 64: return launch_low<T, 64>(tmX, tmA, t, ldt, M, K, status, st);
+    case 96: return launch_low<T, 96>(tmX, tmA, t, ldt, M, K, status, st);
+    case 128: return launch_low<T, 128>(tmX, tmA, t, ldt, M, K, status, st);
+    default: return PQ_ERR_UNSUPPORTED;
+  }
 }
 
 }  // namespace
@@ -230,9 +251,10 @@ int launch_low(const CUtensorMap& tmX, const CUtensorMap& tmA, void* t, int64_t 
 
 using namespace pq;
 
-extern "C" int pq_lowrank_down(const void* x, int dtype, int64_t ldx, const void* a_t, int64_t lda, void* t, int64_t ldt,
-                               int64_t M, int64_t K, void* workspace, size_t ws_bytes, void* stream) {
-  if (M < 0 || K <= 0 || M > 0x7fffff00LL || K > 0x7fffff00LL || ldx < K || lda < K || ldt < kLR) return PQ_ERR_SHAPE;
+extern "C" int pq_lowrank_down(const void* x, int dtype, int64_t ldx, const void* a_t, int64_t lda, int R, void* t,
+                               int64_t ldt, int64_t M, int64_t K, void* workspace, size_t ws_bytes, void* stream) {
+  if (M < 0 || K <= 0 || M > 0x7fffff00LL || K > 0x7fffff00LL || ldx < K || lda < K || R <= 0 || ldt < R) return PQ_ERR_SHAPE;
+  if (R % 32 != 0 || R > kLowMaxCols) return PQ_ERR_UNSUPPORTED;
   if (dtype != PQ_DTYPE_BF16 && dtype != PQ_DTYPE_FP16) return PQ_ERR_DTYPE;
   if (M == 0) return PQ_OK;
   if (x == nullptr || a_t == nullptr || t == nullptr) return PQ_ERR_NULL;
@@ -244,10 +266,10 @@ extern "C" int pq_lowrank_down(const void* x, int dtype, int64_t ldx, const void
   CUtensorMap tmX, tmA;
   int rc = make_map16(&tmX, x, M, K, ldx, LM, bf16);
   if (rc != PQ_OK) return rc;
-  rc = make_map16(&tmA, a_t, kLR, K, lda, kLR, bf16);
+  rc = make_map16(&tmA, a_t, R, K, lda, R, bf16);
   if (rc != PQ_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int32_t* status = static_cast<int32_t*>(workspace);
-  if (bf16) return launch_low<__nv_bfloat16>(tmX, tmA, t, ldt, M, K, status, st);
-  return launch_low<__half>(tmX, tmA, t, ldt, M, K, status, st);
+  if (bf16) return launch_low_cols<__nv_bfloat16>(R, tmX, tmA, t, ldt, M, K, status, st);
+  return launch_low_cols<__half>(R, tmX, tmA, t, ldt, M, K, status, st);
 }

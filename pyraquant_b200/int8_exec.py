@@ -170,7 +170,8 @@ class SharedInputGroup:
     quantisation and one down-projection ``x @ [A_1 | A_2 | ...]`` instead of one each.  The first member called on
     an input does both and keeps the results; the others recognise the input (same storage, shape, strides and
     version counter) and reuse them.  Results are bit-identical to the ungrouped layers except for the
-    down-projection, whose cuBLAS kernel may differ with the width (same caveat as between any two GEMM shapes).
+    down-projection, whose fp32 summation order may differ with the width (same caveat as between any two GEMM
+    shapes).
     The cache keeps the last input and its codes alive until the next input arrives or ``clear()`` is called."""
 
     def __init__(self, layers: Sequence["Int8Linear"]):
@@ -182,6 +183,7 @@ class SharedInputGroup:
         self._key = None
         self._val = None
         self._A_cat = None
+        self._A_cat_t = None
         self._A_slots: Dict[int, int] = {}
         for m in layers:
             m.__dict__["_shared_input"] = self
@@ -201,6 +203,7 @@ class SharedInputGroup:
                     off += 32
             c = torch.cat(mats, dim=1).contiguous() if mats else torch.empty((0, 0), dtype=dtype, device=device)
             self._A_cat = c
+            self._A_cat_t = c.t().contiguous() if c.numel() else None
         return c if c.numel() else None
 
     def prepare(self, x2: torch.Tensor):
@@ -208,7 +211,12 @@ class SharedInputGroup:
         key = (x2.data_ptr(), tuple(x2.shape), tuple(x2.stride()), x2.dtype, x2._version, x2.device)
         if key != self._key:
             a_cat = self._a_cat(x2.dtype, x2.device)
-            T = (x2 @ a_cat) if a_cat is not None else None
+            if a_cat is None:
+                T = None
+            elif a_cat.shape[1] in ops.LOWRANK_DOWN_COLS and ops.lowrank_down_ok(x2):
+                T = ops.lowrank_down(x2, self._A_cat_t)
+            else:
+                T = x2 @ a_cat
             xq, sx = ops._quant_rows_impl(x2)
             self._key, self._val = key, (x2, xq, sx, T)          # x2 kept so that its storage cannot be recycled
         _x, xq, sx, T = self._val

@@ -164,19 +164,23 @@ LOWRANK_DOWN_NATIVE = True
 # below this many rows the 64-row tiles do not fill the SMs evenly and torch's split-K matmul is faster (measured:
 # 66048 rows 349 -> 308 us at K = 15360, 76 -> 70 us at K = 3072; 16896 rows 66 -> 74 us, 26 -> 35 us)
 LOWRANK_DOWN_MIN_ROWS = 32768
+# output widths the kernel is built for: one rank-32 factor, or up to four side by side
+LOWRANK_DOWN_COLS = (32, 64, 96, 128)
 
 
 def lowrank_down(x2: Tensor, a_t: Tensor) -> Tensor:
-    """t [M, 32] = x2 [M, K] @ A [K, 32] with A given transposed (a_t [32, K] contiguous), fp32 accumulation, rounded to
-    the activation dtype (pq_lowrank_down)."""
+    """t [M, R] = x2 [M, K] @ A [K, R] with A given transposed (a_t [R, K] contiguous; R in LOWRANK_DOWN_COLS), fp32
+    accumulation, rounded to the activation dtype (pq_lowrank_down)."""
     assert x2.is_cuda and x2.dim() == 2 and x2.stride(1) == 1 and x2.dtype in _DT
-    assert a_t.dtype == x2.dtype and a_t.shape == (32, x2.shape[1]) and a_t.is_contiguous() and a_t.device == x2.device
+    R = a_t.shape[0]
+    assert R in LOWRANK_DOWN_COLS, f"{R} columns; supported: {LOWRANK_DOWN_COLS}"
+    assert a_t.dtype == x2.dtype and a_t.shape == (R, x2.shape[1]) and a_t.is_contiguous() and a_t.device == x2.device
     M, K = x2.shape
-    t = torch.empty((M, 32), dtype=x2.dtype, device=x2.device)
+    t = torch.empty((M, R), dtype=x2.dtype, device=x2.device)
     ws = status_word(x2.device)
     ld = x2.stride(0) if M > 1 else max(K, x2.stride(0))
     with _on_device(x2):
-        rc = _LIB().pq_lowrank_down(x2.data_ptr(), _dt(x2.dtype), ld, a_t.data_ptr(), K, t.data_ptr(), 32, M, K,
+        rc = _LIB().pq_lowrank_down(x2.data_ptr(), _dt(x2.dtype), ld, a_t.data_ptr(), K, R, t.data_ptr(), R, M, K,
                                     ws.data_ptr(), ws.numel() * 4, _stream(x2))
     _lib.check(rc, f"pq_lowrank_down(M={M}, K={K})")
     return t

@@ -482,15 +482,17 @@ def test_packed_low_tier(cuda_dev):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("M,K", [(1, 64), (63, 128), (64, 200), (129, 3072), (1000, 1288), (4608, 3072)])
-def test_lowrank_down_projection(cuda_dev, M, K, dtype):
+@pytest.mark.parametrize("M,K,R", [(1, 64, 32), (63, 128, 32), (64, 200, 32), (129, 3072, 32), (1000, 1288, 32),
+                                   (4608, 3072, 32), (65, 200, 64), (1000, 1288, 96), (129, 3072, 128),
+                                   (9500, 3072, 128), (9500, 512, 64)])
+def test_lowrank_down_projection(cuda_dev, M, K, R, dtype):
     """t = x @ A on the streaming tensor-core kernel against the fp64 product: within one unit in the last place of
     the output type (fp32 accumulation order differs from any reference), identical to torch's own matmul almost
-    everywhere; row tails, K tails (K % 64 != 0), strided rows."""
-    g = torch.Generator().manual_seed(M + K)
+    everywhere; row tails, K tails (K % 64 != 0), strided rows, one to four rank-32 factors side by side."""
+    g = torch.Generator().manual_seed(M + K + R)
     xp = torch.randn(M, K + 8, generator=g).to(dtype)
     x = xp[:, :K]
-    A = (torch.randn(K, 32, generator=g) * 0.05).to(dtype)
+    A = (torch.randn(K, R, generator=g) * 0.05).to(dtype)
     xd, Ad = xp.to(cuda_dev)[:, :K], A.to(cuda_dev)                   # row stride K + 8 on the device too
     assert xd.stride(0) == K + 8 or M == 1
     t = ops.lowrank_down(xd, Ad.t().contiguous()).cpu()
@@ -501,6 +503,37 @@ def test_lowrank_down_projection(cuda_dev, M, K, dtype):
     assert bool((err <= ulp * ref.abs() * 1.01 + 1e-6 * mag).all()), err.max().item()
     t_torch = (xd @ Ad).cpu()
     assert (t != t_torch).float().mean().item() < 0.02
+    ops.check_device_status(cuda_dev)
+
+
+def test_shared_input_group_uses_native_down_projection_for_many_rows(cuda_dev, monkeypatch):
+    """A group of layers on one input takes ONE native down-projection of width 32 x members from 32768 rows up, and
+    every member's output equals the ungrouped layer's wherever the two down-projections agree (they differ in fp32
+    summation order only)."""
+    from pyraquant_b200.int8_exec import share_input_quantisation
+    g = torch.Generator().manual_seed(11)
+    M, K = ops.LOWRANK_DOWN_MIN_ROWS + 37, 256
+    grouped = [_toy_layer(cuda_dev, g, K, n, lowrank=True) for n in (256, 512, 256)]
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(cuda_dev)
+    alone = [m(x) for m in grouped]                                  # before grouping: one kernel call each
+    t_alone = [m._down(x) for m in grouped]
+    calls = []
+    real = ops.lowrank_down
+
+    def counting(x2, a_t):
+        calls.append(tuple(a_t.shape))
+        return real(x2, a_t)
+
+    monkeypatch.setattr(ops, "lowrank_down", counting)
+    grp = share_input_quantisation(grouped)
+    outs = [m(x) for m in grouped]
+    assert calls == [(96, K)], calls
+    _, _, T = grp.prepare(x)
+    for i, m in enumerate(grouped):
+        same_t = (grp.t_of(m, T) == t_alone[i]).all(dim=1)
+        assert same_t.float().mean().item() > 0.9
+        assert torch.equal(outs[i][same_t], alone[i][same_t])
+        assert (outs[i].float() - alone[i].float()).abs().max().item() <= 0.02 * alone[i].float().abs().max().item()
     ops.check_device_status(cuda_dev)
 
 
