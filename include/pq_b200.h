@@ -53,6 +53,8 @@ int pq_last_cuda_error(void);
  *   "gemm_block_n"      column tile of the single-CTA kernels (128 or 256);
  *   "gemm_pm","gemm_pn" shape of the CTA grid of the tile schedule;
  *   "gemm_max_ctas"     upper bound of CTAs (or CTA pairs x 2) launched;
+ *   "gemm_epi_warps"    epilogue warps per CTA of the CTA-pair kernel: 0 = automatic (16 up to K = 1536 without a low-rank
+ *                       term, where the epilogue outlasts the K loop; else 8), 8 or 16;
  *   "gemm_pair"         0 = never use the CTA-pair kernel, 1 = automatic (default), 2 = whenever it is legal;
  *   "gemm_debug_timing" 1 = the CTA-pair kernel writes per-role cycle counters to workspace + 256
  *                       (needs ws_bytes >= 256 + 4096*64).

@@ -42,6 +42,7 @@ struct Options {
   int gemm_pn = 0;         // tile schedule override: CTA grid columns (0 = auto)
   int gemm_max_ctas = 0;   // 0 = one per SM
   int gemm_debug_timing = 0;   // experiments: cycle counters into workspace + 256 (CTA-pair kernel)
+  int gemm_epi_warps = 0;  // epilogue warps of the CTA-pair kernel: 0 automatic (16 up to K = 1536 without low-rank term, else 8), 8 or 16
   int gemm_pair = 1;       // CTA-pair (cta_group::2) kernel: 0 off, 1 when the problem is large enough, 2 whenever it applies
 };
 Options& options();

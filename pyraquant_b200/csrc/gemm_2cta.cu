@@ -29,8 +29,11 @@ constexpr int kRowBytesLr = kLR * 2;       // 64-byte rows of the t / lbT tiles
 constexpr int kLrChunks = 2;               // the low-rank term is added in column chunks of PBN / kLrChunks
 constexpr int kLrChunkN = PBN / kLrChunks; // 128 columns: one kind::f16 MMA pair per chunk
 constexpr int kLbChunkRows = kLrChunkN / 2;   // lbT rows each CTA stages per chunk
-constexpr int kLrWarp = 2 + kNumEpiWarps;  // warp that issues the low-rank MMAs (leader CTA)
-constexpr int kPairThreads = (kLrWarp + 1) * 32;
+// Warps of a CTA: 0 TMA producer, 1 MMA issuer, 2 .. 2 + EW - 1 epilogue, 2 + EW issuer of the low-rank MMAs (leader
+// CTA).  EW = 8 when the main loop of a tile outlasts its epilogue (long K); EW = 16 for short K without a low-rank
+// term, where the epilogue is the critical path: each warp then owns 16 rows x 128 columns instead of 32 x 128.
+constexpr int pair_threads(int ew) { return (3 + ew) * 32; }
+constexpr int kShortK = 1536;              // up to this K (and without a low-rank term) the sixteen-warp epilogue is used
 
 struct PairSmem {
   static constexpr int kABytes = BM * BK;
@@ -165,12 +168,17 @@ __device__ __forceinline__ PairCoord pair_coord(int mt, int mt0, const GemmParam
   return c;
 }
 
-template <typename OutT, bool HAS_LR, bool DBG>
-__global__ void __launch_bounds__(kPairThreads, 1)
+template <int EW>
+__device__ __forceinline__ void pair_epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory"); }
+
+template <typename OutT, bool HAS_LR, bool DBG, int EW>
+__global__ void __launch_bounds__(pair_threads(EW), 1)
 pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                                const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmT, const __grid_constant__ CUtensorMap tmLbT,
                                const GemmParams p) {
   using L = PairSmem;
+  static_assert(EW == 8 || EW == 16, "eight or sixteen epilogue warps");
+  constexpr int kLrWarp = 2 + EW;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* empty_bar = full_bar + PSTAGES;
@@ -203,10 +211,10 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     if (HAS_LR) { tma_prefetch_desc(&tmT); tma_prefetch_desc(&tmLbT); }
     for (int s = 0; s < PSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 2 * kNumEpiWarps);
+      mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 2 * EW);
       mbar_init(&t_full[b], 1);
       for (int c = 0; c < kLrChunks; ++c) {
-        mbar_init(&ylr_ready[b * kLrChunks + c], 2 * kNumEpiWarps); mbar_init(&lr_done[b * kLrChunks + c], 1);
+        mbar_init(&ylr_ready[b * kLrChunks + c], 2 * EW); mbar_init(&lr_done[b * kLrChunks + c], 1);
       }
     }
     mbar_init(&lb_full[0], 1); mbar_init(&lb_full[1], 1);
@@ -378,10 +386,13 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       if (!ok) *abort_flag = 1;
       if (p.timing) { p.timing[blockIdx.x * 16 + 8] = tm_det[0]; p.timing[blockIdx.x * 16 + 9] = tm_det[1]; }
     }
-  } else if (run && warp >= 2 && warp < 2 + kNumEpiWarps) {
-    // ------------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
+  } else if (run && warp >= 2 && warp < 2 + EW) {
+    // ------------------------------------------------------------------ epilogue (warps 2 .. 2 + EW - 1 of both CTAs)
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = ((warp - 2) >> 2) & 1;
+    // sixteen warps: warps 2..9 take the first 16 rows of each 32-row lane quarter, warps 10..17 the other 16
+    constexpr int MBN = EW == 16 ? 1 : 2;                // 16-row blocks per warp
+    const int mb_base = EW == 16 ? ((warp - 2) >> 3) : 0;
     const int etid = threadIdx.x - 64;
     const int g = lane >> 2, q = lane & 3;
     constexpr int UNIT_N = 64;
@@ -397,8 +408,8 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     float srow_next[2][2];
     auto load_srow = [&](const PairCoord& pc, float (&dst)[2][2]) {
 #pragma unroll
-      for (int mb = 0; mb < 2; ++mb) {
-        const int rA = pc.row0 + quarter * 32 + mb * 16 + g;
+      for (int mb = 0; mb < MBN; ++mb) {
+        const int rA = pc.row0 + quarter * 32 + (mb_base + mb) * 16 + g;
         dst[mb][0] = rA < pc.row_end ? p.s_row[rA] : 0.0f;
         dst[mb][1] = rA + 8 < pc.row_end ? p.s_row[rA + 8] : 0.0f;
       }
@@ -418,20 +429,20 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         aux_n0 = n0; aux_set = c.set;
         const float* scol_g = p.s_col[0];
         if (c.set != 0) scol_g = p.s_col[1];
-        epi_bar_sync();
+        pair_epi_bar_sync<EW>();
 #pragma unroll 1
-        for (int i = etid; i < PBN; i += kNumEpiWarps * 32) {
+        for (int i = etid; i < PBN; i += EW * 32) {
           const int col = n0 + i;
           scol_s[i] = col < p.N ? scol_g[col] : 0.0f;
           bias_s[i] = (p.has_bias && col < p.N) ? p.bias[col] : 0.0f;
         }
-        epi_bar_sync();
+        pair_epi_bar_sync<EW>();
       }
       // row scales of this tile: fetched while the previous tile was being stored (first tile: here)
       float srow[2][2];
       if (it == 0) load_srow(c, srow_next);
 #pragma unroll
-      for (int mb = 0; mb < 2; ++mb) { srow[mb][0] = srow_next[mb][0]; srow[mb][1] = srow_next[mb][1]; }
+      for (int mb = 0; mb < MBN; ++mb) { srow[mb][0] = srow_next[mb][0]; srow[mb][1] = srow_next[mb][1]; }
 
       const long long e1 = p.timing ? clock64() : 0;
       if (!aborted) {
@@ -452,7 +463,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       // columns, those of half 1 the other 64, so that one low-rank MMA pair per chunk serves all sixteen warps.
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(buf * PBN + half * UNIT_N);
       auto unit_addr = [&](int ch, int mb) {
-        return t_acc + (static_cast<uint32_t>(quarter * 32 + mb * 16) << 16) + static_cast<uint32_t>(ch * kLrChunkN);
+        return t_acc + (static_cast<uint32_t>(quarter * 32 + (mb_base + mb) * 16) << 16) + static_cast<uint32_t>(ch * kLrChunkN);
       };
       uint32_t va[32], vb[32];
 
@@ -465,7 +476,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           const int cl = col_unit + nb * 8 + 2 * q;
           const float2 sc = *reinterpret_cast<const float2*>(scol_s + cl);
           if constexpr (DBG) {
-            const int rA = row0 + quarter * 32 + mb * 16 + g;
+            const int rA = row0 + quarter * 32 + (mb_base + mb) * 16 + g;
             dump_acc_pair(p.dbg_acc, p.N, rA, rA + 8, n0 + cl, row_end, v[4 * nb + 0], v[4 * nb + 1], v[4 * nb + 2], v[4 * nb + 3]);
           }
           const float2 yA = __fmul2_rn(int2_to_float2_rn(static_cast<int32_t>(v[4 * nb + 0]), static_cast<int32_t>(v[4 * nb + 1])),
@@ -479,7 +490,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       // + bias, round, transpose inside quads, store one 16 x 64 block of fp32 values
       auto store_unit = [&](const uint32_t (&v)[32], int ch, int mb) {
         const int col_unit = ch * kLrChunkN + half * UNIT_N;
-        const int rA = row0 + quarter * 32 + mb * 16 + g;
+        const int rA = row0 + quarter * 32 + (mb_base + mb) * 16 + g;
         const int rB = rA + 8;
 #pragma unroll
         for (int grp = 0; grp < 2; ++grp) {
@@ -539,18 +550,25 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
 #pragma unroll 1
         for (int ch = 0; ch < kLrChunks; ++ch) {
           tc_wait_ld();
-          tmem_ld_16x256b_x8(unit_addr(ch, 1), vb);
-          scale_unit(va, ch, 0);
-          tmem_st_x8(unit_addr(ch, 0), va);
-          tc_wait_ld();
-          scale_unit(vb, ch, 1);
-          tmem_st_x8(unit_addr(ch, 1), vb);
-          wait_st();
-          if (ch + 1 < kLrChunks) tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+          if constexpr (EW == 16) {                       // one 16-row block per warp and chunk; the other warps overlap
+            scale_unit(va, ch, 0);
+            tmem_st_x8(unit_addr(ch, 0), va);
+            wait_st();
+            if (ch + 1 < kLrChunks) tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+          } else {
+            tmem_ld_16x256b_x8(unit_addr(ch, 1), vb);
+            scale_unit(va, ch, 0);
+            tmem_st_x8(unit_addr(ch, 0), va);
+            tc_wait_ld();
+            scale_unit(vb, ch, 1);
+            tmem_st_x8(unit_addr(ch, 1), vb);
+            wait_st();
+            if (ch + 1 < kLrChunks) tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+          }
           tc_fence_before();
           __syncwarp();
           if (p.timing && warp == 2 && lane == 0) stamp[buf * kLrChunks + ch] = clock64();
-          if (trace && it < 1000 && ch == 0 && lane == 0) trace[it * 24 + rank * 8 + (warp - 2)] = static_cast<long long>(global_timer_ns());
+          if (trace && it < 1000 && ch == 0 && lane == 0 && warp < 10) trace[it * 24 + rank * 8 + (warp - 2)] = static_cast<long long>(global_timer_ns());
           if (lane == 0) mbar_arrive_cluster(leader_addr(&ylr_ready[buf * kLrChunks + ch]));
         }
         if (p.timing) e3 = clock64();
@@ -572,16 +590,25 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
 #pragma unroll 1
       for (int ch = 0; ch < kLrChunks; ++ch) {
         tc_wait_ld();
-        tmem_ld_16x256b_x8(unit_addr(ch, 1), vb);
-        if constexpr (!HAS_LR) scale_unit(va, ch, 0);
-        store_unit(va, ch, 0);
-        tc_wait_ld();
-        if (ch + 1 < kLrChunks) {
-          if (!chunk_ready(ch + 1)) { aborted = true; break; }
-          tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+        if constexpr (EW == 16) {                         // one 16-row block per warp and chunk; the other warps overlap
+          if constexpr (!HAS_LR) scale_unit(va, ch, 0);
+          store_unit(va, ch, 0);
+          if (ch + 1 < kLrChunks) {
+            if (!chunk_ready(ch + 1)) { aborted = true; break; }
+            tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+          }
+        } else {
+          tmem_ld_16x256b_x8(unit_addr(ch, 1), vb);
+          if constexpr (!HAS_LR) scale_unit(va, ch, 0);
+          store_unit(va, ch, 0);
+          tc_wait_ld();
+          if (ch + 1 < kLrChunks) {
+            if (!chunk_ready(ch + 1)) { aborted = true; break; }
+            tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
+          }
+          if constexpr (!HAS_LR) scale_unit(vb, ch, 1);
+          store_unit(vb, ch, 1);
         }
-        if constexpr (!HAS_LR) scale_unit(vb, ch, 1);
-        store_unit(vb, ch, 1);
       }
       if (aborted) continue;
       e4 = e3 + lr_wait;
@@ -609,10 +636,10 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   }
 }
 
-template <typename OutT, bool HAS_LR, bool DBG>
-int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmW1, const CUtensorMap& tmT,
+template <typename OutT, bool HAS_LR, bool DBG, int EW>
+int launch_pair_ew(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmW1, const CUtensorMap& tmT,
                 const CUtensorMap& tmLbT, GemmParams p, int mt_pairs, int ntl, cudaStream_t st) {
-  auto kern = pq_int8_gemm_fused_pair_kernel<OutT, HAS_LR, DBG>;
+  auto kern = pq_int8_gemm_fused_pair_kernel<OutT, HAS_LR, DBG, EW>;
   static int max_pairs[64] = {0};
   int dev = 0;
   PQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -621,7 +648,7 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMa
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(kPairThreads, 1, 1);
+  cfg.blockDim = dim3(pair_threads(EW), 1, 1);
   cfg.dynamicSmemBytes = PairSmem::kTotal;
   cfg.stream = st;
   cfg.attrs = attr; cfg.numAttrs = 1;
@@ -640,6 +667,17 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMa
   cfg.gridDim = dim3(2 * p.sched_pm * p.sched_pn, 1, 1);
   PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmW1, tmT, tmLbT, p));
   return PQ_OK;
+}
+
+// Sixteen epilogue warps when the K loop of a tile is shorter than its epilogue and there is no low-rank term (measured:
+// 5-12 % faster there, slower with the two-pass low-rank epilogue); option gemm_epi_warps overrides (0 = this rule).
+template <typename OutT, bool HAS_LR, bool DBG>
+int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmW1, const CUtensorMap& tmT,
+                const CUtensorMap& tmLbT, GemmParams p, int mt_pairs, int ntl, cudaStream_t st) {
+  const int want = options().gemm_epi_warps;
+  const bool wide = want == 16 || (want != 8 && !HAS_LR && p.K <= kShortK);
+  if (wide) return launch_pair_ew<OutT, HAS_LR, DBG, 16>(tmA, tmW, tmW1, tmT, tmLbT, p, mt_pairs, ntl, st);
+  return launch_pair_ew<OutT, HAS_LR, DBG, 8>(tmA, tmW, tmW1, tmT, tmLbT, p, mt_pairs, ntl, st);
 }
 
 int make_lr_map64(CUtensorMap* map, const void* base, int64_t rows, int64_t ld, int box_rows, bool bf16) {

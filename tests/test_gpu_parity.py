@@ -227,17 +227,19 @@ def test_gemm_schedule_grids(cuda_dev, pm, pn):
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (128, 256, 256), (300, 512, 192), (1000, 768, 640), (2049, 1288, 384),
                                    (4608, 3072, 3072)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_gemm_cta_pair_kernel(cuda_dev, M, N, K, dtype):
+@pytest.mark.parametrize("ew", [8, 16])
+def test_gemm_cta_pair_kernel(cuda_dev, M, N, K, dtype, ew):
     """The cta_group::2 kernel forced on for every shape it accepts: odd numbers of 128-row tiles (one CTA of the
-    last pair has no rows), ragged N, several tiles per pair, with and without the low-rank term."""
-    _lib.set_option("gemm_pair", 2)
+    last pair has no rows), ragged N, several tiles per pair, with and without the low-rank term; both epilogue
+    widths (eight warps: long K; sixteen warps: short K) at every shape."""
+    _lib.set_option("gemm_pair", 2); _lib.set_option("gemm_epi_warps", ew)
     try:
         run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=True, dtype=dtype, seed=M + N)
         run_gemm_case(cuda_dev, M, N, K, lowrank=False, bias=True, dtype=dtype, seed=M + N + 1)
         _lib.set_option("gemm_max_ctas", 4)          # two pairs only: long per-pair tile sequences
         run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=False, dtype=dtype, seed=M + N + 2)
     finally:
-        _lib.set_option("gemm_pair", 1); _lib.set_option("gemm_max_ctas", 0)
+        _lib.set_option("gemm_pair", 1); _lib.set_option("gemm_max_ctas", 0); _lib.set_option("gemm_epi_warps", 0)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -253,13 +255,13 @@ def test_gemm_production_kernels_bit_equal_without_lowrank(cuda_dev, dtype):
     b = torch.randn(N, generator=g) * 0.01
     y32 = oracle.epilogue(oracle.int_mm(xq, wq), sr, sc, b, None, None, dtype)
     d = cuda_dev
-    for pair, bn in ((0, 256), (0, 128), (2, 0)):
-        _lib.set_option("gemm_pair", pair); _lib.set_option("gemm_block_n", bn)
+    for pair, bn, ew in ((0, 256, 0), (0, 128, 0), (2, 0, 8), (2, 0, 16)):
+        _lib.set_option("gemm_pair", pair); _lib.set_option("gemm_block_n", bn); _lib.set_option("gemm_epi_warps", ew)
         try:
             y = int8_exec.int8_gemm_fused(xq.to(d), sr.to(d), wq.to(d), sc.to(d), b.to(d), dtype)
         finally:
-            _lib.set_option("gemm_pair", 1); _lib.set_option("gemm_block_n", 0)
-        assert torch.equal(y.cpu(), y32), (pair, bn)
+            _lib.set_option("gemm_pair", 1); _lib.set_option("gemm_block_n", 0); _lib.set_option("gemm_epi_warps", 0)
+        assert torch.equal(y.cpu(), y32), (pair, bn, ew)
 
 
 def test_gemm_cfg0_layer(cuda_dev):
