@@ -310,13 +310,15 @@ __device__ __forceinline__ float int_to_float_rn(int32_t v) {
   return fmaf(fh, 2048.0f, fl);
 }
 
-// Two at once on the packed fp32 pipe (identical results).
+// Two at once on the packed fp32 pipe (identical results), with one operation less per value: the high part is placed
+// at its final weight by the exponent of the constant (1.5 * 2^34 has a unit in the last place of 2^11, so adding
+// v >> 11 to its bit pattern adds (v >> 11) * 2048 to its value), the low part keeps its 2^23 offset, and the first
+// addition removes both offsets at once: d = (v >> 11) * 2048 - 2^23 exactly, d + (2^23 + lo) = v rounded once.
 __device__ __forceinline__ float2 int2_to_float2_rn(int32_t a, int32_t b) {
-  const float2 fh = __fadd2_rn(make_float2(__int_as_float(0x4B400000 + (a >> 11)), __int_as_float(0x4B400000 + (b >> 11))),
-                               make_float2(-12582912.0f, -12582912.0f));
-  const float2 fl = __fadd2_rn(make_float2(__int_as_float(0x4B000000 | (a & 0x7FF)), __int_as_float(0x4B000000 | (b & 0x7FF))),
-                               make_float2(-8388608.0f, -8388608.0f));
-  return __ffma2_rn(fh, make_float2(2048.0f, 2048.0f), fl);
+  constexpr float kOffsets = 25778192384.0f;                                           // 1.5 * 2^34 + 2^23
+  const float2 d = __fadd2_rn(make_float2(__int_as_float(0x50C00000 + (a >> 11)), __int_as_float(0x50C00000 + (b >> 11))),
+                              make_float2(-kOffsets, -kOffsets));
+  return __fadd2_rn(d, make_float2(__int_as_float(0x4B000000 | (a & 0x7FF)), __int_as_float(0x4B000000 | (b & 0x7FF))));
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -264,6 +264,30 @@ def test_gemm_production_kernels_bit_equal_without_lowrank(cuda_dev, dtype):
         assert torch.equal(y.cpu(), y32), (pair, bn, ew)
 
 
+@pytest.mark.parametrize("pair", [0, 2])
+def test_gemm_accumulators_beyond_24_bits_round_like_the_restatement(cuda_dev, pair):
+    """Same-sign codes and K = 8192 give accumulators of 2^24 .. 2^27 with arbitrary low bits: the int32 -> fp32
+    conversion of the epilogue has to round them to nearest-even exactly like the fp32 restatement.  Scales of 1 and
+    no bias, fp16 and bf16 outputs of power-of-two-scaled sums expose the conversion's rounding at output ties."""
+    g = torch.Generator().manual_seed(5)
+    M, N, K = 512, 512, 8192
+    xq = torch.randint(0, 128, (M, K), generator=g, dtype=torch.int8)
+    wq = torch.randint(0, 128, (N, K), generator=g, dtype=torch.int8)
+    wq[::2] = -wq[::2]
+    acc = oracle.int_mm(xq, wq)
+    assert int(acc.abs().max()) > 2 ** 24
+    d = cuda_dev
+    _lib.set_option("gemm_pair", pair)
+    try:
+        for dtype, sr_v in ((torch.bfloat16, 1.0), (torch.float16, 2.0 ** -12), (torch.bfloat16, 2.0 ** -7)):
+            sr = torch.full((M,), sr_v); sc = torch.ones(N)
+            want = oracle.epilogue(acc, sr, sc, None, None, None, dtype)
+            got = int8_exec.int8_gemm_fused(xq.to(d), sr.to(d), wq.to(d), sc.to(d), None, dtype)
+            assert torch.equal(got.cpu(), want), (pair, dtype)
+    finally:
+        _lib.set_option("gemm_pair", 1)
+
+
 def test_gemm_cfg0_layer(cuda_dev):
     """BASELINE config 0: M=4608, K=N=3072, rank-32 branch and bias, through Int8Linear.forward."""
     L = oracle.make_layer(0, 4608, 3072, 3072)
