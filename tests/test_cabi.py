@@ -44,6 +44,19 @@ def test_options_roundtrip():
         _lib.set_option("no_such_knob", 1)
 
 
+def test_documented_options_exist():
+    """Every knob the header documents is accepted by pq_set_option and starts at 0 or its documented default."""
+    header = (ROOT / "include" / "pq_b200.h").read_text()
+    block = header[header.index("Internal tuning / test knobs"):header.index("int pq_set_option")]
+    names = re.findall(r'"([a-z0-9_]+)"', block)
+    assert {"quant_tpr", "gemm_stages", "gemm_block_n", "gemm_pm", "gemm_pn", "gemm_max_ctas", "gemm_epi_warps",
+            "gemm_pair", "gemm_debug_timing"} <= set(names)
+    for n in names:
+        v = _lib.get_option(n)
+        _lib.set_option(n, v)
+        assert _lib.get_option(n) == v
+
+
 def test_quant_rows_argument_checks():
     lib = _lib.load()
     buf = ctypes.create_string_buffer(4096)
