@@ -316,8 +316,12 @@ __device__ __forceinline__ float int_to_float_rn(int32_t v) {
 // addition removes both offsets at once: d = (v >> 11) * 2048 - 2^23 exactly, d + (2^23 + lo) = v rounded once.
 __device__ __forceinline__ float2 int2_to_float2_rn(int32_t a, int32_t b) {
   constexpr float kOffsets = 25778192384.0f;                                           // 1.5 * 2^34 + 2^23
-  const float2 d = __fadd2_rn(make_float2(__int_as_float(0x50C00000 + (a >> 11)), __int_as_float(0x50C00000 + (b >> 11))),
-                              make_float2(-kOffsets, -kOffsets));
+  // (v >> 11) + constant as one multiply-high-add: it issues on the multiply pipe, which the epilogues leave idle,
+  // instead of a shift and an addition on the integer pipe, which they saturate
+  int32_t ha, hb;
+  asm("mad.hi.s32 %0, %1, %2, %3;" : "=r"(ha) : "r"(a), "r"(1 << 21), "r"(0x50C00000));
+  asm("mad.hi.s32 %0, %1, %2, %3;" : "=r"(hb) : "r"(b), "r"(1 << 21), "r"(0x50C00000));
+  const float2 d = __fadd2_rn(make_float2(__int_as_float(ha), __int_as_float(hb)), make_float2(-kOffsets, -kOffsets));
   return __fadd2_rn(d, make_float2(__int_as_float(0x4B000000 | (a & 0x7FF)), __int_as_float(0x4B000000 | (b & 0x7FF))));
 }
 
