@@ -55,6 +55,7 @@ int pq_last_cuda_error(void);
  *   "gemm_max_ctas"     upper bound of CTAs (or CTA pairs x 2) launched;
  *   "gemm_epi_warps"    epilogue warps per CTA of the CTA-pair kernel: 0 = automatic (16 up to K = 1536 without a low-rank
  *                       term, where the epilogue outlasts the K loop; else 8), 8 or 16;
+ *   "gemm_tma_store"    1 (default) = sixteen-warp tiles of plain calls store through shared memory + TMA, 0 = never;
  *   "gemm_pair"         0 = never use the CTA-pair kernel, 1 = automatic (default), 2 = whenever it is legal;
  *   "gemm_debug_timing" 1 = the CTA-pair kernel writes per-role cycle counters to workspace + 256
  *                       (needs ws_bytes >= 256 + 4096*64).

@@ -60,6 +60,7 @@ int* option_slot(const char* key) {
   if (std::strcmp(key, "gemm_max_ctas") == 0) return &o.gemm_max_ctas;
   if (std::strcmp(key, "gemm_pair") == 0) return &o.gemm_pair;
   if (std::strcmp(key, "gemm_epi_warps") == 0) return &o.gemm_epi_warps;
+  if (std::strcmp(key, "gemm_tma_store") == 0) return &o.gemm_tma_store;
   if (std::strcmp(key, "gemm_debug_timing") == 0) return &o.gemm_debug_timing;
   return nullptr;
 }

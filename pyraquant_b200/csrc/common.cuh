@@ -43,6 +43,7 @@ struct Options {
   int gemm_max_ctas = 0;   // 0 = one per SM
   int gemm_debug_timing = 0;   // experiments: cycle counters into workspace + 256 (CTA-pair kernel)
   int gemm_epi_warps = 0;  // epilogue warps of the CTA-pair kernel: 0 automatic (16 up to K = 1536 without low-rank term, else 8), 8 or 16
+  int gemm_tma_store = 1;  // sixteen-warp pair tiles store through shared memory + TMA (0: register stores)
   int gemm_pair = 1;       // CTA-pair (cta_group::2) kernel: 0 off, 1 when the problem is large enough, 2 whenever it applies
 };
 Options& options();
@@ -72,6 +73,18 @@ __device__ __forceinline__ uint4 ld_v4(const void* p) {
 }
 __device__ __forceinline__ void st_v2(void* p, uint32_t a, uint32_t b) {
   asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+// TMA tile store (shared memory -> global) and its bulk-group bookkeeping; all three by the one issuing thread
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
+               "r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_src))), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_u32(void* p, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(p))), "r"(v) : "memory");
 }
 __device__ __forceinline__ void st_v4(void* p, uint4 v) {
   asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)

@@ -175,7 +175,7 @@ template <typename OutT, bool HAS_LR, bool DBG, int EW>
 __global__ void __launch_bounds__(pair_threads(EW), 1)
 pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                                const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmT, const __grid_constant__ CUtensorMap tmLbT,
-                               const GemmParams p) {
+                               const __grid_constant__ CUtensorMap tmOut, const GemmParams p) {
   using L = PairSmem;
   static_assert(EW == 8 || EW == 16, "eight or sixteen epilogue warps");
   constexpr int kLrWarp = 2 + EW;
@@ -542,6 +542,34 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         }
       };
 
+      // Sixteen-warp tiles without low-rank term are bound by the integer pipe and the global-store path: the rounded
+      // 16 x 64 block goes to shared memory in the 128-byte-swizzled layout (conflict-free: the eight rows of a store
+      // land in eight different 16-byte columns) and one TMA store writes it; no in-quad transposes, no row
+      // predicates (TMA clips at M and N).  The staging buffers are the t / lbT tiles this variant does not use.
+      auto stage_unit = [&](const uint32_t (&v)[32], int ch) {
+        const int col_unit = ch * kLrChunkN + half * UNIT_N;
+        uint8_t* sbuf = smem + L::kTOff + (warp - 2) * 2048;
+        if (lane == 0) bulk_wait_group_read0();            // the previous store of this warp has read the buffer
+        __syncwarp();
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+          const float2 bi = *reinterpret_cast<const float2*>(bias_s + col_unit + nb * 8 + 2 * q);
+          uint32_t wA = pack2(__fadd_rn(__uint_as_float(v[4 * nb + 0]), bi.x), __fadd_rn(__uint_as_float(v[4 * nb + 1]), bi.y), OutT{});
+          uint32_t wB = pack2(__fadd_rn(__uint_as_float(v[4 * nb + 2]), bi.x), __fadd_rn(__uint_as_float(v[4 * nb + 3]), bi.y), OutT{});
+          if (p.epi_flags & PQ_EPI_GELU_TANH) { wA = gelu_word<OutT>(wA); wB = gelu_word<OutT>(wB); }
+          uint8_t* dst = sbuf + g * 128 + ((nb ^ g) << 4) + q * 4;
+          st_shared_u32(dst, wA);
+          st_shared_u32(dst + 8 * 128, wB);                // row g + 8: same swizzle phase
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        const int r_first = row0 + quarter * 32 + mb_base * 16;
+        if (lane == 0 && r_first < row_end && n0 + col_unit < p.N) {
+          tma_store_2d(&tmOut, sbuf, n0 + col_unit, r_first);
+          bulk_commit_group();
+        }
+      };
+
       long long lr_wait = 0;
       if constexpr (HAS_LR) {
         // pass 1, chunk by chunk: scaled accumulator back to tensor memory; the MMA thread adds t @ lb on top of a
@@ -592,7 +620,11 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         tc_wait_ld();
         if constexpr (EW == 16) {                         // one 16-row block per warp and chunk; the other warps overlap
           if constexpr (!HAS_LR) scale_unit(va, ch, 0);
-          store_unit(va, ch, 0);
+          bool staged = false;
+          if constexpr (!HAS_LR) {
+            if (p.tma_store) { stage_unit(va, ch); staged = true; }
+          }
+          if (!staged) store_unit(va, ch, 0);
           if (ch + 1 < kLrChunks) {
             if (!chunk_ready(ch + 1)) { aborted = true; break; }
             tmem_ld_16x256b_x8(unit_addr(ch + 1, 0), va);
@@ -617,6 +649,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       if (lane == 0) mbar_arrive_cluster(leader_addr(&tempty_bar[buf]));
       if (p.timing) { te_aux += e1 - e0; te_tfull += e2 - e1; te_p1 += e3 - e2; te_lr += e4 - e3; te_p2 += clock64() - e4; }
     }
+    if (EW == 16 && !HAS_LR && p.tma_store && lane == 0) bulk_wait_group0();   // stores done before shared memory goes
     if (p.timing && warp == 2 && lane == 0) {
       p.timing[blockIdx.x * 16 + 2] = te_aux; p.timing[blockIdx.x * 16 + 3] = te_tfull; p.timing[blockIdx.x * 16 + 4] = te_p1;
       p.timing[blockIdx.x * 16 + 5] = te_lr; p.timing[blockIdx.x * 16 + 6] = te_p2; p.timing[blockIdx.x * 16 + 7] = it;
@@ -636,9 +669,33 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   }
 }
 
+// Output [M, N] of 16-bit elements, row stride ldo: boxes of 64 columns x 16 rows, 128-byte swizzle (TMA store).
+int make_out_map16(CUtensorMap* map, void* base, int64_t M, int64_t N, int64_t ldo, bool bf16) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return PQ_ERR_CUDA;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldo) * 2};
+  cuuint32_t box[2] = {64, 16};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { g_last_cuda_error = static_cast<int>(r); return PQ_ERR_CUDA; }
+  return PQ_OK;
+}
+
 template <typename OutT, bool HAS_LR, bool DBG, int EW>
 int launch_pair_ew(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmW1, const CUtensorMap& tmT,
                 const CUtensorMap& tmLbT, GemmParams p, int mt_pairs, int ntl, cudaStream_t st) {
+  // sixteen-warp tiles of a plain single-tier call store through shared memory + TMA when the output allows it
+  CUtensorMap tmOut = tmA;
+  p.tma_store = 0;
+  if (EW == 16 && !HAS_LR && p.m_split == p.M && !(p.epi_flags & PQ_EPI_ACCUMULATE) && options().gemm_tma_store != 0 &&
+      p.ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+    const int rc = make_out_map16(&tmOut, p.out, p.M, p.N, p.ldo, std::is_same<OutT, __nv_bfloat16>::value);
+    if (rc != PQ_OK) return rc;
+    p.tma_store = 1;
+  }
   auto kern = pq_int8_gemm_fused_pair_kernel<OutT, HAS_LR, DBG, EW>;
   static int max_pairs[64] = {0};
   int dev = 0;
@@ -665,7 +722,7 @@ int launch_pair_ew(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtenso
   if (pairs_cap < 1) pairs_cap = 1;
   choose_cta_grid(mt_pairs, ntl, pairs_cap, &p.sched_pm, &p.sched_pn);
   cfg.gridDim = dim3(2 * p.sched_pm * p.sched_pn, 1, 1);
-  PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmW1, tmT, tmLbT, p));
+  PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmW1, tmT, tmLbT, tmOut, p));
   return PQ_OK;
 }
 

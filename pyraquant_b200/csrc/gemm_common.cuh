@@ -24,6 +24,7 @@ struct GemmParams {
   int sched_n_rounds;       // ceil(column tiles / sched_pn)
   int has_bias;
   int epi_flags;            // PQ_EPI_* bits (CTA-pair kernel only)
+  int tma_store;            // CTA-pair kernel, sixteen epilogue warps: output tiles leave through shared memory + TMA
   long long* timing;        // experiments: per-CTA cycle counters [grid][8] (NULL in normal use)
 };
 

@@ -236,10 +236,16 @@ def test_gemm_cta_pair_kernel(cuda_dev, M, N, K, dtype, ew):
     try:
         run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=True, dtype=dtype, seed=M + N)
         run_gemm_case(cuda_dev, M, N, K, lowrank=False, bias=True, dtype=dtype, seed=M + N + 1)
+        if ew == 16:                                 # the same tiles stored from registers instead of shared memory + TMA
+            _lib.set_option("gemm_tma_store", 0)
+            run_gemm_case(cuda_dev, M, N, K, lowrank=False, bias=True, dtype=dtype, seed=M + N + 1)
+            _lib.set_option("gemm_tma_store", 1)
         _lib.set_option("gemm_max_ctas", 4)          # two pairs only: long per-pair tile sequences
         run_gemm_case(cuda_dev, M, N, K, lowrank=True, bias=False, dtype=dtype, seed=M + N + 2)
+        run_gemm_case(cuda_dev, M, N, K, lowrank=False, bias=False, dtype=dtype, seed=M + N + 3)
     finally:
         _lib.set_option("gemm_pair", 1); _lib.set_option("gemm_max_ctas", 0); _lib.set_option("gemm_epi_warps", 0)
+        _lib.set_option("gemm_tma_store", 1)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
