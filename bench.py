@@ -385,7 +385,9 @@ def main_ours(args):
                      "ops_per_launch": [2.0 * rows * K * N for _n, K, N in LAYERS]},
         "kernels": kern,
         "clocks": clocks,
-        "gpu_launches": 3 * len(LAYERS) * args.steps,      # down-projection, quantisation and GEMM kernels of this library
+        # this library's kernels per step and layer: quantisation, GEMM and, from ops.LOWRANK_DOWN_MIN_ROWS rows per
+        # rank up, the down-projection (below that it is torch's matmul, as in the reference, and not counted)
+        "gpu_launches": sum(2 + (1 if ops.lowrank_down_ok(x) else 0) for x in xs) * args.steps,
     }
     if e2e is not None:
         line["e2e"] = e2e
