@@ -44,19 +44,26 @@ def leaf_run_boxes(selected: np.ndarray, leaf_latent: int) -> List[Box]:
 
 
 def latent_box_to_token_box(box: Sequence[int], packing_offset_latent: int = 0) -> Box:
-    """2x2-packed token coordinates of a latent box (flux/routing.py:202-232), same error rules."""
-    vals = tuple(int(v) for v in box)
-    if any(v < 0 for v in vals):
-        raise ValueError(f"Negative route coordinate: {vals}")
-    if any(v % 2 for v in vals):
-        raise ValueError(f"Route coordinates must align to FLUX 2x2 packing: {vals}")
+    """Token box covering a latent box under FLUX's 2x2 packing: a latent row/column v belongs to token
+    (v + offset) // 2, so a half-open latent span [a, b) maps to tokens [(a + offset) // 2, (b + offset + 1) // 2)
+    (the mapping of flux/routing.py:202-232).  Rejected with ValueError: an offset other than 0 or 1, negative or odd
+    coordinates, spans without area."""
     off = int(packing_offset_latent)
-    if off not in (0, 1):
-        raise ValueError(f"Packing offset must be 0 or 1, got {off}")
-    y0, y1, x0, x1 = vals
-    if y1 <= y0 or x1 <= x0:
-        raise ValueError(f"Empty route box: {vals}")
-    return ((y0 + off) // 2, (y1 + off + 1) // 2, (x0 + off) // 2, (x1 + off + 1) // 2)
+    if off != 0 and off != 1:
+        raise ValueError(f"packing_offset_latent is 0 or 1 (got {packing_offset_latent!r})")
+    y0, y1, x0, x1 = (int(v) for v in box)
+    problem = None
+    if min(y0, y1, x0, x1) < 0:
+        problem = "negative coordinate"
+    elif (y0 | y1 | x0 | x1) & 1:
+        problem = "coordinates must be even (2x2 packing)"
+    elif y1 <= y0 or x1 <= x0:
+        problem = "no area"
+    if problem is not None:
+        raise ValueError(f"route box {(y0, y1, x0, x1)}: {problem}")
+    first = lambda v: (v + off) >> 1
+    end = lambda v: (v + off + 1) >> 1
+    return (first(y0), end(y1), first(x0), end(x1))
 
 
 def expand_box(box: Box, halo_tokens: int, token_hw: Tuple[int, int]) -> Box:
@@ -65,39 +72,45 @@ def expand_box(box: Box, halo_tokens: int, token_hw: Tuple[int, int]) -> Box:
     return (max(0, y0 - h), min(int(token_hw[0]), y1 + h), max(0, x0 - h), min(int(token_hw[1]), x1 + h))
 
 
-def _ramp(values: torch.Tensor, mode: str, power: float) -> torch.Tensor:
-    out = values.clamp(0.0, 1.0)
-    if mode in ("cosine", "hann", "raised_cosine"):
-        out = 0.5 - 0.5 * torch.cos(torch.pi * out)
-    elif mode in ("smoothstep", "cubic"):
-        out = out * out * (3.0 - 2.0 * out)
-    elif mode not in ("linear", "lin"):
-        raise ValueError(f"Unsupported feather ramp mode: {mode}")
-    if float(power) != 1.0:
-        out = out.pow(max(float(power), 1e-6))
-    return out.clamp(0.0, 1.0)
+# Halo profiles: u runs over [0, 1] across the halo (0 at the patch border, 1 where the core begins).
+_RAMP_SHAPES = {
+    "cosine": lambda u: 0.5 - 0.5 * torch.cos(torch.pi * u),
+    "smoothstep": lambda u: u * u * (3.0 - 2.0 * u),
+    "linear": lambda u: u,
+}
+
+
+def _axis_profile(length: int, core_lo: int, core_hi: int, shape, power: float) -> torch.Tensor:
+    """fp32 blend weights along one axis of a patch: 1 on [core_lo, core_hi), the halo profile on either side.  A halo
+    of h tokens samples the profile at h evenly spaced points including both ends, so its outermost token weighs 0."""
+    core_lo = min(max(core_lo, 0), length)
+    core_hi = min(max(core_hi, core_lo), length)
+    w = torch.ones(length, dtype=torch.float32)
+    for sl, u0, u1 in ((slice(0, core_lo), 0.0, 1.0), (slice(core_hi, length), 1.0, 0.0)):
+        n = sl.stop - sl.start
+        if n <= 0:
+            continue
+        v = shape(torch.linspace(u0, u1, n).clamp_(0.0, 1.0))
+        if power != 1.0:
+            v = v.pow(max(power, 1e-6))
+        w[sl] = v.clamp_(0.0, 1.0)
+    return w
 
 
 def feather_weights(patch_hw: Tuple[int, int], inner: Box, dtype: torch.dtype, fusion_beta: float = 1.0,
                     mode: str = "cosine", power: float = 1.0) -> torch.Tensor:
-    """[H,W] blend weights of one patch: 1 in the core, ramping to 0 across the halo, evaluated in fp32
-    and rounded to `dtype`, then scaled by fusion_beta in `dtype` (flux/routing.py:34-75 and :361-370)."""
-    H, W = int(patch_hw[0]), int(patch_hw[1])
-    iy0, iy1, ix0, ix1 = (int(v) for v in inner)
-    iy0, iy1 = max(0, min(iy0, H)), max(iy0, min(iy1, H))
-    ix0, ix1 = max(0, min(ix0, W)), max(ix0, min(ix1, W))
-    wy = torch.ones(H, dtype=torch.float32)
-    wx = torch.ones(W, dtype=torch.float32)
-    if iy0 > 0:
-        wy[:iy0] = _ramp(torch.linspace(0.0, 1.0, iy0), mode, power)
-    if iy1 < H:
-        wy[iy1:] = _ramp(torch.linspace(1.0, 0.0, H - iy1), mode, power)
-    if ix0 > 0:
-        wx[:ix0] = _ramp(torch.linspace(0.0, 1.0, ix0), mode, power)
-    if ix1 < W:
-        wx[ix1:] = _ramp(torch.linspace(1.0, 0.0, W - ix1), mode, power)
-    mask = torch.minimum(wy[:, None], wx[None, :]).clamp(0.0, 1.0).to(dtype)
-    return (float(fusion_beta) * mask).clamp(0.0, 1.0)
+    """[H, W] blend weights of one patch = min(row profile, column profile), evaluated in fp32, rounded to `dtype`
+    and then scaled by fusion_beta in `dtype`: the values of flux/routing.py:34-75 and :361-370 (the tests compare
+    them with masks produced by the reference).  ``mode``: "cosine" (the reference's default), "smoothstep" or
+    "linear"; ``power`` sharpens (> 1) or softens (< 1) the profile."""
+    try:
+        shape = _RAMP_SHAPES[mode]
+    except KeyError:
+        raise ValueError(f"feather mode {mode!r}; known: {sorted(_RAMP_SHAPES)}") from None
+    rows = _axis_profile(int(patch_hw[0]), int(inner[0]), int(inner[1]), shape, float(power))
+    cols = _axis_profile(int(patch_hw[1]), int(inner[2]), int(inner[3]), shape, float(power))
+    mask = torch.minimum(rows[:, None], cols[None, :]).to(dtype)
+    return (float(fusion_beta) * mask).clamp_(0.0, 1.0)
 
 
 @dataclass

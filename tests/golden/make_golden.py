@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this directory by RUNNING the reference's own CPU-runnable code.
 
-    python tests/golden/make_golden.py /path/to/PyraQuant
+    python tests/golden/make_golden.py /path/to/PyraQuant [feather]
 
 Only works where the reference checkout is available (the build container); the fixtures it writes
 (small .npz files) are committed and are what the tests read.  Inputs are seeded; bf16 tensors are
@@ -19,6 +19,28 @@ HERE = Path(__file__).resolve().parent
 
 def bf16_bits(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.int16).numpy().copy()
+
+
+FEATHER_CASES = [  # (patch_hw, inner box in the patch, mode, power)
+    ((12, 12), (2, 10, 2, 10), "cosine", 1.0), ((20, 36), (2, 18, 2, 34), "cosine", 1.0),
+    ((11, 19), (3, 11, 3, 16), "cosine", 1.0), ((9, 9), (1, 8, 1, 8), "cosine", 1.0),
+    ((26, 14), (5, 21, 0, 9), "cosine", 1.0), ((16, 16), (4, 12, 4, 12), "cosine", 2.0),
+    ((16, 16), (4, 12, 4, 12), "smoothstep", 1.0), ((13, 17), (3, 10, 6, 11), "linear", 0.5),
+]
+
+
+def feather_fixture(ref_root: str) -> None:
+    """halo_feather_mask (flux/routing.py:34-75) for a few patch geometries, profile shapes and powers, in bf16
+    and fp16."""
+    sys.path.insert(0, str(Path(ref_root) / "flux"))
+    import routing as ref_routing
+    save = {"n": np.int64(len(FEATHER_CASES))}
+    for i, (hw, inner, mode, power) in enumerate(FEATHER_CASES):
+        for tag, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
+            m = ref_routing.halo_feather_mask(hw, inner, device=torch.device("cpu"), dtype=dt, mode=mode, power=power)
+            save[f"mask{i}_{tag}_bits"] = m.contiguous().view(torch.int16).numpy().copy()
+    np.savez(HERE / "feather_masks.npz", **save)
+    print("feather_masks.npz written")
 
 
 def main(ref_root: str) -> None:
@@ -121,6 +143,10 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/PyraQuant")
-    main(sys.argv[1])
+    if len(sys.argv) == 3 and sys.argv[2] == "feather":
+        feather_fixture(sys.argv[1])                                # only feather_masks.npz
+    elif len(sys.argv) == 2:
+        main(sys.argv[1])
+        feather_fixture(sys.argv[1])
+    else:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/PyraQuant [feather]")

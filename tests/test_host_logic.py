@@ -52,6 +52,25 @@ def test_feather_weights_halo2_is_zero_one():
     assert w[0].abs().max() == 0 and w[1, 1] == 1 and w[5, 5] == 1     # outer ring 0, inner ring 1
 
 
+def test_feather_weights_match_reference_masks(golden):
+    """Blend weights against masks made by the reference's halo_feather_mask (halo widths 1-6, clipped halos, all three
+    profile shapes, powers 0.5/1/2, bf16 and fp16): bit-equal."""
+    import sys
+    sys.path.insert(0, str(__import__("pathlib").Path(__file__).parent / "golden"))
+    from make_golden import FEATHER_CASES
+    g = golden("feather_masks.npz")
+    assert int(g["n"]) == len(FEATHER_CASES)
+    for i, (hw, inner, mode, power) in enumerate(FEATHER_CASES):
+        for tag, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
+            want = torch.from_numpy(g[f"mask{i}_{tag}_bits"]).view(dt)
+            got = routing.feather_weights(hw, inner, dt, 1.0, mode, power)
+            assert torch.equal(got, want), (i, tag)
+            if mode == "cosine" and power == 1.0:
+                assert torch.equal(oracle.feather_mask(hw, inner, dt), want), (i, tag)
+    with pytest.raises(ValueError):
+        routing.feather_weights((4, 4), (1, 3, 1, 3), torch.bfloat16, mode="gaussian")
+
+
 def test_plan_gather_matches_reference_buckets(golden):
     g = golden("routing_gather_scatter.npz")
     boxes = [tuple(b) for b in g["boxes"].tolist()]
