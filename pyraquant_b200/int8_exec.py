@@ -168,8 +168,10 @@ class SharedInputGroup:
     """Sibling ``Int8Linear`` layers that are called one after the other on the SAME input tensor (FLUX: to_q / to_k /
     to_v, add_*_proj, and proj_mlp next to the attention projections of a single-stream block) share one per-token
     quantisation and one down-projection ``x @ [A_1 | A_2 | ...]`` instead of one each.  The first member called on
-    an input does both and keeps the results; the others recognise the input (same storage, shape, strides and
-    version counter) and reuse them.  Results are bit-identical to the ungrouped layers except for the
+    an input does both and keeps the results; the others recognise the input (same storage, shape, strides,
+    version counter and CUDA stream) and reuse them.  Inference tensors keep no version counter, so under
+    ``torch.inference_mode()`` the members run ungrouped.  The library's own in-place writes (the accumulate epilogue,
+    the 4-bit expansion) bump the version of what they write, as torch's in-place operators do.  Results are bit-identical to the ungrouped layers except for the
     down-projection, whose fp32 summation order may differ with the width (same caveat as between any two GEMM
     shapes).
     The cache keeps the last input and its codes alive until the next input arrives or ``clear()`` is called."""
@@ -208,7 +210,7 @@ class SharedInputGroup:
 
     def prepare(self, x2: torch.Tensor):
         """(codes, row scales, T) for x2; T [M, 32 * members with a rank-32 branch] or None."""
-        key = (x2.data_ptr(), tuple(x2.shape), tuple(x2.stride()), x2.dtype, x2._version, x2.device)
+        key = (x2.data_ptr(), tuple(x2.shape), tuple(x2.stride()), x2.dtype, x2._version, x2.device, ops._stream(x2))
         if key != self._key:
             a_cat = self._a_cat(x2.dtype, x2.device)
             if a_cat is None:
@@ -281,19 +283,22 @@ class Int8Linear(nn.Module):
 
     def _lr_Bt(self) -> torch.Tensor:
         """K-major copy of lr_B for the tensor-core low-rank path, made once per device/dtype (not part of the state)."""
-        c = getattr(self, "_lr_Bt_cache", None)
-        if c is None or c.device != self.lr_B.device or c.dtype != self.lr_B.dtype or c.shape[0] != self.lr_B.shape[1]:
-            c = self.lr_B.t().contiguous()
-            self._lr_Bt_cache = c
-        return c
+        return self._transposed("lr_B")
 
     def _lr_At(self) -> torch.Tensor:
         """K-major copy of lr_A ([32, K]) for the native down-projection kernel, made once (not part of the state)."""
-        c = getattr(self, "_lr_At_cache", None)
-        if c is None or c.device != self.lr_A.device or c.dtype != self.lr_A.dtype or c.shape[1] != self.lr_A.shape[0]:
-            c = self.lr_A.t().contiguous()
-            self._lr_At_cache = c
-        return c
+        return self._transposed("lr_A")
+
+    def _transposed(self, name: str) -> torch.Tensor:
+        """Contiguous transpose of a low-rank factor, remade whenever the buffer is replaced, converted (.to / .half),
+        moved or written in place."""
+        src = getattr(self, name)
+        key = (src.data_ptr(), src.dtype, src.device, tuple(src.shape), ops.tensor_version(src))
+        c = self.__dict__.get("_t_cache_" + name)
+        if c is None or c[0] != key:
+            c = (key, src.t().contiguous())
+            self.__dict__["_t_cache_" + name] = c
+        return c[1]
 
     def _down(self, x2: torch.Tensor) -> torch.Tensor:
         """t = x2 @ lr_A rounded to the activation dtype (reference :390): the native streaming kernel for rank 32
@@ -304,7 +309,7 @@ class Int8Linear(nn.Module):
 
     def _fusable_lowrank(self, x2: torch.Tensor) -> bool:
         return (self.lr_A is not None and self.lr_A.shape[1] == 32 and x2.shape[1] % 32 == 0
-                and self.lr_A.dtype == x2.dtype and self.out_features % 8 == 0)
+                and self.lr_A.dtype == x2.dtype and self.lr_B.dtype == x2.dtype and self.out_features % 8 == 0)
 
     def _lean_forward(self, x2: torch.Tensor):
         """Eager fast path for the common case (aligned rows, rank-32 branch or none): the two C-ABI calls are made
@@ -319,9 +324,16 @@ class Int8Linear(nn.Module):
             return None
         c = self.__dict__.get("_lean_cache")
         wptr = self.weight_int8.data_ptr()
-        if c is None or c[0] != wptr or c[1] != x2.dtype:
-            lbt = self._lr_Bt() if lr else None
-            c = (wptr, x2.dtype, self.weight_int8.stride(0), self.w_scale.data_ptr(),
+        # every buffer whose address is cached takes part in the key: .to(dtype) / .half() / load_state_dict(assign=True)
+        # replace the float buffers while the int8 weight stays where it is
+        lbt = self._lr_Bt() if lr else None
+        key = (wptr, x2.dtype, self.w_scale.data_ptr(), self.bias.data_ptr() if self.bias is not None else 0,
+               self.lr_B.data_ptr() if lr else 0, lbt.data_ptr() if lr else 0)
+        if c is None or c[0] != key:
+            assert self.w_scale.dtype == torch.float32 and (self.bias is None or self.bias.dtype == torch.float32), \
+                "w_scale and bias are fp32 buffers"
+            assert self.w_scale.numel() == self.out_features and (self.bias is None or self.bias.numel() == self.out_features)
+            c = (key, x2.dtype, self.weight_int8.stride(0), self.w_scale.data_ptr(),
                  self.bias.data_ptr() if self.bias is not None else None,
                  self.lr_B.data_ptr() if lr else None, self.lr_B.stride(0) if lr else 0,
                  lbt.data_ptr() if lr else None, ops._DT[x2.dtype], ops._LIB(), ops.status_word(x2.device))
@@ -353,7 +365,7 @@ class Int8Linear(nn.Module):
         grp = self.__dict__.get("_shared_input")
         M, K = x2.shape
         if (grp is None or M == 0 or not x2.is_cuda or x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16
-                or K % 32 or x2.dtype not in ops._DT or torch.compiler.is_compiling()):
+                or K % 32 or x2.dtype not in ops._DT or torch.compiler.is_compiling() or x2.is_inference()):
             return None
         if self.lr_A is not None and not self._fusable_lowrank(x2):
             return None
@@ -390,7 +402,8 @@ class Int8Linear(nn.Module):
                 return out
             return y
         grp = self.__dict__.get("_shared_input")
-        if grp is not None and x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0 and K % 32 == 0:
+        if (grp is not None and x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0 and K % 32 == 0
+                and not x2.is_inference()):
             xq, sx, T = grp.prepare(x2)
             t = grp.t_of(self, T) if lr else None
         else:
@@ -512,7 +525,7 @@ class Int8LinearG32(nn.Module):
         return f"in={self.in_features}, out={self.out_features}, int8 group-32 W / per-token group-32 A"
 
 
-_LO_SCRATCH: Dict[Tuple[int, int], torch.Tensor] = {}      # (device index, bytes) -> shared expansion buffer
+_LO_SCRATCH: Dict[Tuple[int, int, int], torch.Tensor] = {}      # (device index, stream, bytes) -> expansion buffer
 
 
 class Int8LinearRouted(Int8Linear):
@@ -520,8 +533,14 @@ class Int8LinearRouted(Int8Linear):
     the INT8 codes, the rest against the nested 4-bit grid derived from them (``nested4_codes``).
 
     ``pack_lo=True`` keeps the low tier at rest as packed nibbles (``weight_lo_packed`` uint8 [N, K/2], half the
-    bytes of ``weight_lo``) and expands it into a per-device scratch buffer shared by all layers of the same size
-    right before each forward (one small HBM-bound kernel): the reference's storage-only W4 tier made real."""
+    bytes of ``weight_lo``) and expands it right before each forward (one small HBM-bound kernel) into a scratch
+    buffer that all layers of the same size share: the reference's storage-only W4 tier made real.  The buffer is
+    refilled by every forward and read by the GEMM that follows on the same stream, so there is one per CUDA stream:
+    layers running on different streams never see each other's weights.
+
+    A low-rank branch the fused epilogue does not take (rank other than 32, factors in another dtype than the
+    activations, in_features not a multiple of 32) is added after the GEMM as ``(x @ lr_A) @ lr_B``, the way
+    ``Int8Linear.forward`` does."""
 
     def __init__(self, lin: nn.Linear, device: Optional[torch.device] = None,
                  lowrank: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, pack_lo: bool = False):
@@ -536,37 +555,39 @@ class Int8LinearRouted(Int8Linear):
         self.register_buffer("w_scale_lo", s4)
 
     def _lo_codes(self) -> torch.Tensor:
-        """The low tier as int8 [N, K]: the buffer itself, or the packed nibbles expanded into the shared scratch."""
+        """The low tier as int8 [N, K]: the buffer itself, or the packed nibbles expanded into this stream's scratch."""
         if not self.pack_lo:
             return self.weight_lo
         p = self.weight_lo_packed
-        key = (p.device.index if p.device.index is not None else torch.cuda.current_device(), p.numel() * 2)
+        key = (p.device.index if p.device.index is not None else torch.cuda.current_device(), ops._stream(p), p.numel() * 2)
         buf = _LO_SCRATCH.get(key)
         if buf is None:
             buf = torch.empty(p.numel() * 2, dtype=torch.int8, device=p.device)
             _LO_SCRATCH[key] = buf
         return ops.unpack_int4(p, buf.view(self.out_features, self.in_features))
 
+    def _two_tier(self, xq, sx, x_rows: Callable[[], torch.Tensor], m_hi: int, dtype: torch.dtype, fused: bool):
+        t = lb = lbt = None
+        if fused:
+            t = self._down(x_rows())
+            lb = self.lr_B; lbt = self._lr_Bt()
+        y = int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self._lo_codes(), self.w_scale_lo,
+                              self.bias, t, lb, m_hi, dtype, lbt)
+        if self.lr_A is not None and not fused:                    # branch the fused epilogue does not take
+            xa = x_rows().to(self.lr_A.dtype) @ self.lr_A
+            y.addmm_(xa.to(y.dtype), self.lr_B.to(y.dtype))
+        return y
+
     def forward_rows(self, x2: torch.Tensor, m_hi: int) -> torch.Tensor:
         """x2 [M,K] already gathered and ordered hi-tier rows first."""
-        t = lb = lbt = None
-        if self._fusable_lowrank(x2):
-            t = self._down(x2)
-            lb = self.lr_B; lbt = self._lr_Bt()
         xq, sx = quant_rows(x2)
-        return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self._lo_codes(), self.w_scale_lo,
-                                 self.bias, t, lb, m_hi, x2.dtype, lbt)
+        return self._two_tier(xq, sx, lambda: x2, m_hi, x2.dtype, self._fusable_lowrank(x2))
 
     def forward_gathered(self, canvas: torch.Tensor, row_idx: torch.Tensor, m_hi: int) -> torch.Tensor:
         """Gather + quantise in one kernel straight from the canvas, then the two-tier GEMM."""
-        t = lb = lbt = None
         xq, sx = gather_quant_rows(canvas, row_idx)
-        if self.lr_A is not None and self.lr_A.shape[1] == 32 and self.lr_A.dtype == canvas.dtype:
-            xg = torch.ops.pq_b200.gather_rows(canvas, row_idx)
-            t = self._down(xg)
-            lb = self.lr_B; lbt = self._lr_Bt()
-        return int8_gemm_grouped(xq, sx, self.weight_int8, self.w_scale, self._lo_codes(), self.w_scale_lo,
-                                 self.bias, t, lb, m_hi, canvas.dtype, lbt)
+        return self._two_tier(xq, sx, lambda: torch.ops.pq_b200.gather_rows(canvas, row_idx), m_hi, canvas.dtype,
+                              self._fusable_lowrank(canvas))
 
 
 # --------------------------------------------------------------------------- model conversion
@@ -670,48 +691,58 @@ def warm_kernels(Ms=(4352, 16640, 65792), device="cuda", lowrank_R=32, warm_lowr
 
 # --------------------------------------------------------------------------- self-test / micro-benchmark
 def _bench(fn, iters=20, warm=3):
+    """Mean milliseconds per call of `fn` (same signature and unit as the reference's helper, :486-492), timed on the
+    device with CUDA events on the current stream."""
     for _ in range(warm):
         fn()
-    torch.cuda.synchronize(); t = time.perf_counter()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
     for _ in range(iters):
         fn()
-    torch.cuda.synchronize(); return (time.perf_counter() - t) / iters * 1e3
+    stop.record()
+    stop.synchronize()
+    return start.elapsed_time(stop) / iters
 
 
-def selftest_and_bench(Ms=(4352, 16640, 33744, 65792), iters=10):
-    """The reference's numerical self-test (:498-536), asserted with its thresholds, followed by its
-    per-M micro-benchmark over the FLUX token-level shapes (:541-570)."""
-    dev = "cuda"
+def _rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
+    return float(((a - b).norm() / b.norm()).item())
+
+
+def _selftest(dev: str) -> Dict[str, object]:
+    """The reference's numerical self-test (:498-536) on its input (seed 0, 4352 x 3072 -> 12288, channel 5 scaled by
+    30), reported under the same keys and asserted with the same thresholds."""
     torch.manual_seed(0)
     lin = nn.Linear(3072, 12288, bias=True).to(dev, torch.bfloat16)
     x = (torch.randn(4352, 3072, device=dev) * 2).to(torch.bfloat16)
     x[:, 5] *= 30.0
-    ref_bf16 = F.linear(x, lin.weight, lin.bias).float()
-    q = Int8Linear(lin, device=torch.device(dev))
-    y = q(x).float()
-    xq, sx = quant_rows(x)
-    acc = torch._int_mm(xq, q.weight_int8.t()).float() if xq.shape[0] > 16 else xq.float() @ q.weight_int8.float().t()
-    ref_int8 = (acc * sx[:, None] * q.w_scale[None, :] + q.bias[None, :]).to(torch.bfloat16).float()
-    # torch reference quantizer, evaluated on the CPU where scalar division is an IEEE division
-    xf = x.float().cpu(); sc = xf.abs().amax(1, keepdim=True).clamp_min(1e-8) / 127
-    xq_ref = torch.round(xf / sc).clamp(-127, 127).to(torch.int8).to(dev); sc = sc.to(dev)
-    x_plain = torch.randn(4352, 3072, device=dev).to(torch.bfloat16)
-    y_plain = q(x_plain).float(); ref_plain = F.linear(x_plain, lin.weight, lin.bias).float()
-    xs = x[:8]
-    ys = q(xs).float()
-    xqs, sxs = quant_rows(xs)
-    rs = ((xqs.float() @ q.weight_int8.float().t()) * sxs[:, None] * q.w_scale[None, :] + q.bias[None, :]
-          ).to(torch.bfloat16).float()
-    x3 = x[:2048].reshape(8, 256, 3072)
+    layer = Int8Linear(lin, device=torch.device(dev))
+
+    def unfused(rows: torch.Tensor) -> torch.Tensor:
+        """codes @ codes in fp32, the two scales applied one after the other, bias, rounded (:506-510)."""
+        codes, scale = quant_rows(rows)
+        acc = codes.float() @ layer.weight_int8.float().t()
+        return ((acc * scale[:, None] * layer.w_scale[None, :] + layer.bias[None, :]).to(torch.bfloat16).float())
+
+    y = layer(x).float()
+    y_unfused = unfused(x)
+    y_bf16 = F.linear(x, lin.weight, lin.bias).float()
+    # torch's quantiser evaluated on the CPU, where division by a Python scalar is an IEEE division
+    xf = x.float().cpu()
+    scale_ref = xf.abs().amax(1, keepdim=True).clamp_min(1e-8) / 127
+    codes_ref = torch.round(xf / scale_ref).clamp(-127, 127).to(torch.int8)
+    codes, scale = quant_rows(x)
+    plain = torch.randn(4352, 3072, device=dev).to(torch.bfloat16)
+    few = x[:8]
+    stacked = x[:2048].reshape(8, 256, 3072)
     rep = {
-        "act_quant_mismatch_elems": int((xq != xq_ref).sum().item()),
-        "act_scale_max_rel_err": float(((sx - sc[:, 0]).abs() / sc[:, 0]).max().item()),
-        "fused_vs_unfused_int8_max_abs": float((y - ref_int8).abs().max().item()),
-        "fused_vs_unfused_int8_rel": float(((y - ref_int8).norm() / ref_int8.norm()).item()),
-        "int8_vs_bf16_rel_outlier30x": float(((y - ref_bf16).norm() / ref_bf16.norm()).item()),
-        "int8_vs_bf16_rel_plain": float(((y_plain - ref_plain).norm() / ref_plain.norm()).item()),
-        "smallM_fused_vs_unfused_rel": float(((ys - rs).norm() / rs.norm()).item()),
-        "3d_input_ok": bool(torch.equal(q(x3).reshape(2048, -1), q(x[:2048]))),
+        "act_quant_mismatch_elems": int((codes.cpu() != codes_ref).sum().item()),
+        "act_scale_max_rel_err": float(((scale.cpu() - scale_ref[:, 0]).abs() / scale_ref[:, 0]).max().item()),
+        "fused_vs_unfused_int8_max_abs": float((y - y_unfused).abs().max().item()),
+        "fused_vs_unfused_int8_rel": _rel_l2(y, y_unfused),
+        "int8_vs_bf16_rel_outlier30x": _rel_l2(y, y_bf16),
+        "int8_vs_bf16_rel_plain": _rel_l2(layer(plain).float(), F.linear(plain, lin.weight, lin.bias).float()),
+        "smallM_fused_vs_unfused_rel": _rel_l2(layer(few).float(), unfused(few)),
+        "3d_input_ok": bool(torch.equal(layer(stacked).reshape(2048, -1), layer(x[:2048]))),
     }
     rep["act_quant_mismatch_frac"] = rep["act_quant_mismatch_elems"] / x.numel()
     print("[int8_exec] selftest:", rep, flush=True)
@@ -719,30 +750,39 @@ def selftest_and_bench(Ms=(4352, 16640, 33744, 65792), iters=10):
     assert rep["fused_vs_unfused_int8_rel"] < 1e-3 and rep["int8_vs_bf16_rel_plain"] < 2e-2, rep
     assert rep["smallM_fused_vs_unfused_rel"] < 1e-3 and rep["3d_input_ok"], rep
     ops.check_device_status(dev)
-    del lin, q, x, ref_bf16, ref_int8, y, x_plain, y_plain, ref_plain
+    return rep
+
+
+def selftest_and_bench(Ms=(4352, 16640, 33744, 65792), iters=10):
+    """Self-test, then the per-M micro-benchmark over the FLUX token-level shapes weighted by how often each occurs
+    in the model (:541-570); result layout as the reference's (``selftest``, ``gpu``, ``per_M`` -> totals and
+    ``per_shape``)."""
+    dev = "cuda"
+    out = {"selftest": _selftest(dev), "gpu": torch.cuda.get_device_name(), "per_M": {}}
     torch.cuda.empty_cache()
-    out = {"selftest": rep, "gpu": torch.cuda.get_device_name(), "per_M": {}}
+    columns = ("bf16_ms", "int8_fused_ms", "quant_ms", "gemm_fused_ms")
     for M in Ms:
-        tot = {"bf16_ms": 0.0, "int8_fused_ms": 0.0, "quant_ms": 0.0, "gemm_fused_ms": 0.0}
+        image = dict.fromkeys(columns, 0.0)
         per_shape = {}
-        for (K, N), cnt in FLUX_TOKEN_SHAPES.items():
+        for (K, N), count in FLUX_TOKEN_SHAPES.items():
             lin = nn.Linear(K, N, bias=True).to(dev, torch.bfloat16)
             x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
-            q = Int8Linear(lin, device=torch.device(dev))
-            b = _bench(lambda: F.linear(x, lin.weight, lin.bias), iters)
-            f = _bench(lambda: q(x), iters)
-            xq, sx = quant_rows(x)
-            qq = _bench(lambda: quant_rows(x), iters)
-            tg = _bench(lambda: int8_gemm_fused(xq, sx, q.weight_int8, q.w_scale, q.bias, torch.bfloat16), iters)
-            per_shape[f"{K}x{N}"] = {"count": cnt, "bf16_ms": round(b, 3), "int8_fused_ms": round(f, 3),
-                                     "quant_ms": round(qq, 3), "gemm_fused_ms": round(tg, 3),
-                                     "speedup": round(b / f, 3),
-                                     "gemm_tops": round(2.0 * M * N * K / (tg * 1e-3) / 1e12, 1)}
-            tot["bf16_ms"] += b * cnt; tot["int8_fused_ms"] += f * cnt
-            tot["quant_ms"] += qq * cnt; tot["gemm_fused_ms"] += tg * cnt
-            del lin, x, q, xq, sx
+            layer = Int8Linear(lin, device=torch.device(dev))
+            codes, scale = quant_rows(x)
+            ms = dict(zip(columns, (
+                _bench(lambda: F.linear(x, lin.weight, lin.bias), iters),
+                _bench(lambda: layer(x), iters),
+                _bench(lambda: quant_rows(x), iters),
+                _bench(lambda: int8_gemm_fused(codes, scale, layer.weight_int8, layer.w_scale, layer.bias,
+                                               torch.bfloat16), iters))))
+            for c in columns:
+                image[c] += ms[c] * count
+            per_shape[f"{K}x{N}"] = {"count": count, **{c: round(v, 3) for c, v in ms.items()},
+                                     "speedup": round(ms["bf16_ms"] / ms["int8_fused_ms"], 3),
+                                     "gemm_tops": round(2.0 * M * N * K / (ms["gemm_fused_ms"] * 1e-3) / 1e12, 1)}
+            del lin, x, layer, codes, scale
             torch.cuda.empty_cache()
-        tot = {k: round(v, 2) for k, v in tot.items()}
+        tot = {c: round(v, 2) for c, v in image.items()}
         tot["speedup_fused_vs_bf16"] = round(tot["bf16_ms"] / tot["int8_fused_ms"], 3)
         tot["per_shape"] = per_shape
         out["per_M"][str(M)] = tot

@@ -62,6 +62,18 @@ def _ptr(t: Optional[Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+def _written_in_place(t: Tensor) -> None:
+    """The library writes through raw pointers, which torch cannot see: tell it that `t` changed, so that anything
+    keyed on the tensor's version counter (autograd's saved-tensor check, SharedInputGroup's cache) notices."""
+    if not t.is_inference():
+        torch.autograd.graph.increment_version(t)
+
+
+def tensor_version(t: Tensor) -> int:
+    """Version counter of `t`, or -1 for inference tensors (which do not keep one)."""
+    return -1 if t.is_inference() else t._version
+
+
 _lib_handle = None
 
 
@@ -214,6 +226,7 @@ def unpack_int4(packed: Tensor, out: Optional[Tensor] = None) -> Tensor:
     with _on_device(packed):
         rc = _LIB().pq_unpack_int4(packed.data_ptr(), K // 2, out.data_ptr(), K, N, K, _stream(packed))
     _lib.check(rc, f"pq_unpack_int4(N={N}, K={K})")
+    _written_in_place(out)
     return out
 
 
@@ -221,6 +234,24 @@ def unpack_int4(packed: Tensor, out: Optional[Tensor] = None) -> Tensor:
 def epilogue_supported(N: int, out_stride0: int, out_ptr: int, has_lowrank: bool, rank: int = 32) -> bool:
     """Whether pq_int8_gemm_ex takes this problem (its variants live in the CTA-pair kernel's vector stores)."""
     return N % 32 == 0 and out_stride0 % 8 == 0 and out_ptr % 16 == 0 and (not has_lowrank or rank == 32)
+
+
+def check_gemm_extents(M: int, N: int, K: int, s_row: Tensor, w_scale: Tensor, bias: Optional[Tensor],
+                        t: Optional[Tensor], lb: Optional[Tensor], lb_t: Optional[Tensor] = None,
+                        s_lo: Optional[Tensor] = None, m_hi: Optional[int] = None) -> None:
+    """The C ABI receives bare pointers, so a scale, bias or low-rank tensor that is too short would be read out of
+    bounds on the device.  Every operand's extent is checked here, on the host, before anything is launched
+    (AssertionError, like the reference's shape asserts)."""
+    assert s_row.numel() == M, f"s_row has {s_row.numel()} entries for {M} rows"
+    assert w_scale.numel() == N, f"w_scale has {w_scale.numel()} entries for {N} output channels"
+    assert bias is None or bias.numel() == N, f"bias has {bias.numel()} entries for {N} output channels"
+    assert s_lo is None or s_lo.numel() == N, f"low-tier scale has {s_lo.numel()} entries for {N} output channels"
+    assert m_hi is None or 0 <= int(m_hi) <= M, f"m_hi={m_hi} outside [0, {M}]"
+    assert (t is None) == (lb is None), "t and lb go together"
+    if t is not None:
+        assert t.dim() == 2 and lb.dim() == 2 and t.shape[0] == M and lb.shape == (t.shape[1], N), \
+            f"low-rank operands t {tuple(t.shape)} / lb {tuple(lb.shape)} do not fit [M={M}, R] / [R, N={N}]"
+        assert lb_t is None or tuple(lb_t.shape) == (N, t.shape[1]), f"lb_t {tuple(lb_t.shape)} is not [N, R]"
 
 
 def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias: Optional[Tensor],
@@ -235,6 +266,7 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
     assert w_int8.shape[1] == K, (w_int8.shape, K)
     assert K % 16 == 0, f"K={K} must be a multiple of 16"
     assert s_row.dtype == torch.float32 and w_scale.dtype == torch.float32
+    check_gemm_extents(M, N, K, s_row, w_scale, bias, t, lb, lb_t, s_lo, m_hi if w_lo is not None else None)
     s_row = s_row.contiguous(); w_scale = w_scale.contiguous()
     if bias is not None:
         assert bias.dtype == torch.float32
@@ -289,6 +321,8 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
                                           ws.data_ptr(), ws.numel() * 4, _stream(xq))
     if rc:
         _lib.check(rc, f"pq_int8_gemm(M={M}, N={N}, K={K})")
+    if epilogue & EPI_ACCUMULATE:
+        _written_in_place(out)
     return out
 
 
@@ -300,6 +334,7 @@ def _gemm_g32_impl(xq: Tensor, s_a: Tensor, w_int8: Tensor, s_w_gm: Tensor, bias
     N = w_int8.shape[0]
     assert w_int8.shape[1] == K and K % 128 == 0, (w_int8.shape, K)
     assert s_a.shape == (M, K // 32) and s_w_gm.shape == (K // 32, N), (s_a.shape, s_w_gm.shape)
+    assert bias is None or bias.numel() == N, f"bias has {bias.numel()} entries for {N} output channels"
     xq = xq.contiguous(); w_int8 = w_int8.contiguous()
     s_a = s_a.contiguous().float(); s_w_gm = s_w_gm.contiguous().float()
     if bias is not None:
@@ -327,6 +362,15 @@ def _dequant_epilogue_impl(acc: Tensor, s_row: Tensor, s_col: Tensor, bias: Opti
     return out
 
 
+def check_scatter_extents(m_act: int, canvas_rows: int, tokens: Tensor, ptr: Tensor, src: Tensor, beta: Tensor) -> None:
+    """Extents of the contributor lists (their contents are trusted: they come from routing.build_route_plan)."""
+    assert tokens.dim() == 1 and ptr.dim() == 1 and src.dim() == 1 and beta.dim() == 1
+    assert ptr.numel() == tokens.numel() + 1, f"ptr has {ptr.numel()} entries for {tokens.numel()} tokens"
+    assert src.numel() == beta.numel(), f"{src.numel()} sources but {beta.numel()} weights"
+    assert tokens.numel() <= canvas_rows, f"{tokens.numel()} touched tokens on a canvas of {canvas_rows}"
+    assert src.numel() == 0 or m_act > 0, "contributors without rows to take them from"
+
+
 def _scatter_rows_impl(y: Tensor, tokens: Tensor, ptr: Tensor, src: Tensor, beta: Tensor, canvas: Tensor) -> None:
     assert y.is_cuda and canvas.is_cuda and y.dtype == canvas.dtype and y.dim() == 2 and canvas.dim() == 2
     assert y.stride(1) == 1 and canvas.stride(1) == 1 and y.shape[1] == canvas.shape[1]
@@ -334,7 +378,7 @@ def _scatter_rows_impl(y: Tensor, tokens: Tensor, ptr: Tensor, src: Tensor, beta
         assert v.is_cuda and v.dtype == torch.int32 and v.is_contiguous()
     assert beta.is_cuda and beta.dtype == torch.float32 and beta.is_contiguous()
     n_tokens = tokens.numel()
-    assert ptr.numel() == n_tokens + 1 and src.numel() == beta.numel()
+    check_scatter_extents(y.shape[0], canvas.shape[0], tokens, ptr, src, beta)
     with _on_device(canvas):
         rc = _LIB().pq_scatter_rows(y.data_ptr(), max(y.stride(0), y.shape[1]), y.shape[0], tokens.data_ptr(),
                                          ptr.data_ptr(), src.data_ptr(), beta.data_ptr(), n_tokens,

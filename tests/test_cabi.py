@@ -125,3 +125,33 @@ def test_scatter_and_gather_argument_checks():
     # group-32 GEMM: K must be whole 128-byte stages
     assert lib.pq_int8_gemm_g32(p16, 96, p16, p16, 96, p16, None, p16, 0, 64, 8, 64, 96, None, 0, None) == 7
     assert lib.pq_int8_gemm_g32(p16, 128, None, p16, 128, p16, None, p16, 0, 64, 8, 64, 128, None, 0, None) == 1
+
+
+def test_operand_extent_checks_run_on_the_host():
+    """The C ABI sees bare pointers; the Python operators check every operand's extent before a launch, so a short
+    scale, bias or low-rank tensor is an AssertionError instead of an out-of-bounds device read."""
+    import torch
+    from pyraquant_b200 import ops
+    M, N, K = 8, 64, 64
+    f = lambda *shape: torch.zeros(*shape)
+    ok = dict(s_row=f(M), w_scale=f(N), bias=f(N), t=f(M, 32), lb=f(32, N), lb_t=f(N, 32))
+    ops.check_gemm_extents(M, N, K, **ok)
+    ops.check_gemm_extents(M, N, K, f(M), f(N), None, None, None)
+    for key, bad in (("s_row", f(M - 1)), ("w_scale", f(N + 1)), ("bias", f(N - 8)), ("t", f(M - 1, 32)),
+                     ("lb", f(32, N - 8)), ("lb", f(16, N)), ("lb_t", f(32, N))):
+        with pytest.raises(AssertionError):
+            ops.check_gemm_extents(M, N, K, **{**ok, key: bad})
+    with pytest.raises(AssertionError):
+        ops.check_gemm_extents(M, N, K, f(M), f(N), None, f(M, 32), None)          # t without lb
+    with pytest.raises(AssertionError):
+        ops.check_gemm_extents(M, N, K, f(M), f(N), None, None, None, s_lo=f(N - 1), m_hi=4)
+    with pytest.raises(AssertionError):
+        ops.check_gemm_extents(M, N, K, f(M), f(N), None, None, None, s_lo=f(N), m_hi=M + 1)
+    i = lambda n: torch.zeros(n, dtype=torch.int32)
+    ops.check_scatter_extents(10, 16, i(3), i(4), i(5), f(5))
+    with pytest.raises(AssertionError):
+        ops.check_scatter_extents(10, 16, i(3), i(3), i(5), f(5))                   # ptr too short
+    with pytest.raises(AssertionError):
+        ops.check_scatter_extents(10, 16, i(3), i(4), i(5), f(4))                   # src / beta differ
+    with pytest.raises(AssertionError):
+        ops.check_scatter_extents(10, 2, i(3), i(4), i(5), f(5))                    # more tokens than canvas rows

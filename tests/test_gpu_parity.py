@@ -768,3 +768,97 @@ def test_routed_two_tier_linear(cuda_dev):
     assert max_rel_err(y, ref) <= TOL
     y2 = q.forward_rows(rows.to(cuda_dev), mh).cpu()
     assert max_rel_err(y2, ref) <= TOL
+
+
+@pytest.mark.parametrize("case", ["rank16", "fp16_factors"])
+def test_routed_linear_keeps_a_lowrank_branch_it_cannot_fuse(cuda_dev, case):
+    """A low-rank branch outside the fused epilogue's reach (rank 16; factors in another dtype than the activations)
+    is added after the two-tier GEMM instead of being dropped."""
+    H = W = 16; K = 128; N = 256
+    g = torch.Generator().manual_seed(90)
+    sel = np.zeros((2, 2), np.float32); sel[0, 0] = sel[1, 1] = 1
+    tmap = routing.leaf_tier_to_token_map(np.array([[1, 0], [0, 0]], np.float32), (H, W))
+    plan = routing.build_route_plan((H, W), routing.leaf_run_boxes(sel, 16), 2, token_tier_hi=tmap)
+    canvas = rand_act(H * W, K, torch.bfloat16, 91)
+    lin = nn.Linear(K, N, bias=True).to(torch.bfloat16)
+    R, fdt = (16, torch.bfloat16) if case == "rank16" else (32, torch.float16)
+    A = (torch.randn(K, R, generator=g) * 0.05).to(fdt)
+    B = (torch.randn(R, N, generator=g) * 0.05).to(fdt)
+    q = int8_exec.Int8LinearRouted(lin, device=cuda_dev, lowrank=(A, B))
+    rows = canvas[torch.from_numpy(plan.row_idx).long()]
+    w8, s8 = oracle.quant_weight(lin.weight.detach())
+    w4, s4 = oracle.nested4_from_int8(w8, s8)
+    xq, sx = oracle.quant_rows(rows)
+    t = (rows.to(fdt).float() @ A.float()).to(fdt)
+    b32 = lin.bias.detach().float()
+    mh = plan.m_hi
+    assert 0 < mh < plan.n_rows
+    ref = torch.cat([oracle.exact_dequant_f64(oracle.int_mm(xq[:mh], w8), sx[:mh], s8, b32, t[:mh], B),
+                     oracle.exact_dequant_f64(oracle.int_mm(xq[mh:], w4), sx[mh:], s4, b32, t[mh:], B)])
+    no_branch = torch.cat([oracle.exact_dequant_f64(oracle.int_mm(xq[:mh], w8), sx[:mh], s8, b32, None, None),
+                           oracle.exact_dequant_f64(oracle.int_mm(xq[mh:], w4), sx[mh:], s4, b32, None, None)])
+    assert max_rel_err(no_branch.float(), ref) > 5 * TOL           # the branch matters in this case
+    # two roundings to bf16 (GEMM output, then the added term) instead of one: twice the usual bound
+    y = q.forward_gathered(canvas.to(cuda_dev), plan.to(cuda_dev)["row_idx"], mh).cpu()
+    assert max_rel_err(y, ref) <= 2 * TOL
+    y2 = q.forward_rows(rows.to(cuda_dev), mh).cpu()
+    assert max_rel_err(y2, ref) <= 2 * TOL
+
+
+def test_shared_input_group_under_inference_mode_and_after_inplace_writes(cuda_dev, monkeypatch):
+    """Inference tensors keep no version counter: grouped layers then run ungrouped instead of failing.  The
+    library's own in-place write (accumulate epilogue) bumps the version of its target, so a cached quantisation of
+    that tensor is not reused afterwards."""
+    g = torch.Generator().manual_seed(34)
+    K = 256
+    a, b = _toy_layer(cuda_dev, g, K, 256), _toy_layer(cuda_dev, g, K, 256)
+    x = rand_act(300, K, torch.bfloat16, 35).to(cuda_dev)
+    alone = [a(x), b(x)]
+    int8_exec.share_input_quantisation([a, b])
+    with torch.inference_mode():
+        xi = x.clone()
+        assert xi.is_inference()
+        got = [a(xi), b(xi)]
+    assert torch.equal(got[0], alone[0]) and torch.equal(got[1], alone[1])
+    # accumulate into a tensor the group has cached, then feed it to the group again
+    calls = {"n": 0}
+    real = ops._quant_rows_impl
+
+    def counting(x2):
+        calls["n"] += 1
+        return real(x2)
+    monkeypatch.setattr(ops, "_quant_rows_impl", counting)
+    h = x.clone()
+    y0 = a(h)                                                       # caches the quantisation of h
+    n0 = calls["n"]
+    v0 = h._version
+    c = _toy_layer(cuda_dev, g, K, K, lowrank=False)
+    c.forward_ex(x, ops.EPI_ACCUMULATE, out=h)                      # h += c(x), written by the GEMM epilogue
+    assert h._version > v0
+    y1 = b(h)
+    assert calls["n"] == n0 + 2 and not torch.equal(h, x)         # c quantised x, b quantised the updated h
+    monkeypatch.setattr(ops, "_quant_rows_impl", real)
+    b.__dict__.pop("_shared_input"); a.__dict__.pop("_shared_input")
+    assert torch.equal(y1, b(h))                                    # the fresh codes, not the stale ones
+    del y0
+
+
+def test_lean_path_follows_converted_buffers(cuda_dev):
+    """Replacing or converting the float buffers (w_scale, bias, lr_B) while the int8 weight stays in place must not
+    leave the fast path with stale addresses."""
+    g = torch.Generator().manual_seed(36)
+    m = _toy_layer(cuda_dev, g, 256, 512)
+    x = rand_act(200, 256, torch.bfloat16, 37).to(cuda_dev)
+    y0 = m(x)
+    with torch.no_grad():
+        new_scale = (m.w_scale * 2.0).clone()
+        new_B = (m.lr_B.float() * 0.5).to(torch.bfloat16)
+    m.w_scale = new_scale
+    m.lr_B = new_B
+    y1 = m(x)
+    xq, sx = int8_exec.quant_rows(x)
+    want = int8_exec.int8_gemm_lr(xq, sx, m.weight_int8, new_scale, m.bias, x @ m.lr_A, new_B, torch.bfloat16)
+    assert torch.equal(y1, want) and not torch.equal(y1, y0)
+    m.lr_B.mul_(2.0)                                               # in place: the K-major copy must follow
+    want2 = int8_exec.int8_gemm_lr(xq, sx, m.weight_int8, new_scale, m.bias, x @ m.lr_A, m.lr_B, torch.bfloat16)
+    assert torch.equal(m(x), want2)
