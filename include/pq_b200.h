@@ -57,8 +57,8 @@ int pq_last_cuda_error(void);
  *                       term, where the epilogue outlasts the K loop; else 8), 8 or 16;
  *   "gemm_tma_store"    1 (default) = sixteen-warp tiles of plain calls store through shared memory + TMA, 0 = never;
  *   "gemm_pair"         0 = never use the CTA-pair kernel, 1 = automatic (default), 2 = whenever it is legal;
- *   "gemm_debug_timing" 1 = the CTA-pair kernel writes per-role cycle counters to workspace + 256
- *                       (needs ws_bytes >= 256 + 4096*64).
+ *   "gemm_debug_timing" 1 = the CTA-pair kernel runs in its debug instantiation (the production kernel contains no
+ *                       counters) and writes per-role cycle counters to workspace + 256 (needs ws_bytes >= 256 + 4096*64).
  * Unknown keys return PQ_ERR_UNSUPPORTED.  Not part of the reference API. */
 int pq_set_option(const char* key, int value);
 int pq_get_option(const char* key, int* value);
@@ -228,6 +228,13 @@ int pq_int8_linear_noalloc(const void* x, int dtype, int64_t ldx,
  * pq_status (PQ_OK or PQ_ERR_TIMEOUT); *raw receives the word itself (role and barrier that gave
  * up) when raw != NULL.  The word is cleared when `clear` is non-zero. */
 int pq_read_status_word(void* workspace, int32_t* raw, int clear, void* stream);
+
+/* Diagnostic for the bounded waits (no counterpart in the reference): launches one warp in which a thread waits,
+ * through the same bounded wait the GEMM roles use, on a barrier that nothing ever completes.  After `budget_us`
+ * microseconds (1 .. 100000) the wait gives up, the kernel writes the status word (role 5) and returns normally; the
+ * context stays usable.  pq_read_status_word then reports PQ_ERR_TIMEOUT.  Shows the path from a wait that runs out
+ * to the host-visible error without a GPU fault, trap or endless loop. */
+int pq_wait_probe(void* workspace, size_t ws_bytes, int budget_us, void* stream);
 
 /* Tensor-pipe ceiling probe: every CTA issues `iters` tcgen05.mma kind::i8 128x256x32 instructions
  * on shared-memory operands with no global traffic and writes elapsed clock cycles per CTA to

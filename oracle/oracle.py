@@ -49,20 +49,33 @@ def quant_rows_g32(x: torch.Tensor, group: int = 32) -> Tuple[torch.Tensor, torc
     return q.reshape(M, K).to(torch.int8), s[..., 0].contiguous()
 
 
-def quant_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def over_qmax(amax: torch.Tensor, qmax: float, where: str) -> torch.Tensor:
+    """`amax / qmax` with qmax a Python scalar, as torch evaluates it where the reference's constructor runs.
+    On the CPU it is an IEEE division.  torch's CUDA kernel for division by a host scalar multiplies by the fp32
+    reciprocal instead (amax * fl32(1 / qmax)), which differs from the quotient by one unit in the last place for some
+    inputs and moves weights that sit on a rounding tie to the neighbouring code.  `where` = "cpu" | "cuda" selects
+    which of the two results is restated; both are pinned by fixtures made by the reference (int8linear_ctor.npz on
+    the CPU, the w_scale / code row sums of forward_reference_gpu.npz on a B200)."""
+    if where == "cpu":
+        return amax / qmax
+    assert where == "cuda", where
+    return amax * torch.tensor(float(np.float32(1.0) / np.float32(qmax)), dtype=torch.float32)
+
+
+def quant_weight(w: torch.Tensor, where: str = "cpu") -> Tuple[torch.Tensor, torch.Tensor]:
     """Per-output-channel symmetric INT8 weights.  deploy/int8_exec.py:355-357."""
     wf = w.float()
-    s = wf.abs().amax(dim=1).clamp_min(1e-8) / 127.0
+    s = over_qmax(wf.abs().amax(dim=1).clamp_min(1e-8), 127.0, where)
     q = torch.round(wf / s[:, None]).clamp_(-127, 127).to(torch.int8)
     return q.contiguous(), s.contiguous()
 
 
-def quant_weight_g32(w: torch.Tensor, group: int = 32) -> Tuple[torch.Tensor, torch.Tensor]:
+def quant_weight_g32(w: torch.Tensor, group: int = 32, where: str = "cpu") -> Tuple[torch.Tensor, torch.Tensor]:
     """Group-32 INT8 weight grid = the codes and scales behind qdq_weight(w, 8, 32).
     pyraquant/quantizers_weight.py:96-109 (W8_GROUPED is True, :65)."""
     out_f, in_f = w.shape
     wg = w.detach().float().reshape(out_f, in_f // group, group)
-    scale = wg.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8) / 127
+    scale = over_qmax(wg.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8), 127, where)
     q = (wg / scale).round().clamp_(-127, 127)
     return q.reshape(out_f, in_f).to(torch.int8), scale[..., 0].contiguous()
 

@@ -58,6 +58,7 @@ SIGNATURES = {
     "pq_int8_linear_noalloc": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                        c_int64, c_int64, c_int64, c_int64, POINTER(c_void_p), c_void_p]),
     "pq_read_status_word": (c_int, [c_void_p, POINTER(c_int32), c_int, c_void_p]),
+    "pq_wait_probe": (c_int, [c_void_p, c_size_t, c_int, c_void_p]),
     "pq_i8_mma_issue_loop": (c_int, [c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
 }
 

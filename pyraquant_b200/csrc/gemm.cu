@@ -417,6 +417,20 @@ pq_i8_mma_issue_loop_kernel(int iters, long long* cycles, int32_t* status) {
   if (threadIdx.x < 32) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
 }
 
+// Wait that nothing ends: one thread waits on a barrier no one arrives on, through the same bounded wait the GEMM
+// roles use, with a budget of `budget_ns`; when the wait gives up it reports (role 5) and the kernel returns.
+__global__ void pq_wait_probe_kernel(int32_t* status, unsigned long long budget_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); abort_flag = 0; fence_mbar_init(); }
+  __syncthreads();
+  if (threadIdx.x == 0 && !wait_or_abort(&bar, 0u, &abort_flag, budget_ns)) {
+    report_timeout(status, 5, 1);
+    abort_flag = 1;
+  }
+  __syncthreads();
+}
+
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -555,12 +569,12 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
     if (epi_flags != 0) {
       // the epilogue variants exist in the CTA-pair kernel's vector store path only
       if (!pair_legal || N % 32 != 0 || ldo % 8 != 0 || !aligned_to(out, 16)) return PQ_ERR_UNSUPPORTED;
-      return launch_gemm_pair(out_dtype == PQ_DTYPE_BF16, dbg_acc != nullptr, xq, ldx, w0, w1, ldw, has_lr ? t : nullptr, ldt,
+      return launch_gemm_pair(out_dtype == PQ_DTYPE_BF16, dbg_acc != nullptr || p.timing != nullptr, xq, ldx, w0, w1, ldw, has_lr ? t : nullptr, ldt,
                               has_lr ? lb_t : nullptr, M, N, K, p, static_cast<cudaStream_t>(stream));
     }
     if (options().gemm_pair != 0 && bn == 256 && pair_legal &&
         pair_rows * ((N + 255) / 256) >= (options().gemm_pair == 2 ? 1 : sm_count() / 2)) {
-      return launch_gemm_pair(out_dtype == PQ_DTYPE_BF16, dbg_acc != nullptr, xq, ldx, w0, w1, ldw, has_lr ? t : nullptr, ldt,
+      return launch_gemm_pair(out_dtype == PQ_DTYPE_BF16, dbg_acc != nullptr || p.timing != nullptr, xq, ldx, w0, w1, ldw, has_lr ? t : nullptr, ldt,
                               has_lr ? lb_t : nullptr, M, N, K, p, static_cast<cudaStream_t>(stream));
     }
   }
@@ -627,6 +641,16 @@ extern "C" int pq_int8_gemm_grouped(const int8_t* xq, int64_t ldx, const float* 
                                     void* stream) {
   return gemm_common(xq, ldx, s_row, w_hi, s_col_hi, w_lo, s_col_lo, ldw, bias, t, ldt, lb, ldb, lb_t, R, lr_dtype, out,
                      out_dtype, ldo, M_hi, M, N, K, workspace, ws_bytes, nullptr, stream);
+}
+
+extern "C" int pq_wait_probe(void* workspace, size_t ws_bytes, int budget_us, void* stream) {
+  if (workspace == nullptr) return PQ_ERR_NULL;
+  if (ws_bytes < PQ_GEMM_WORKSPACE_BYTES) return PQ_ERR_WORKSPACE;
+  if (budget_us <= 0 || budget_us > 100000) return PQ_ERR_SHAPE;
+  pq_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<int32_t*>(workspace), static_cast<unsigned long long>(budget_us) * 1000ull);
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
 }
 
 extern "C" int pq_i8_mma_issue_loop(int ctas, int iters, long long* cycles, void* workspace, size_t ws_bytes,

@@ -203,8 +203,10 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   const int num_kb = (p.K + BK - 1) / BK;
   constexpr uint32_t kTmemCols = 2 * PBN;
   const int pair = static_cast<int>(blockIdx.x) >> 1;
-  // cycle-counter experiments: wall-clock trace of the first pair, 24 slots per tile
-  long long* trace = (p.timing != nullptr && pair == 0) ? p.timing + 8192 : nullptr;
+  // cycle-counter experiments exist in the DBG instantiation only: in the production kernel `timing` is a
+  // compile-time null pointer and every branch on it is removed.  Wall-clock trace of the first pair, 24 slots per tile.
+  long long* const timing = DBG ? p.timing : nullptr;
+  long long* trace = (timing != nullptr && pair == 0) ? timing + 8192 : nullptr;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmW1);
@@ -315,20 +317,20 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       for (; w.valid() && ok; w.advance(), ++it) {
         const int buf = it & 1;
         const uint32_t use = static_cast<uint32_t>(it >> 1);
-        const long long c0 = p.timing ? clock64() : 0;
+        const long long c0 = timing ? clock64() : 0;
         if (!wait_or_abort(&tempty_bar[buf], (use & 1u) ^ 1u, abort_flag)) {
           report_timeout(p.status, 2, 2); *abort_flag = 1; ok = false; break;
         }
-        if (p.timing) tm_tempty += clock64() - c0;
+        if (timing) tm_tempty += clock64() - c0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * PBN);
 #pragma unroll 1
         for (int kb = 0; kb < num_kb; ++kb) {
-          const long long c1 = p.timing ? clock64() : 0;
+          const long long c1 = timing ? clock64() : 0;
           if (!wait_or_abort(&full_bar[stage], phase, abort_flag)) {
             report_timeout(p.status, 2, 1); *abort_flag = 1; ok = false; break;
           }
-          if (p.timing) tm_full += clock64() - c1;
+          if (timing) tm_full += clock64() - c1;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
           const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
@@ -344,7 +346,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         commit_both(&tfull_bar[buf]);
         if (trace && it < 1000) trace[it * 24 + 18] = static_cast<long long>(global_timer_ns());
       }
-      if (p.timing) { p.timing[blockIdx.x * 16 + 0] = tm_tempty; p.timing[blockIdx.x * 16 + 1] = tm_full; }
+      if (timing) { timing[blockIdx.x * 16 + 0] = tm_tempty; timing[blockIdx.x * 16 + 1] = tm_full; }
     }
   } else if (HAS_LR && run && warp == kLrWarp && rank == 0) {
     // ------------------------------------------------------------------ low-rank MMA issuer (leader CTA only)
@@ -380,11 +382,11 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           tc_mma_f16_pair(d_tmem, a_desc, b_desc, idesc_lr, 1u);
           tc_mma_f16_pair(d_tmem, a_desc + 2, b_desc + 2, idesc_lr, 1u);
           commit_both(&lr_done[pb * kLrChunks + chunk]);
-          if (p.timing) { const long long now = clock64(); tm_det[chunk] += now - stamp[pb * kLrChunks + chunk]; stamp[4 + pb * kLrChunks + chunk] = now; }
+          if (timing) { const long long now = clock64(); tm_det[chunk] += now - stamp[pb * kLrChunks + chunk]; stamp[4 + pb * kLrChunks + chunk] = now; }
         }
       }
       if (!ok) *abort_flag = 1;
-      if (p.timing) { p.timing[blockIdx.x * 16 + 8] = tm_det[0]; p.timing[blockIdx.x * 16 + 9] = tm_det[1]; }
+      if (timing) { timing[blockIdx.x * 16 + 8] = tm_det[0]; timing[blockIdx.x * 16 + 9] = tm_det[1]; }
     }
   } else if (run && warp >= 2 && warp < 2 + EW) {
     // ------------------------------------------------------------------ epilogue (warps 2 .. 2 + EW - 1 of both CTAs)
@@ -424,7 +426,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       const int buf = it & 1;
       const uint32_t par = static_cast<uint32_t>(it >> 1) & 1u;
 
-      const long long e0 = p.timing ? clock64() : 0;
+      const long long e0 = timing ? clock64() : 0;
       if (n0 != aux_n0 || c.set != aux_set) {
         aux_n0 = n0; aux_set = c.set;
         const float* scol_g = p.s_col[0];
@@ -444,7 +446,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
 #pragma unroll
       for (int mb = 0; mb < MBN; ++mb) { srow[mb][0] = srow_next[mb][0]; srow[mb][1] = srow_next[mb][1]; }
 
-      const long long e1 = p.timing ? clock64() : 0;
+      const long long e1 = timing ? clock64() : 0;
       if (!aborted) {
         const bool landed = wait_or_abort(&tfull_bar[buf], par, abort_flag);
         if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 3); *abort_flag = 1; aborted = true; }
@@ -452,7 +454,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       if (aborted) continue;
       tc_fence_after();
       if (trace && it < 1000 && warp == 2 && lane == 0) trace[it * 24 + 20 + rank] = static_cast<long long>(global_timer_ns());
-      const long long e2 = p.timing ? clock64() : 0;
+      const long long e2 = timing ? clock64() : 0;
       long long e3 = e2, e4 = e2;
       {
         PairWalker wn = w; wn.advance();
@@ -477,7 +479,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           const float2 sc = *reinterpret_cast<const float2*>(scol_s + cl);
           if constexpr (DBG) {
             const int rA = row0 + quarter * 32 + (mb_base + mb) * 16 + g;
-            dump_acc_pair(p.dbg_acc, p.N, rA, rA + 8, n0 + cl, row_end, v[4 * nb + 0], v[4 * nb + 1], v[4 * nb + 2], v[4 * nb + 3]);
+            if (p.dbg_acc != nullptr) dump_acc_pair(p.dbg_acc, p.N, rA, rA + 8, n0 + cl, row_end, v[4 * nb + 0], v[4 * nb + 1], v[4 * nb + 2], v[4 * nb + 3]);
           }
           const float2 yA = __fmul2_rn(int2_to_float2_rn(static_cast<int32_t>(v[4 * nb + 0]), static_cast<int32_t>(v[4 * nb + 1])),
                                        __fmul2_rn(srA, sc));
@@ -595,21 +597,21 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           }
           tc_fence_before();
           __syncwarp();
-          if (p.timing && warp == 2 && lane == 0) stamp[buf * kLrChunks + ch] = clock64();
+          if (timing && warp == 2 && lane == 0) stamp[buf * kLrChunks + ch] = clock64();
           if (trace && it < 1000 && ch == 0 && lane == 0 && warp < 10) trace[it * 24 + rank * 8 + (warp - 2)] = static_cast<long long>(global_timer_ns());
           if (lane == 0) mbar_arrive_cluster(leader_addr(&ylr_ready[buf * kLrChunks + ch]));
         }
-        if (p.timing) e3 = clock64();
+        if (timing) e3 = clock64();
       }
       // final pass: (scale when there is no low-rank term,) + bias, round, store
       auto chunk_ready = [&](int ch) -> bool {     // low-rank term of chunk ch has landed in tensor memory
         if constexpr (HAS_LR) {
-          const long long c0 = p.timing ? clock64() : 0;
+          const long long c0 = timing ? clock64() : 0;
           const bool landed = wait_or_abort(&lr_done[buf * kLrChunks + ch], par, abort_flag);
           if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 6); *abort_flag = 1; return false; }
           tc_fence_after();
           if (trace && it < 1000 && ch == 0 && warp == 2 && lane == 0) trace[it * 24 + (rank ? 22 : 19)] = static_cast<long long>(global_timer_ns());
-          if (p.timing) { const long long now = clock64(); lr_wait += now - c0; te_exec[ch] += now - stamp[4 + buf * kLrChunks + ch]; }
+          if (timing) { const long long now = clock64(); lr_wait += now - c0; te_exec[ch] += now - stamp[4 + buf * kLrChunks + ch]; }
         }
         return true;
       };
@@ -647,13 +649,13 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_addr(&tempty_bar[buf]));
-      if (p.timing) { te_aux += e1 - e0; te_tfull += e2 - e1; te_p1 += e3 - e2; te_lr += e4 - e3; te_p2 += clock64() - e4; }
+      if (timing) { te_aux += e1 - e0; te_tfull += e2 - e1; te_p1 += e3 - e2; te_lr += e4 - e3; te_p2 += clock64() - e4; }
     }
     if (EW == 16 && !HAS_LR && p.tma_store && lane == 0) bulk_wait_group0();   // stores done before shared memory goes
-    if (p.timing && warp == 2 && lane == 0) {
-      p.timing[blockIdx.x * 16 + 2] = te_aux; p.timing[blockIdx.x * 16 + 3] = te_tfull; p.timing[blockIdx.x * 16 + 4] = te_p1;
-      p.timing[blockIdx.x * 16 + 5] = te_lr; p.timing[blockIdx.x * 16 + 6] = te_p2; p.timing[blockIdx.x * 16 + 7] = it;
-      p.timing[blockIdx.x * 16 + 10] = te_exec[0]; p.timing[blockIdx.x * 16 + 11] = te_exec[1];
+    if (timing && warp == 2 && lane == 0) {
+      timing[blockIdx.x * 16 + 2] = te_aux; timing[blockIdx.x * 16 + 3] = te_tfull; timing[blockIdx.x * 16 + 4] = te_p1;
+      timing[blockIdx.x * 16 + 5] = te_lr; timing[blockIdx.x * 16 + 6] = te_p2; timing[blockIdx.x * 16 + 7] = it;
+      timing[blockIdx.x * 16 + 10] = te_exec[0]; timing[blockIdx.x * 16 + 11] = te_exec[1];
     }
   }
 

@@ -62,7 +62,8 @@ constexpr int kLR = 32;          // low-rank width handled in the epilogue
 
 // Bounded wait on an mbarrier phase.  The first probe is inline; the polling loop (wall-clock budget, abort
 // flag) lives out of line to keep the role loops small.
-__device__ __noinline__ bool wait_or_abort_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __noinline__ bool wait_or_abort_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                uint64_t budget_ns = kWaitBudgetNs) {
   uint64_t t0 = 0;
   for (uint32_t i = 1; i < kWaitMaxPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -70,14 +71,15 @@ __device__ __noinline__ bool wait_or_abort_slow(uint64_t* bar, uint32_t parity, 
       if (*abort_flag != 0) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitBudgetNs) return false;
+      else if (now - t0 > budget_ns) return false;
     }
   }
   return false;
 }
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              uint64_t budget_ns = kWaitBudgetNs) {
   if (mbar_try_wait(bar, parity)) return true;
-  return wait_or_abort_slow(bar, parity, abort_flag);
+  return wait_or_abort_slow(bar, parity, abort_flag, budget_ns);
 }
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }

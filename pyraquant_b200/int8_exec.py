@@ -146,12 +146,12 @@ LOWRANK_B_ATTR = "_lowrank_B"
 def _quantize_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Per-output-channel symmetric absmax INT8 (reference :355-357): fp32 math, round-half-even.
 
-    The divisor 127 is passed as a tensor: torch's CUDA kernel turns division by a Python scalar into a
-    multiplication with its reciprocal, which moves some scales by one ulp; tensor / tensor is an IEEE
-    division on every device, so CPU and GPU conversions give identical codes and scales."""
+    The scale is formed exactly as the reference forms it, `amax / 127.0` with a Python scalar, so that a layer
+    converted on a device gets the codes and scales the reference's constructor produces on that device, bit for bit.
+    (torch's CUDA kernel multiplies by fl32(1 / 127) where the CPU divides; a few per cent of the channels then differ
+    by one code at rounding ties between a CPU-converted and a GPU-converted layer, in the reference as here.)"""
     wf = w.float()
-    amax = wf.abs().amax(dim=1).clamp_min(1e-8)
-    scale = amax / torch.full_like(amax, 127.0)
+    scale = wf.abs().amax(dim=1).clamp_min(1e-8) / 127.0
     codes = torch.round(wf / scale[:, None]).clamp_(-127, 127).to(torch.int8)
     return codes.contiguous(), scale.contiguous()
 
@@ -486,8 +486,7 @@ def _quantize_weight_g32(w: torch.Tensor, group: int = 32) -> Tuple[torch.Tensor
     (pyraquant/quantizers_weight.py:96-109).  Returns codes [N,K] and scales [N, K/32]."""
     out_f, in_f = w.shape
     wg = w.float().reshape(out_f, in_f // group, group)
-    amax = wg.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8)
-    scale = amax / torch.full_like(amax, 127.0)
+    scale = wg.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8) / 127        # the reference's expression, scalar divisor
     codes = torch.round(wg / scale).clamp_(-127, 127).to(torch.int8)
     return codes.reshape(out_f, in_f).contiguous(), scale[..., 0].contiguous()
 

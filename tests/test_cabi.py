@@ -122,6 +122,9 @@ def test_scatter_and_gather_argument_checks():
     assert lib.pq_gather_rows(p16, 0, 16, 64, 64, None, 4, p16, 64, None) == 1
     assert lib.pq_gather_quant_rows(p16, 0, 16, 64, 64, None, 4, p16, p16, None) == 1
     assert lib.pq_i8_mma_issue_loop(0, 10, p16, None, 0, None) == 2
+    assert lib.pq_wait_probe(None, 256, 1000, None) == 1
+    assert lib.pq_wait_probe(p16, 8, 1000, None) == 8
+    assert lib.pq_wait_probe(p16, 256, 0, None) == 2
     # group-32 GEMM: K must be whole 128-byte stages
     assert lib.pq_int8_gemm_g32(p16, 96, p16, p16, 96, p16, None, p16, 0, 64, 8, 64, 96, None, 0, None) == 7
     assert lib.pq_int8_gemm_g32(p16, 128, None, p16, 128, p16, None, p16, 0, 64, 8, 64, 128, None, 0, None) == 1
