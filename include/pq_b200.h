@@ -59,6 +59,8 @@ int pq_last_cuda_error(void);
  *   "gemm_pair"         0 = never use the CTA-pair kernel, 1 = automatic (default), 2 = whenever it is legal;
  *   "gemm_debug_timing" 1 = the CTA-pair kernel runs in its debug instantiation (the production kernel contains no
  *                       counters) and writes per-role cycle counters to workspace + 256 (needs ws_bytes >= 256 + 4096*64).
+ *   "g32_variant"       group-32 GEMM: bit 0 = eight epilogue warps instead of sixteen; bit 1 = scalar instead of packed
+ *                       fp32 operations; bit 3 = data path only (measurements; the output is meaningless).
  * Unknown keys return PQ_ERR_UNSUPPORTED.  Not part of the reference API. */
 int pq_set_option(const char* key, int value);
 int pq_get_option(const char* key, int* value);

@@ -1,13 +1,29 @@
 // Group-32 W8A8 GEMM for sm_100a:
 //   out[m,n] = sum_g s_a[m,g] * s_w[g,n] * (sum_{k in group g} xq[m,k] * w[n,k])  (+ bias[n])
-// A group is 32 consecutive K = exactly one tcgen05.mma kind::i8 instruction, so every instruction starts a
-// fresh int32 accumulator (exact per-group partial sum) in one of four tensor-memory slots (the four groups of
-// a 128-byte stage are issued back to back and handed over with one barrier); the epilogue warps drain each slot
-// and fold it into fp32 running sums in registers with one packed fused multiply-add per pair of
-// outputs: sum = fma(float(partial), s_a * s_w, sum).
-// The scale work (one multiply and one add per output element and group) is what bounds this kernel, not the
-// tensor pipe.  Roles and barriers mirror the per-channel GEMM: warp 0 TMA producer (operand stages plus a ring
-// of scale tiles), warp 1 MMA issuer, warps 2-9 epilogue.  Every wait is bounded.  No clusters, no multicast.
+// A group is 32 consecutive K = exactly one tcgen05.mma kind::i8 instruction, so every instruction produces the exact
+// int32 partial sum of one group in one of four 128-column tensor-memory slots; the epilogue warps drain the slots and
+// fold them into fp32 running sums in registers: sum = fma(float(partial), s_a * s_w, sum), ascending groups, the
+// arithmetic of the CPU restatement (bit-equal outputs).
+//
+// Two things bound the kernel, and neither is the tensor pipe (under 10 % busy):
+//  * every partial sum crosses from tensor memory to registers, 64 KB per 128 x 128 tile and group, at about 140 bytes
+//    per clock and SM (measured with the arithmetic removed);
+//  * a conversion, a product of the two scales and a fused multiply-add per output element and group.  The conversion
+//    is the hardware one (cvt.rn.f32.s32): it issues on the integer pipe and leaves the fp32 pipe to the two packed
+//    operations; converting with the add-a-magic-number trick puts three operations per element pair on the fp32 pipe
+//    and runs 10 % slower.
+// A thread owns four rows of an 8-column block pair (the tcgen05.ld 16x256b arrangement, two loads of 16 rows per group),
+// so one 8-byte shared-memory load of column scales serves eight outputs.  Sixteen epilogue warps (32 columns each) hide
+// the latency of the tensor-memory loads better than eight; within a slot pair the load of the next 16 rows is in flight
+// while the current ones are folded.  Slots are handed over in pairs, so the MMA thread refills one pair while the
+// warps work on the other.
+// Tried and dropped: a row-per-thread arrangement (tcgen05.ld 32x32b: the row scale becomes a register, but the loads
+// are no faster and the column scales need twice the shared-memory loads); accumulators pre-biased with 0x4B400000 so
+// that the int32 result read as fp32 bits needs only a subtraction (the tcgen05.st that restores the bias costs more
+// tensor-memory bandwidth than the integer additions it saves); keeping a load in flight across slot pairs, stages and
+// tiles (more live registers than the 96 per thread that 18 warps leave).
+// Roles: warp 0 TMA producer (operand stages plus a ring of scale tiles), warp 1 MMA issuer, warps 2.. epilogue.
+// Every wait is bounded.  No clusters, no multicast.
 #include <type_traits>
 
 #include "gemm_common.cuh"
@@ -17,14 +33,11 @@ namespace {
 
 constexpr int GBN = 128;                 // columns per tile = one tensor-memory slot
 constexpr int kSlots = 4;
+constexpr int kSlotPairs = 2;
 constexpr int kG32Stages = 4;
 constexpr int kGroupsPerStage = BK / 32;  // 4
-constexpr int kG32EpiWarps = 8;          // two per tensor-memory lane quarter (16 measured the same: not latency-bound)
-constexpr int kColW = GBN / (kG32EpiWarps / 4);   // columns of the tile per epilogue warp (64)
-constexpr int kNB = kColW / 8;           // 8-column blocks per warp
-constexpr int kG32Threads = 64 + 32 * kG32EpiWarps;
+constexpr int g32_threads(int ew) { return 64 + 32 * ew; }
 
-// 16 lanes x (8 x NB) columns of tensor memory -> 4 x NB registers per thread
 __device__ __forceinline__ void tmem_ld_cols(uint32_t addr, uint32_t (&v)[32]) { tmem_ld_16x256b_x8(addr, v); }
 __device__ __forceinline__ void tmem_ld_cols(uint32_t addr, uint32_t (&v)[16]) { tmem_ld_16x256b_x4(addr, v); }
 
@@ -47,25 +60,30 @@ struct G32Smem {
   static constexpr int kScaleBytes = kSaBytes + kSwBytes;
   static constexpr int kScaleOff = kG32Stages * kStageBytes;
   static constexpr int kBarOff = kScaleOff + kG32Stages * kScaleBytes;
-  static constexpr int kNumBars = 4 * kG32Stages + 2 * kSlots;
+  static constexpr int kNumBars = 4 * kG32Stages + 2 * kSlotPairs;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kDynamic = kMiscOff + 16 + 1024;
 };
 
-template <typename OutT>
-__global__ void __launch_bounds__(kG32Threads, 1)
+// EW epilogue warps; ARITH = false replaces the scale arithmetic by a plain sum (measurement of the data path only, the
+// output is then meaningless); PACKED = false uses scalar instead of packed fp32 operations.
+template <typename OutT, int EW, bool ARITH, bool PACKED>
+__global__ void __launch_bounds__(g32_threads(EW), 1)
 pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                         const __grid_constant__ CUtensorMap tmSa, const __grid_constant__ CUtensorMap tmSw,
                         const G32Params p) {
   using L = G32Smem;
+  static_assert(EW == 8 || EW == 16, "eight or sixteen epilogue warps");
+  constexpr int kColW = GBN / (EW / 4);       // columns of the tile per epilogue warp: 64 or 32
+  constexpr int kNB = kColW / 8;              // 8-column blocks per warp: 8 or 4
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* empty_bar = full_bar + kG32Stages;
   uint64_t* sfull_bar = empty_bar + kG32Stages;
   uint64_t* sempty_bar = sfull_bar + kG32Stages;
-  uint64_t* slot_full = sempty_bar + kG32Stages;
-  uint64_t* slot_empty = slot_full + kSlots;
+  uint64_t* slot_full = sempty_bar + kG32Stages;      // [pair]
+  uint64_t* slot_empty = slot_full + kSlotPairs;      // [pair]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
 
@@ -80,9 +98,9 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmSa); tma_prefetch_desc(&tmSw);
     for (int s = 0; s < kG32Stages; ++s) {
       mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1);
-      mbar_init(&sfull_bar[s], 1); mbar_init(&sempty_bar[s], kG32EpiWarps);
+      mbar_init(&sfull_bar[s], 1); mbar_init(&sempty_bar[s], EW);
     }
-    for (int s = 0; s < kSlots; ++s) { mbar_init(&slot_full[s], 1); mbar_init(&slot_empty[s], kG32EpiWarps); }
+    for (int s = 0; s < kSlotPairs; ++s) { mbar_init(&slot_full[s], 1); mbar_init(&slot_empty[s], EW); }
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -133,7 +151,7 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc_i8(BM, GBN);
       int stage = 0; uint32_t phase = 0; bool ok = true;
-      uint32_t gc = 0;                                // stages issued so far
+      uint32_t uses = 0;                              // stages issued so far = uses of either slot pair
       TileWalker w; w.init(p.sched_pm, p.sched_pn, mt_total, nt);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance()) {
@@ -146,118 +164,126 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           const uint32_t a_addr = smem_u32(smem + stage * L::kStageBytes);
           const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
           const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + L::kABytes);
-          // the four groups of a stage go to the four slots back to back; one "slots free" wait and one "slots
-          // written" commit per stage (every barrier operation costs this thread a few hundred cycles)
-          if (!wait_or_abort(&slot_empty[0], (gc & 1u) ^ 1u, abort_flag)) {
-            report_timeout(p.status, 2, 2); *abort_flag = 1; ok = false; break;
-          }
-          tc_fence_after();
 #pragma unroll
-          for (int g = 0; g < kGroupsPerStage; ++g)
-            tc_mma_i8(tmem_base + g * GBN, a_desc + static_cast<uint64_t>(2 * g), b_desc + static_cast<uint64_t>(2 * g),
-                      idesc, 0u);
-          tc_commit(&slot_full[0]);
-          ++gc;
-          if (ok) tc_commit(&empty_bar[stage]);
+          for (int pr = 0; pr < kSlotPairs; ++pr) {
+            // the epilogue's initial hand-over is completion 0 of slot_empty: use n of a pair waits for completion n
+            if (!wait_or_abort(&slot_empty[pr], uses & 1u, abort_flag)) {
+              report_timeout(p.status, 2, 2); *abort_flag = 1; ok = false; break;
+            }
+            tc_fence_after();
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int g = 2 * pr + j;
+              tc_mma_i8(tmem_base + g * GBN, a_desc + static_cast<uint64_t>(2 * g), b_desc + static_cast<uint64_t>(2 * g),
+                        idesc, 0u);
+            }
+            tc_commit(&slot_full[pr]);
+          }
+          if (!ok) break;
+          ++uses;
+          tc_commit(&empty_bar[stage]);
           if (++stage == kG32Stages) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..)
+    // A stage is eight chunks: chunk k = rows [16 (k & 1), +16) of this warp's lane quarter, group k >> 1, slot pair
+    // k >> 2.  Chunks alternate between two register buffers; inside a slot pair the load of chunk k + 1 is issued as
+    // soon as chunk k has landed and stays in flight while chunk k is folded.  A slot pair is handed back to the MMA
+    // thread as soon as its last chunk is in registers (before that chunk is folded).
     const int quarter = warp & 3;              // tensor-memory lanes [32*quarter, +32)
     const int colg = (warp - 2) >> 2;          // columns [kColW*colg, +kColW) of the tile
-    auto ld_cols = [](uint32_t addr, uint32_t (&v)[4 * kNB]) { tmem_ld_cols(addr, v); };
     const int g4 = lane >> 2, q = lane & 3;
     OutT* out = static_cast<OutT*>(p.out);
     const bool vec_store = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     bool aborted = false;
     int stage = 0; uint32_t phase = 0;
-    uint32_t gc = 0;
+    uint32_t uses = 0;
+    // lanes [32 quarter + 16 h, +16), this warp's columns, of slot g
+    auto slot_addr = [&](int g, int h) {
+      return tmem_base + static_cast<uint32_t>(g * GBN + colg * kColW) + (static_cast<uint32_t>(quarter * 32 + h * 16) << 16);
+    };
+    // the slots start out free
+    if (lane == 0) { mbar_arrive(&slot_empty[0]); mbar_arrive(&slot_empty[1]); }
+
     TileWalker w; w.init(p.sched_pm, p.sched_pn, mt_total, nt);
 #pragma unroll 1
-    for (; w.valid(); w.advance()) {
+    for (; w.valid() && !aborted; w.advance()) {
       const int row0 = w.mt * BM, n0 = w.ntile * GBN;
-      // y[mb][nb][0] = (row g4, cols 2q, 2q+1), y[mb][nb][1] = (row g4 + 8, same cols) of n8 block nb, 16-row block mb
+      // y[h][nb][0] = (row 16 h + g4, cols 2q, 2q+1 of 8-column block nb), y[h][nb][1] = same columns, row + 8
       float2 y[2][kNB][2];
 #pragma unroll
-      for (int mb = 0; mb < 2; ++mb)
+      for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int nb = 0; nb < kNB; ++nb) { y[mb][nb][0] = make_float2(0.f, 0.f); y[mb][nb][1] = make_float2(0.f, 0.f); }
+        for (int nb = 0; nb < kNB; ++nb) { y[h][nb][0] = make_float2(0.f, 0.f); y[h][nb][1] = make_float2(0.f, 0.f); }
 
 #pragma unroll 1
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = 0; kb < num_kb && !aborted; ++kb) {
         const float* sa_s = reinterpret_cast<const float*>(smem + L::kScaleOff + stage * L::kScaleBytes);
         const float* sw_s = sa_s + BM * kGroupsPerStage;
-        if (!aborted) {
+        {
           const bool landed = wait_or_abort(&sfull_bar[stage], phase, abort_flag);
-          if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 4); *abort_flag = 1; aborted = true; }
+          if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 4); *abort_flag = 1; aborted = true; break; }
         }
-        if (!aborted) {
-          const bool landed = wait_or_abort(&slot_full[0], gc & 1u, abort_flag);
-          if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 3); *abort_flag = 1; aborted = true; }
-        }
-        ++gc;
-        if (!aborted) tc_fence_after();
+        // row scales of this thread's four rows (g4 + 8 r) sit at sa_row[8 r * 4 + group]
+        const float* sa_row = sa_s + (quarter * 32 + g4) * kGroupsPerStage;
         uint32_t va[4 * kNB], vb[4 * kNB];
-        if (!aborted) {
-          const uint32_t t0_acc = tmem_base + colg * kColW;
-          ld_cols(t0_acc + (static_cast<uint32_t>(quarter * 32) << 16), va);
-        }
-#pragma unroll 1
-        for (int g = 0; g < kGroupsPerStage; ++g) {
-          if (aborted) continue;
-          const uint32_t t_acc = tmem_base + g * GBN + colg * kColW;
-          const float2 kNegMagic2 = make_float2(-12582912.0f, -12582912.0f);
-          // |partial| <= 32 * 127^2 < 2^22: adding the bit pattern of 1.5 * 2^23 converts exactly
-          auto cvt2 = [&](uint32_t a, uint32_t b) {
-            return __fadd2_rn(make_float2(__int_as_float(0x4B400000 + static_cast<int32_t>(a)),
-                                          __int_as_float(0x4B400000 + static_cast<int32_t>(b))), kNegMagic2);
-          };
-          const float* swg = sw_s + g * GBN + colg * kColW + 2 * q;
-          // row scales of this thread's four rows for this group (shared memory tile [128 rows][4 groups])
-          const float* sag = sa_s + (quarter * 32 + g4) * kGroupsPerStage + g;
-          tc_wait_ld();                                                       // rows 0..15 of group g are in va
-          ld_cols(t_acc + (static_cast<uint32_t>(quarter * 32 + 16) << 16), vb);
-          {
-            const float saA = sag[0], saB = sag[8 * kGroupsPerStage];
 #pragma unroll
-            for (int nb = 0; nb < kNB; ++nb) {
-              const float2 sw2 = *reinterpret_cast<const float2*>(swg + nb * 8);
-              // same arithmetic as the CPU restatement: running sum = fma(partial, s_a * s_w, running sum)
-              y[0][nb][0] = __ffma2_rn(cvt2(va[4 * nb + 0], va[4 * nb + 1]), __fmul2_rn(make_float2(saA, saA), sw2), y[0][nb][0]);
-              y[0][nb][1] = __ffma2_rn(cvt2(va[4 * nb + 2], va[4 * nb + 3]), __fmul2_rn(make_float2(saB, saB), sw2), y[0][nb][1]);
-            }
+        for (int k = 0; k < 8; ++k) {
+          const int g = k >> 1, h = k & 1, pr = k >> 2;
+          uint32_t (&v)[4 * kNB] = h == 0 ? va : vb;
+          uint32_t (&vnext)[4 * kNB] = h == 0 ? vb : va;
+          if ((k & 3) == 0) {                                        // first chunk of a pair: the MMAs have completed
+            const bool landed = wait_or_abort(&slot_full[pr], uses & 1u, abort_flag);
+            if (!__all_sync(0xffffffffu, landed)) { report_timeout(p.status, 3, 3); *abort_flag = 1; aborted = true; break; }
+            tc_fence_after();
+            tmem_ld_cols(slot_addr(g, 0), v);
           }
-          tc_wait_ld();                                                       // rows 16..31 of group g are in vb
-          if (g + 1 < kGroupsPerStage) {
-            ld_cols(t_acc + GBN + (static_cast<uint32_t>(quarter * 32) << 16), va);
+          tc_wait_ld();                                              // chunk k is in v
+          if ((k & 3) == 3) {                                        // the pair is in registers: hand it back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&slot_empty[pr]);
           } else {
-            tc_fence_before();                                                // all four slots are in registers:
-            __syncwarp();                                                     // the MMA thread may refill them
-            if (lane == 0) mbar_arrive(&slot_empty[0]);
+            tmem_ld_cols(slot_addr((k + 1) >> 1, (k + 1) & 1), vnext);   // on its way while chunk k is folded
           }
-          {
-            const float saA = sag[16 * kGroupsPerStage], saB = sag[24 * kGroupsPerStage];
+          const float sa_lo = sa_row[(16 * h) * kGroupsPerStage + g], sa_hi = sa_row[(16 * h + 8) * kGroupsPerStage + g];
+          const float* swp = sw_s + g * GBN + colg * kColW + 2 * q;
 #pragma unroll
-            for (int nb = 0; nb < kNB; ++nb) {
-              const float2 sw2 = *reinterpret_cast<const float2*>(swg + nb * 8);
-              y[1][nb][0] = __ffma2_rn(cvt2(vb[4 * nb + 0], vb[4 * nb + 1]), __fmul2_rn(make_float2(saA, saA), sw2), y[1][nb][0]);
-              y[1][nb][1] = __ffma2_rn(cvt2(vb[4 * nb + 2], vb[4 * nb + 3]), __fmul2_rn(make_float2(saB, saB), sw2), y[1][nb][1]);
+          for (int nb = 0; nb < kNB; ++nb) {
+            // column scales: one 8-byte load per 8-column block serves the thread's two rows of this chunk
+            const float2 sw2 = *reinterpret_cast<const float2*>(swp + nb * 8);
+            const float2 pA = make_float2(__int2float_rn(static_cast<int32_t>(v[4 * nb + 0])), __int2float_rn(static_cast<int32_t>(v[4 * nb + 1])));
+            const float2 pB = make_float2(__int2float_rn(static_cast<int32_t>(v[4 * nb + 2])), __int2float_rn(static_cast<int32_t>(v[4 * nb + 3])));
+            if constexpr (!ARITH) {
+              y[h][nb][0] = __fadd2_rn(make_float2(__uint_as_float(v[4 * nb + 0]), __uint_as_float(v[4 * nb + 1])), y[h][nb][0]);
+              y[h][nb][1] = __fadd2_rn(make_float2(__uint_as_float(v[4 * nb + 2]), __uint_as_float(v[4 * nb + 3])), y[h][nb][1]);
+            } else if constexpr (PACKED) {
+              // same arithmetic as the CPU restatement: running sum = fma(partial, s_a * s_w, running sum)
+              y[h][nb][0] = __ffma2_rn(pA, __fmul2_rn(make_float2(sa_lo, sa_lo), sw2), y[h][nb][0]);
+              y[h][nb][1] = __ffma2_rn(pB, __fmul2_rn(make_float2(sa_hi, sa_hi), sw2), y[h][nb][1]);
+            } else {
+              y[h][nb][0].x = __fmaf_rn(pA.x, __fmul_rn(sa_lo, sw2.x), y[h][nb][0].x);
+              y[h][nb][0].y = __fmaf_rn(pA.y, __fmul_rn(sa_lo, sw2.y), y[h][nb][0].y);
+              y[h][nb][1].x = __fmaf_rn(pB.x, __fmul_rn(sa_hi, sw2.x), y[h][nb][1].x);
+              y[h][nb][1].y = __fmaf_rn(pB.y, __fmul_rn(sa_hi, sw2.y), y[h][nb][1].y);
             }
           }
         }
+        if (aborted) break;
+        ++uses;
         // scales of this stage consumed
         __syncwarp();
         if (lane == 0) mbar_arrive(&sempty_bar[stage]);
         if (++stage == kG32Stages) { stage = 0; phase ^= 1u; }
       }
-      if (aborted) continue;
+      if (aborted) break;
 
       // ---- bias, rounding, store
 #pragma unroll
-      for (int mb = 0; mb < 2; ++mb) {
-        const int rA = row0 + quarter * 32 + mb * 16 + g4;
+      for (int h = 0; h < 2; ++h) {
+        const int rA = row0 + quarter * 32 + h * 16 + g4;
         const int rB = rA + 8;
 #pragma unroll
         for (int grp = 0; grp < kColW / 32; ++grp) {
@@ -269,7 +295,7 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             float2 b2 = make_float2(0.f, 0.f);
             if (p.has_bias && col + 1 < p.N) b2 = *reinterpret_cast<const float2*>(p.bias + col);
             else if (p.has_bias && col < p.N) b2.x = p.bias[col];
-            const float2 a = __fadd2_rn(y[mb][nb][0], b2), b = __fadd2_rn(y[mb][nb][1], b2);
+            const float2 a = __fadd2_rn(y[h][nb][0], b2), b = __fadd2_rn(y[h][nb][1], b2);
             wA[j] = pack2(a.x, a.y, OutT{});
             wB[j] = pack2(b.x, b.y, OutT{});
           }
@@ -286,6 +312,7 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
       }
     }
+    tc_wait_ld();                                  // nothing of this warp may be in flight when tensor memory is freed
   }
 
   tc_fence_before();
@@ -299,14 +326,31 @@ pq_int8_gemm_g32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   }
 }
 
+template <typename OutT, int EW, bool ARITH, bool PACKED>
+int launch_g32_variant(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmSa, const CUtensorMap& tmSw,
+                       const G32Params& p, int grid, cudaStream_t st) {
+  auto kern = pq_int8_gemm_g32_kernel<OutT, EW, ARITH, PACKED>;
+  PQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G32Smem::kDynamic));
+  kern<<<grid, g32_threads(EW), G32Smem::kDynamic, st>>>(tmA, tmW, tmSa, tmSw, p);
+  PQ_CUDA_TRY(cudaGetLastError());
+  return PQ_OK;
+}
+
+// Option "g32_variant": bit 0 = eight epilogue warps (default sixteen); bit 1 = scalar instead of packed fp32
+// operations; bit 3 = data path only (no scale arithmetic: for measurements, output meaningless).
+template <typename OutT, int EW>
+int launch_g32_e(int v, const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmSa, const CUtensorMap& tmSw,
+                 const G32Params& p, int grid, cudaStream_t st) {
+  if (v & 8) return launch_g32_variant<OutT, EW, false, true>(tmA, tmW, tmSa, tmSw, p, grid, st);
+  if (v & 2) return launch_g32_variant<OutT, EW, true, false>(tmA, tmW, tmSa, tmSw, p, grid, st);
+  return launch_g32_variant<OutT, EW, true, true>(tmA, tmW, tmSa, tmSw, p, grid, st);
+}
 template <typename OutT>
 int launch_g32(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmSa, const CUtensorMap& tmSw,
                const G32Params& p, int grid, cudaStream_t st) {
-  auto kern = pq_int8_gemm_g32_kernel<OutT>;
-  PQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G32Smem::kDynamic));
-  kern<<<grid, kG32Threads, G32Smem::kDynamic, st>>>(tmA, tmW, tmSa, tmSw, p);
-  PQ_CUDA_TRY(cudaGetLastError());
-  return PQ_OK;
+  const int v = options().g32_variant;
+  if (v & 1) return launch_g32_e<OutT, 8>(v, tmA, tmW, tmSa, tmSw, p, grid, st);
+  return launch_g32_e<OutT, 16>(v, tmA, tmW, tmSa, tmSw, p, grid, st);
 }
 
 }  // namespace
