@@ -3,8 +3,9 @@
 Every output row depends only on its own input row (per-token scales are row-local,
 deploy/int8_exec.py:83-101) and on the weights, so the path shards by contiguous row blocks over the
 ranks of one node with replicated weights and no collective on the data path.  The only exchange is
-the OPTIONAL all-gather of the 16-bit outputs (NCCL over NVLink on GPUs, gloo on CPU in the tests).
-One process per GPU; rendezvous comes from the torchrun environment.
+the OPTIONAL all-gather of the 16-bit outputs (NCCL over NVLink on GPUs, gloo on CPU in the tests), either after
+the layer (`all_gather_rows`) or hidden behind it chunk by chunk (`OverlappedRowGather` with NCCL / gloo,
+`PeerPushGather` with the copy engines).  One process per GPU; rendezvous comes from the torchrun environment.
 """
 from __future__ import annotations
 
@@ -59,6 +60,133 @@ def all_gather_rows(y_local: torch.Tensor, M: int, group: Optional[dist.ProcessG
     full = y_local.new_empty((world * per, N))
     dist.all_gather_into_tensor(full, y_local.contiguous(), group=group)
     return full[:M]
+
+
+# ------------------------------------------------------------------------------------------------ overlapped gather
+def cyclic_block_rows(M: int, world: int, chunks: int) -> int:
+    """Rows per block when the M rows are dealt out block-cyclically: `chunks * world` blocks of equal height c (the
+    last ones short or empty), block j = rows [j c, (j + 1) c), owned by rank j % world."""
+    n = int(world) * int(chunks)
+    return (int(M) + n - 1) // n
+
+
+def cyclic_local_blocks(M: int, world: int, rank: int, chunks: int):
+    """[(start, stop)] of this rank's `chunks` blocks, in the order it processes them (block i of the rank is global
+    block i * world + rank); stops are clipped to M."""
+    c = cyclic_block_rows(M, world, chunks)
+    out = []
+    for i in range(chunks):
+        a = min(int(M), (i * world + rank) * c)
+        out.append((a, min(int(M), a + c)))
+    return out
+
+
+class OverlappedRowGather:
+    """All-gather of a row-parallel layer's outputs hidden behind its computation.
+
+    With contiguous row blocks per rank the gather can only start when the whole layer is done.  Here the rows are dealt
+    out block-cyclically instead (rows are independent, so any assignment is valid): the rank computes its block of chunk
+    i, hands it to an asynchronous all-gather (NCCL runs it on its own stream), and computes its block of chunk i + 1
+    meanwhile.  Chunk i of all ranks is the contiguous row range [i * world * c, (i + 1) * world * c) of the full output,
+    so every gather writes straight into its place and the result is in natural row order.
+
+    `forward(x_block) -> y_block` is the local layer; `run` takes either the full input (every rank slices its blocks as
+    views) or, with `local=True`, this rank's rows already laid out block after block ([chunks * c, K])."""
+
+    def __init__(self, M: int, N: int, dtype: torch.dtype, device, chunks: int = 4, group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.M, self.N, self.chunks = int(M), int(N), int(chunks)
+        self.c = cyclic_block_rows(M, self.world, chunks)
+        self.full = torch.empty((self.chunks * self.world * self.c, N), dtype=dtype, device=device)
+
+    def run(self, forward, x: torch.Tensor, local: bool = False, wait: bool = True) -> torch.Tensor:
+        """Computes and gathers; with wait=False the last gathers may still be in flight on return (the next layer then
+        computes behind them) and `finish()` must be called before the result is read."""
+        c, W = self.c, self.world
+        works = self._works = []
+        for i, (a, b) in enumerate(cyclic_local_blocks(self.M, W, self.rank, self.chunks)):
+            xb = x[i * c: i * c + (b - a)] if local else x[a:b]
+            dst = self.full[i * W * c: (i + 1) * W * c]
+            if b - a == c:
+                y = forward(xb)
+            else:                                   # short or empty block at the end of M: pad to the common height
+                y = self.full.new_zeros((c, self.N))
+                if b > a:
+                    y[: b - a] = forward(xb)
+            if W == 1:
+                dst.copy_(y)
+            else:
+                works.append(dist.all_gather_into_tensor(dst, y.contiguous(), group=self.group, async_op=True))
+        if wait:
+            self.finish()
+        return self.full[: self.M]
+
+    def finish(self) -> None:
+        for w in getattr(self, "_works", []):
+            w.wait()
+        self._works = []
+
+
+class PeerPushGather(OverlappedRowGather):
+    """The same overlapped gather with the GPUs' copy engines instead of NCCL kernels (CUDA, one node).
+
+    Every rank's full-size output buffer lives in torch's symmetric memory (`torch.distributed._symmetric_memory`: the
+    same allocation on every rank, each mapped into every peer's address space); a finished chunk is then WRITTEN into
+    every peer's buffer by plain device-to-device copies on side streams.  Copies between peer GPUs run on the DMA engines over NVLink, need no SM
+    and therefore overlap with the persistent GEMM, which NCCL's copy kernels cannot (they wait for SMs the GEMM holds
+    until it ends).  No kernel of this library ever reads a peer's memory.
+    Ordering: `run` ends with a stream-ordered all-reduce of one element after this rank's copies, so when it completes
+    on a rank, every peer's writes into that rank's buffer have completed; it starts with one as well, so that no peer
+    overwrites a buffer its owner may still be reading from the previous call."""
+
+    def __init__(self, M: int, N: int, dtype: torch.dtype, device, chunks: int = 4, group: Optional[dist.ProcessGroup] = None,
+                 copy_streams: int = 2):
+        super().__init__(M, N, dtype, device, chunks, group)
+        self.device = torch.device(device)
+        self.peers = [self.full] * self.world
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            shape = tuple(self.full.shape)
+            self.full = symm_mem.empty(shape, dtype=dtype, device=self.device)
+            self._handle = symm_mem.rendezvous(self.full, group=group if group is not None else dist.group.WORLD)
+            self.peers = [self.full if r == self.rank else self._handle.get_buffer(r, shape, dtype) for r in range(self.world)]
+        self.streams = [torch.cuda.Stream(self.device) for _ in range(max(1, copy_streams))]
+        self._token = torch.zeros(1, device=self.device)
+
+    def run(self, forward, x: torch.Tensor, local: bool = False, wait: bool = True) -> torch.Tensor:
+        c, W, r = self.c, self.world, self.rank
+        cur = torch.cuda.current_stream(self.device)
+        if W > 1:
+            dist.all_reduce(self._token, group=self.group)           # peers are done reading what the last call delivered
+        for st in self.streams:
+            st.wait_stream(cur)
+        for i, (a, b) in enumerate(cyclic_local_blocks(self.M, W, r, self.chunks)):
+            if b <= a:
+                continue
+            xb = x[i * c: i * c + (b - a)] if local else x[a:b]
+            y = forward(xb)
+            done = torch.cuda.Event(); done.record(cur)
+            row = (i * W + r) * c
+            for k in range(W):                                       # farthest peers first is of no use on a switch: round robin
+                peer = (r + k) % W
+                st = self.streams[k % len(self.streams)]
+                st.wait_event(done)
+                with torch.cuda.stream(st):
+                    self.peers[peer][row: row + (b - a)].copy_(y, non_blocking=True)
+            for st in self.streams:
+                y.record_stream(st)
+        if wait:
+            self.finish()
+        return self.full[: self.M]
+
+    def finish(self) -> None:
+        cur = torch.cuda.current_stream(self.device)
+        for st in self.streams:
+            cur.wait_stream(st)
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)           # every rank's copies are behind its all-reduce
 
 
 class RowShardedLinear(torch.nn.Module):

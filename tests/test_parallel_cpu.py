@@ -38,6 +38,19 @@ def _worker(rank, world, port, M, ret):
         def forward(self, x):
             return oracle.int8_linear_forward(x, wq, ws, L["bias"], L["lr_A"], L["lr_B"])
 
+    # chunked, overlapped gather over block-cyclic rows: same result, natural row order
+    for chunks in (1, 3, 4):
+        og = parallel.OverlappedRowGather(M, 64, L["x"].dtype, "cpu", chunks=chunks)
+        got = og.run(Lin(), L["x"])
+        assert torch.equal(got, Lin()(L["x"])), chunks
+        blocks = parallel.cyclic_local_blocks(M, world, rank, chunks)
+        xl = torch.cat([L["x"][a:b] for a, b in blocks] + [L["x"][:0]])
+        c = parallel.cyclic_block_rows(M, world, chunks)
+        xpad = torch.zeros(chunks * c, xl.shape[1], dtype=xl.dtype)
+        off = 0
+        for i, (a, b) in enumerate(blocks):
+            xpad[i * c: i * c + (b - a)] = L["x"][a:b]
+        assert torch.equal(og.run(Lin(), xpad, local=True), Lin()(L["x"])), chunks
     full = parallel.RowShardedLinear(Lin(), gather=True)(L["x"])
     local = parallel.RowShardedLinear(Lin(), gather=False)(L["x"])
     want = Lin()(L["x"])
@@ -49,6 +62,22 @@ def _worker(rank, world, port, M, ret):
         ret.put(float(t.item()))
     dist.barrier()
     dist.destroy_process_group()
+
+
+def test_cyclic_blocks_cover_rows_once():
+    for M in (0, 1, 7, 66, 67, 66048, 66049):
+        for world in (1, 2, 4, 8):
+            for chunks in (1, 3, 4):
+                c = parallel.cyclic_block_rows(M, world, chunks)
+                seen = []
+                for r in range(world):
+                    blocks = parallel.cyclic_local_blocks(M, world, r, chunks)
+                    assert len(blocks) == chunks and all(0 <= b - a <= c for a, b in blocks)
+                    seen += [(a, b) for a, b in blocks if b > a]
+                seen.sort()
+                assert (not seen and M == 0) or (seen[0][0] == 0 and seen[-1][1] == M)
+                assert all(seen[i][1] == seen[i + 1][0] for i in range(len(seen) - 1))
+    assert parallel.cyclic_block_rows(66048, 8, 4) == 2064
 
 
 def test_two_rank_gloo_sharded_forward_and_gather():
