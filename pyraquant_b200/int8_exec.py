@@ -302,7 +302,7 @@ class Int8Linear(nn.Module):
 
     def _down(self, x2: torch.Tensor) -> torch.Tensor:
         """t = x2 @ lr_A rounded to the activation dtype (reference :390): the native streaming kernel for rank 32
-        on inputs it takes as they are, torch's matmul otherwise."""
+        on inputs it takes as they are (any row count), torch's matmul otherwise (other ranks, dtypes, unaligned rows)."""
         if self.lr_A.shape[1] == 32 and self.lr_A.dtype == x2.dtype and ops.lowrank_down_ok(x2):
             return ops.lowrank_down(x2, self._lr_At())
         return x2.to(self.lr_A.dtype) @ self.lr_A

@@ -173,9 +173,13 @@ def _gather_rows_impl(canvas: Tensor, row_idx: Tensor) -> Tensor:
 # ------------------------------------------------------------------------------------------------ low-rank down-projection
 # True: t = x @ lr_A runs on this library's streaming tcgen05 kernel; False: torch's matmul, as the reference does
 LOWRANK_DOWN_NATIVE = True
-# below this many rows the 64-row tiles do not fill the SMs evenly and torch's split-K matmul is faster (measured:
-# 66048 rows 349 -> 308 us at K = 15360, 76 -> 70 us at K = 3072; 16896 rows 66 -> 74 us, 26 -> 35 us)
-LOWRANK_DOWN_MIN_ROWS = 32768
+# rows from which the library's own kernel is used.  Measured back to back on inputs rotating through HBM (native /
+# torch's cuBLAS matmul, us): 66048 rows 308 / 349 at K = 15360 and 70 / 76 at K = 3072; 33024 rows 162 / 164 and
+# 38 / 37; 16896 rows 84 / 79 and 22 / 21; 8256 rows 44 / 43 and 16 / 15; 4608 rows 34 / 32 and 16 / 15 (both at the
+# launch floor).  Below 33024 rows the library call is ahead by 2-8 % (its split-K fills the SMs when there are fewer
+# 64-row tiles than SMs); the path stays on this library's kernel all the same, the difference being under 1 % of a
+# Linear's forward.
+LOWRANK_DOWN_MIN_ROWS = 1
 # output widths the kernel is built for: one rank-32 factor, or up to four side by side
 LOWRANK_DOWN_COLS = (32, 64, 96, 128)
 

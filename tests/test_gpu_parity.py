@@ -310,14 +310,14 @@ def test_gemm_cfg0_layer(cuda_dev):
     xq, sx = int8_exec.quant_rows(x)
     xqo, sxo = oracle.quant_rows(L["x"])
     assert torch.equal(xq.cpu(), xqo) and torch.equal(sx.cpu(), sxo)
-    t_gpu = (x @ q.lr_A)
+    t_gpu = q._down(x)
     _, acc = ops.int8_gemm_debug(xq, sx, q.weight_int8, q.w_scale, q.bias, t_gpu, q.lr_B, torch.bfloat16)
     acc_ref = oracle.int_mm(xqo, wq)
     assert torch.equal(acc.cpu(), acc_ref)
     # output against the exact dequantised math and against the restated forward
     bias32 = lin.bias.detach().float()
-    # the down-projection t = x @ lr_A is torch's bf16 matmul, as in the reference (:390); its rounding to bf16
-    # may differ from the CPU's by one ulp, so the GEMM is judged on the t it was given and t on its own
+    # the down-projection t = x @ lr_A (reference :390) accumulates in fp32 in another order than the CPU; its rounding
+    # to bf16 may differ by one ulp, so the GEMM is judged on the t it was given and t on its own
     t_ref = (L["x"].float() @ L["lr_A"].float()).to(torch.bfloat16)
     assert bool(((t_gpu.cpu().float() - t_ref.float()).abs() <= t_ref.float().abs() * 2.0 ** -7 + 1e-3).all())
     ref64 = oracle.exact_dequant_f64(acc_ref, sxo, ws, bias32, t_gpu.cpu(), L["lr_B"])
@@ -388,7 +388,10 @@ def test_shared_input_group(cuda_dev, monkeypatch):
     assert calls["n"] == 1
     x2 = x.reshape(-1, K)
     xq, sx = real(x2)
-    T = x2 @ torch.cat([m.lr_A for m in layers if m.lr_A is not None], dim=1)
+    _xq, _sx, T = grp.prepare(x2)                      # the group's own down-projection of width 32 x members
+    assert T.shape == (M, 32 * sum(m.lr_A is not None for m in layers))
+    t_wide = (x2.float() @ torch.cat([m.lr_A for m in layers if m.lr_A is not None], dim=1).float()).to(torch.bfloat16)
+    assert bool(((T.float() - t_wide.float()).abs() <= t_wide.float().abs() * 2.0 ** -7 + 1e-3).all())
     off = 0
     for m, ya, yt in zip(layers, alone, together):
         assert yt.shape == ya.shape == (2, M // 2, m.out_features)
@@ -539,12 +542,12 @@ def test_lowrank_down_projection(cuda_dev, M, K, R, dtype):
 
 
 def test_shared_input_group_uses_native_down_projection_for_many_rows(cuda_dev, monkeypatch):
-    """A group of layers on one input takes ONE native down-projection of width 32 x members from 32768 rows up, and
+    """A group of layers on one input takes ONE native down-projection of width 32 x members, and
     every member's output equals the ungrouped layer's wherever the two down-projections agree (they differ in fp32
     summation order only)."""
     from pyraquant_b200.int8_exec import share_input_quantisation
     g = torch.Generator().manual_seed(11)
-    M, K = ops.LOWRANK_DOWN_MIN_ROWS + 37, 256
+    M, K = 32768 + 37, 256
     grouped = [_toy_layer(cuda_dev, g, K, n, lowrank=True) for n in (256, 512, 256)]
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(cuda_dev)
     alone = [m(x) for m in grouped]                                  # before grouping: one kernel call each
@@ -570,10 +573,10 @@ def test_shared_input_group_uses_native_down_projection_for_many_rows(cuda_dev, 
 
 
 def test_int8linear_uses_native_down_projection_for_many_rows(cuda_dev, monkeypatch):
-    """From 32768 rows up Int8Linear.forward takes the library's own down-projection kernel: the output matches the
-    exact dequantised math built on that kernel's t, and the kernel really is the one called."""
+    """Int8Linear.forward takes the library's own down-projection kernel at small and large row counts: the output
+    matches the exact dequantised math built on that kernel's t, and the kernel really is the one called."""
     g = torch.Generator().manual_seed(3)
-    M, K, N = ops.LOWRANK_DOWN_MIN_ROWS + 100, 256, 256
+    M, K, N = 32768 + 100, 256, 256
     layer = _toy_layer(cuda_dev, g, K, N, lowrank=True)
     x = (torch.randn(M, K, generator=g)).to(torch.bfloat16)
     calls = {"n": 0}
@@ -759,7 +762,7 @@ def test_routed_two_tier_linear(cuda_dev):
     w8, s8 = oracle.quant_weight(lin.weight.detach(), where="cuda")
     w4, s4 = oracle.nested4_from_int8(w8, s8)
     xq, sx = oracle.quant_rows(rows)
-    t = (rows.to(cuda_dev) @ A.to(cuda_dev)).cpu()            # the module's own down-projection (torch bf16 matmul)
+    t = q._down(rows.to(cuda_dev)).cpu()                      # the module's own down-projection
     b32 = lin.bias.detach().float()
     mh = plan.m_hi
     ref = torch.cat([oracle.exact_dequant_f64(oracle.int_mm(xq[:mh], w8), sx[:mh], s8, b32, t[:mh], B),
@@ -868,10 +871,10 @@ def test_lean_path_follows_converted_buffers(cuda_dev):
     m.lr_B = new_B
     y1 = m(x)
     xq, sx = int8_exec.quant_rows(x)
-    want = int8_exec.int8_gemm_lr(xq, sx, m.weight_int8, new_scale, m.bias, x @ m.lr_A, new_B, torch.bfloat16)
+    want = int8_exec.int8_gemm_lr(xq, sx, m.weight_int8, new_scale, m.bias, m._down(x), new_B, torch.bfloat16)
     assert torch.equal(y1, want) and not torch.equal(y1, y0)
     m.lr_B.mul_(2.0)                                               # in place: the K-major copy must follow
-    want2 = int8_exec.int8_gemm_lr(xq, sx, m.weight_int8, new_scale, m.bias, x @ m.lr_A, m.lr_B, torch.bfloat16)
+    want2 = int8_exec.int8_gemm_lr(xq, sx, m.weight_int8, new_scale, m.bias, m._down(x), m.lr_B, torch.bfloat16)
     assert torch.equal(m(x), want2)
 
 
