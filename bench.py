@@ -530,18 +530,24 @@ def main_ours(args):
     else:
         peak = DATASHEET_INT8_TOPS
         basis = "datasheet dense INT8 figure (the measured ceiling was skipped in this run)"
-    # DRAM traffic of the GEMM launches of one step: linear fit (bytes = a + b * rows) through two ncu captures of the
-    # same kernel at 8192 and 16384 rows, from the committed summary; the weights' share does not grow with the rows
+    # DRAM traffic of the GEMM launches of one step, from ncu captures of the same kernel at 8192, 16384 and 66048 rows
+    # (committed summary), interpolated linearly between the captured row counts; it does not grow in proportion to the
+    # rows (the weights' share and the number of sweeps over the activations change with them)
     traffic = None
     tp = ROOT / "profiles" / "gemm_fused_pair_flux4k_rows8192_full.md"
     if tp.exists():
-        fit = {}
+        pts = {}
         for ln in tp.read_text().splitlines():
-            if ln.startswith("TRAFFIC_FIT"):
-                _tag, name, a0, b1 = ln.split()
-                fit[name] = (float(a0), float(b1))
-        if all(n in fit for n, _K, _N in LAYERS):
-            traffic = sum(fit[n][0] + fit[n][1] * rows for n, _K, _N in LAYERS)
+            if ln.startswith("TRAFFIC_POINT"):
+                _tag, name, r_, b_ = ln.split()
+                pts.setdefault(name, []).append((float(r_), float(b_)))
+        if all(len(pts.get(n, [])) >= 2 for n, _K, _N in LAYERS):
+            def at(points, r):
+                points = sorted(points)
+                for (r0, b0), (r1, b1) in zip(points, points[1:]):
+                    if r <= r1 or (r1, b1) == points[-1]:
+                        return b0 + (b1 - b0) * (r - r0) / (r1 - r0)
+            traffic = sum(at(pts[n], float(rows)) for n, _K, _N in LAYERS)
     min_bytes = sum(rows * K + N * K + 2.0 * rows * N + 64.0 * (rows + N) for _n, K, N in LAYERS)
     line = {
         "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -555,7 +561,8 @@ def main_ours(args):
                             "ordinary channels quantise to a few units around zero (kernels[].mean_abs_code); tensor-core "
                             "power and with it the sustained clock depend on the data, see kernels[].gemm_full_range_codes_*"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOPS", "frac": achieved / peak,
-                     "traffic": traffic, "traffic_basis": "linear fit in the rows through ncu captures at 8192 and 16384 rows",
+                     "traffic": traffic, "traffic_basis": "ncu dram__bytes_read + dram__bytes_write of the two GEMM launches, captured at 8192, 16384 and 66048 "
+                                                         "rows and interpolated to this launch's rows",
                      "algorithmic_min_bytes": min_bytes,
                      "kernel": "pq_int8_gemm_fused_pair_kernel (both launches of a step)",
                      "peak_basis": basis,
