@@ -613,19 +613,33 @@ def main_other(args) -> None:
     peaks = measured_peaks()
     g = torch.Generator(device=dev).manual_seed(1)
 
+    BURST = 4
+
     def interleaved(items, reps):
-        """items: list of (name, fn); returns {name: median microseconds} with the repetitions interleaved."""
+        """items: list of (name, fn); fn takes a call counter (to rotate between input copies).  Returns {name: median
+        microseconds per call}; the repetitions of the items are interleaved.  Each measurement is a burst of BURST calls
+        back to back between two events: the host enqueues the next launch while the previous one runs, so that the
+        host-side cost of a call (5-15 us) is not mistaken for device time of kernels that take 15-50 us."""
+        n = 0
         for _n, fn in items:
-            fn(); fn()
-        ev = {n: [] for n, _ in items}
+            fn(0); fn(1)
+        ev = {name: [] for name, _ in items}
         torch.cuda.synchronize()
         for _ in range(reps):
-            for n, fn in items:
+            for name, fn in items:
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(); fn(); b.record()
-                ev[n].append((a, b))
-        torch.cuda.synchronize()
-        return {n: statistics.median(a.elapsed_time(b) for a, b in v) * 1e3 for n, v in ev.items()}
+                a.record()
+                for _j in range(BURST):
+                    fn(n); n += 1
+                b.record()
+                ev[name].append((a, b))
+            torch.cuda.synchronize()
+        return {name: statistics.median(a.elapsed_time(b) for a, b in v) * 1e3 / BURST for name, v in ev.items()}
+
+    def copies(x, total_bytes):
+        """Enough copies of x that rotating through them defeats L2 (the working set of the copies exceeds 3 x L2)."""
+        k = max(1, min(6, int(3 * 126e6 // max(1, total_bytes)) + 1))
+        return [x] + [x.clone() for _ in range(k - 1)]
 
     def act(M, K, dtype):
         x = torch.randn(M, K, generator=g, device=dev)
@@ -649,7 +663,8 @@ def main_other(args) -> None:
         """--shape MxKxN restricts the SDXL workloads to one layer (profiler captures)."""
         return args.shape is None or args.shape == f"{M}x{K}x{N}"
 
-    out = {"workload": args.workload, "n_gpus": 1, "unit_time": "us (median of interleaved repetitions)", "reps": reps,
+    out = {"workload": args.workload, "n_gpus": 1,
+           "unit_time": f"us per call (median over interleaved repetitions of bursts of {BURST} back-to-back calls)", "reps": reps,
            "data": "synthetic", "items": []}
     if args.workload == "flux2k":
         M = 16384 + 512
@@ -658,14 +673,17 @@ def main_other(args) -> None:
             x = act(M, K, torch.bfloat16)
             xq, sx = int8_exec.quant_rows(x)
             t = x @ m.lr_A
-            r = interleaved([("forward", lambda: m(x)), ("quant", lambda: int8_exec.quant_rows(x)),
-                             ("gemm", lambda: int8_exec.int8_gemm_lr(xq, sx, m.weight_int8, m.w_scale, m.bias, t, m.lr_B,
-                                                                     torch.bfloat16, m._lr_Bt()))], reps)
+            xc = copies(x, 3 * M * K)
+            r = interleaved([("forward", lambda i: m(xc[i % len(xc)])), ("quant", lambda i: int8_exec.quant_rows(xc[i % len(xc)])),
+                             ("down", lambda i: m._down(xc[i % len(xc)])),
+                             ("gemm", lambda i: int8_exec.int8_gemm_lr(xq, sx, m.weight_int8, m.w_scale, m.bias, t, m.lr_B,
+                                                                       torch.bfloat16, m._lr_Bt()))], reps)
             opsn = 2.0 * M * K * N
             out["items"].append({"layer": f"{K}->{N}", "rows": M, "forward_us": r["forward"], "forward_tops": opsn / r["forward"] / 1e6,
                                  "gemm_us": r["gemm"], "gemm_tops": opsn / r["gemm"] / 1e6, "quant_us": r["quant"],
-                                 "quant_gbs": (3.0 * M * K + 4 * M) / r["quant"] / 1e3})
-            del m, x, xq, sx, t
+                                 "quant_gbs": (3.0 * M * K + 4 * M) / r["quant"] / 1e3,
+                                 "lowrank_down_us": r["down"], "lowrank_down_gbs": 2.0 * M * K / r["down"] / 1e3})
+            del m, x, xq, sx, t, xc
     elif args.workload == "sdxl_pc":
         # the reference's SDXL deployment arm: per-channel weights, per-token activations, fp16, no low-rank branch
         # (deploy/run_sdxl_latency.py:214-224, shapes :280)
@@ -679,14 +697,15 @@ def main_other(args) -> None:
             m = int8_exec.Int8Linear(lin, device=dev)
             x = torch.randn(M, K, generator=g, device=dev).to(torch.float16)
             xq, sx = int8_exec.quant_rows(x)
-            r = interleaved([("forward", lambda: m(x)), ("quant", lambda: int8_exec.quant_rows(x)),
-                             ("gemm", lambda: int8_exec.int8_gemm_fused(xq, sx, m.weight_int8, m.w_scale, m.bias, torch.float16)),
-                             ("fp16", lambda: torch.nn.functional.linear(x, lin.weight, lin.bias))], reps)
+            xc = copies(x, 3 * M * K)
+            r = interleaved([("forward", lambda i: m(xc[i % len(xc)])), ("quant", lambda i: int8_exec.quant_rows(xc[i % len(xc)])),
+                             ("gemm", lambda i: int8_exec.int8_gemm_fused(xq, sx, m.weight_int8, m.w_scale, m.bias, torch.float16)),
+                             ("fp16", lambda i: torch.nn.functional.linear(xc[i % len(xc)], lin.weight, lin.bias))], reps)
             opsn = 2.0 * M * K * N
             out["items"].append({"layer": f"{K}->{N}", "rows": M, "forward_us": r["forward"], "forward_tops": opsn / r["forward"] / 1e6,
                                  "gemm_us": r["gemm"], "gemm_tops": opsn / r["gemm"] / 1e6, "quant_us": r["quant"],
                                  "quant_gbs": (3.0 * M * K + 4 * M) / r["quant"] / 1e3, "torch_fp16_linear_us": r["fp16"]})
-            del m, x, lin, xq, sx
+            del m, x, lin, xq, sx, xc
     elif args.workload == "sdxl_g32":
         for M, K, N in ((65536, 640, 640), (65536, 640, 5120), (65536, 2560, 640), (16384, 1280, 1280), (16384, 1280, 10240),
                         (16384, 5120, 1280)):
@@ -697,13 +716,14 @@ def main_other(args) -> None:
                 lin.weight.copy_(torch.randn(N, K, generator=g, device=dev) * 0.02)
             m = int8_exec.Int8LinearG32(lin, device=dev)
             x = torch.randn(M, K, generator=g, device=dev).to(torch.float16)
-            r = interleaved([("forward", lambda: m(x)), ("quant", lambda: int8_exec.quant_rows_g32(x))], reps)
+            xc = copies(x, 3 * M * K)
+            r = interleaved([("forward", lambda i: m(xc[i % len(xc)])), ("quant", lambda i: int8_exec.quant_rows_g32(xc[i % len(xc)]))], reps)
             opsn = 2.0 * M * K * N
             out["items"].append({"layer": f"{K}->{N}", "rows": M, "forward_us": r["forward"], "forward_tops": opsn / r["forward"] / 1e6,
                                  "quant_g32_us": r["quant"], "quant_g32_gbs": (3.0 * M * K + 4.0 * M * K / 32) / r["quant"] / 1e3,
                                  "gemm_g32_us": r["forward"] - r["quant"],
                                  "gemm_g32_tops": opsn / max(r["forward"] - r["quant"], 1e-3) / 1e6})
-            del m, x, lin
+            del m, x, lin, xc
     else:
         H = W = 256
         C, F = 3072, 12288
@@ -718,10 +738,11 @@ def main_other(args) -> None:
         up, down = layer(C, F, torch.bfloat16, routed=True), layer(F, C, torch.bfloat16, routed=True)
         hmid = up.forward_gathered(canvas, d["row_idx"], mh)
         y = down.forward_rows(hmid, mh)
-        r = interleaved([("gather_quant", lambda: routing.gather_quant_rows(canvas, plan)),
-                         ("up", lambda: up.forward_gathered(canvas, d["row_idx"], mh)),
-                         ("down", lambda: down.forward_rows(hmid, mh)),
-                         ("scatter", lambda: routing.scatter_rows_(y, plan, canvas))], reps)
+        cv = [canvas, canvas.clone()]                       # 2 x 403 MB: rotating defeats L2
+        r = interleaved([("gather_quant", lambda i: routing.gather_quant_rows(cv[i % 2], plan)),
+                         ("up", lambda i: up.forward_gathered(cv[i % 2], d["row_idx"], mh)),
+                         ("down", lambda i: down.forward_rows(hmid, mh)),
+                         ("scatter", lambda i: routing.scatter_rows_(y, plan, cv[i % 2]))], reps)
         nt, nnz = int(plan.tokens.shape[0]), int(plan.src.shape[0])
         out.update({"rows_gathered": M, "rows_hi": mh, "touched_tokens": nt, "canvas": [H * W, C]})
         out["items"] = [
