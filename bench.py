@@ -373,42 +373,46 @@ def main_ours(args):
 
         n_g = max(3, min(args.steps, 10))
         seq_ms = timed_steps(lambda: [parallel.all_gather_rows(m(x), M_TOTAL) for m, x in zip(mods, xs)], n_g)
-        chunks = args.gather_chunks
-        c = parallel.cyclic_block_rows(M_TOTAL, world, chunks)
         cls = parallel.PeerPushGather if args.gather_mode == "push" else parallel.OverlappedRowGather
-        ogs = [cls(M_TOTAL, N, torch.bfloat16, dev, chunks=chunks) for _n, _K, N in LAYERS]
-        xl = []
-        for x in xs:                                   # this rank's rows, block after block (synthetic rows: any will do)
-            xp = x.new_zeros((chunks * c, x.shape[1]))
-            xp[: min(x.shape[0], chunks * c)] = x[: chunks * c]
-            xl.append(xp)
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         best = None
-        for spare in ([args.gather_sms] if args.gather_sms >= 0 else ([0] if args.gather_mode == "push" else [0, 8, 16])):
-            # the persistent GEMM otherwise holds every SM for the length of a chunk; NCCL's kernels need a few
-            _lib.set_option("gemm_max_ctas", sms - spare if spare > 0 else 0)
+        # chunks per rank: more chunks start the transfers earlier but cost smaller launches and more copies in flight
+        # (measured: two chunks win on 2 GPUs, one chunk -- only the next layer computes behind the transfers -- on 8)
+        for chunks in ([args.gather_chunks] if args.gather_chunks > 0 else [1, 2]):
+            c = parallel.cyclic_block_rows(M_TOTAL, world, chunks)
+            ogs = [cls(M_TOTAL, N, torch.bfloat16, dev, chunks=chunks) for _n, _K, N in LAYERS]
+            xl = []
+            for x in xs:                               # this rank's rows, block after block (synthetic rows: any will do)
+                xp = x.new_zeros((chunks * c, x.shape[1]))
+                xp[: min(x.shape[0], chunks * c)] = x[: chunks * c]
+                xl.append(xp)
+
             def gather_step():
                 for og, m, x in zip(ogs, mods, xl):            # the next layer computes behind the last pushes of this one
                     og.run(m, x, local=True, wait=False)
                 for og in ogs:
                     og.finish()
-            ms = timed_steps(gather_step, n_g)
-            if best is None or ms < best[0]:
-                best = (ms, spare)
-        _lib.set_option("gemm_max_ctas", 0)
+            for spare in ([args.gather_sms] if args.gather_sms >= 0 else ([0] if args.gather_mode == "push" else [0, 8, 16])):
+                # NCCL's copy kernels need SMs, which the persistent GEMM otherwise holds for the length of a chunk
+                _lib.set_option("gemm_max_ctas", sms - spare if spare > 0 else 0)
+                ms = timed_steps(gather_step, n_g)
+                if best is None or ms < best[0]:
+                    best = (ms, spare, chunks)
+            _lib.set_option("gemm_max_ctas", 0)
+            del ogs, xl
+            torch.cuda.empty_cache()
+        chunks = best[2]
         recv = (world - 1) / world * sum(M_TOTAL * N * 2.0 for _n, _K, N in LAYERS)
         gather = {"ms_per_step": best[0], "tops": step_ops(M_TOTAL) / (best[0] * 1e-3) / 1e12,
                   "mode": (f"overlapped: rows dealt out block-cyclically in {chunks} chunks per rank, chunk i pushed into every "
                            f"peer's output buffer by device-to-device copies (copy engines over NVLink, symmetric-memory buffers) while "
-                           f"chunk i+1 computes; two one-element all-reduces order the step" if args.gather_mode == "push" else
+                           f"the next chunk or layer computes; two one-element all-reduces order the step" if args.gather_mode == "push" else
                            f"overlapped: rows dealt out block-cyclically in {chunks} chunks per rank, chunk i gathered (NCCL, "
                            f"asynchronous) while chunk i+1 computes, {best[1]} SMs left free for NCCL's kernels"),
                   "bytes_recv_per_gpu": recv, "gbps": recv / (best[0] * 1e-3) / 1e9,
                   "sequential_ms_per_step": seq_ms, "sequential_tops": step_ops(M_TOTAL) / (seq_ms * 1e-3) / 1e12,
                   "compute_only_ms_per_step": ms_step,
                   "bound_ms": max(ms_step, recv / 0.9e12 * 1e3)}
-        del ogs, xl
-        torch.cuda.empty_cache()
 
     # ---- per-kernel device times (CUDA events on the launching stream): quantisation and GEMM of each layer
     def time_ms(fn, iters):
@@ -769,7 +773,7 @@ if __name__ == "__main__":
                     help="total token rows (default: the 4K stage's 66048); smaller values are for profiler captures only")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the measurement of the optional output all-gather")
-    ap.add_argument("--gather-chunks", type=int, default=2, help="chunks per rank of the overlapped all-gather")
+    ap.add_argument("--gather-chunks", type=int, default=0, help="chunks per rank of the overlapped all-gather (0: try 1 and 2)")
     ap.add_argument("--gather-mode", choices=("push", "nccl"), default="push",
                     help="overlapped all-gather by copy-engine pushes into peers' buffers (default) or by NCCL")
     ap.add_argument("--gather-sms", type=int, default=-1,
