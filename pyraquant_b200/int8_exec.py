@@ -585,7 +585,8 @@ class Int8LinearRouted(Int8Linear):
     def forward_gathered(self, canvas: torch.Tensor, row_idx: torch.Tensor, m_hi: int) -> torch.Tensor:
         """Gather + quantise in one kernel straight from the canvas, then the two-tier GEMM."""
         xq, sx = gather_quant_rows(canvas, row_idx)
-        return self._two_tier(xq, sx, lambda: torch.ops.pq_b200.gather_rows(canvas, row_idx), m_hi, canvas.dtype,
+        return self._two_tier(xq, sx, lambda: (ops._gather_rows_impl(canvas, row_idx) if _eager() else
+                                               torch.ops.pq_b200.gather_rows(canvas, row_idx)), m_hi, canvas.dtype,
                               self._fusable_lowrank(canvas))
 
 

@@ -23,6 +23,8 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from . import ops
+
 Box = Tuple[int, int, int, int]   # y0, y1, x0, x1 (half-open)
 
 
@@ -254,20 +256,36 @@ def inner_split_median(scores: np.ndarray, sel: np.ndarray, inner_thresh: float)
 
 
 # ------------------------------------------------------------------------------------------------ device ops
+# In eager mode the implementation functions are called directly: the dispatcher round trip of a Python custom op costs
+# tens of microseconds per call, as much as these kernels run.  Under torch.compile the registered ops are used.
+def _eager() -> bool:
+    return not torch.compiler.is_compiling()
+
+
 def gather_rows(canvas: torch.Tensor, plan: RoutePlan) -> torch.Tensor:
     """[tokens, C] canvas -> [M_act, C] gathered rows (no quantisation)."""
-    return torch.ops.pq_b200.gather_rows(canvas, plan.to(canvas.device)["row_idx"])
+    idx = plan.to(canvas.device)["row_idx"]
+    if _eager():
+        return ops._gather_rows_impl(canvas, idx)
+    return torch.ops.pq_b200.gather_rows(canvas, idx)
 
 
 def gather_quant_rows(canvas: torch.Tensor, plan: RoutePlan):
     """Gather fused with per-token INT8 quantisation: (int8 [M_act, C], fp32 [M_act])."""
-    return torch.ops.pq_b200.gather_quant_rows(canvas, plan.to(canvas.device)["row_idx"])
+    idx = plan.to(canvas.device)["row_idx"]
+    if _eager():
+        return ops._gather_quant_rows_impl(canvas, idx)
+    return torch.ops.pq_b200.gather_quant_rows(canvas, idx)
 
 
 def scatter_rows_(y: torch.Tensor, plan: RoutePlan, canvas: torch.Tensor) -> torch.Tensor:
     """Blends routed rows y [M_act, C] over `canvas` [tokens, C] in place and returns it."""
     d = plan.to(canvas.device)
-    torch.ops.pq_b200.scatter_rows_(y, d["tokens"], d["ptr"], d["src"], d["beta"], canvas)
+    if _eager():
+        ops._scatter_rows_impl(y, d["tokens"], d["ptr"], d["src"], d["beta"], canvas)
+        ops._written_in_place(canvas)
+    else:
+        torch.ops.pq_b200.scatter_rows_(y, d["tokens"], d["ptr"], d["src"], d["beta"], canvas)
     return canvas
 
 
