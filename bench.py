@@ -373,14 +373,23 @@ def main_ours(args):
 
         n_g = max(3, min(args.steps, 10))
         seq_ms = timed_steps(lambda: [parallel.all_gather_rows(m(x), M_TOTAL) for m, x in zip(mods, xs)], n_g)
-        cls = parallel.PeerPushGather if args.gather_mode == "push" else parallel.OverlappedRowGather
+        seq_out = [parallel.all_gather_rows(m(x), M_TOTAL) for m, x in zip(mods, xs)]
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        classes = {"push": parallel.PeerPushGather, "nccl": parallel.OverlappedRowGather, "store": parallel.PeerStoreGather}
+        # candidates (mode, chunks per rank): more chunks start the transfers earlier but cost smaller launches and more
+        # copies in flight (measured: two chunks win on 2 GPUs, one chunk -- only the next layer computes behind the
+        # transfers -- on 8); the store mode needs no chunks: tiles leave from the GEMM epilogue as they are finished
+        if args.gather_mode == "auto":
+            cands = [("store", 1), ("push", 1), ("push", 2)]
+        elif args.gather_mode == "store":
+            cands = [("store", max(1, args.gather_chunks))]
+        else:
+            cands = [(args.gather_mode, ch) for ch in ([args.gather_chunks] if args.gather_chunks > 0 else [1, 2])]
         best = None
-        # chunks per rank: more chunks start the transfers earlier but cost smaller launches and more copies in flight
-        # (measured: two chunks win on 2 GPUs, one chunk -- only the next layer computes behind the transfers -- on 8)
-        for chunks in ([args.gather_chunks] if args.gather_chunks > 0 else [1, 2]):
+        tried = []
+        for mode, chunks in cands:
             c = parallel.cyclic_block_rows(M_TOTAL, world, chunks)
-            ogs = [cls(M_TOTAL, N, torch.bfloat16, dev, chunks=chunks) for _n, _K, N in LAYERS]
+            ogs = [classes[mode](M_TOTAL, N, torch.bfloat16, dev, chunks=chunks) for _n, _K, N in LAYERS]
             xl = []
             for x in xs:                               # this rank's rows, block after block (synthetic rows: any will do)
                 xp = x.new_zeros((chunks * c, x.shape[1]))
@@ -388,27 +397,39 @@ def main_ours(args):
                 xl.append(xp)
 
             def gather_step():
-                for og, m, x in zip(ogs, mods, xl):            # the next layer computes behind the last pushes of this one
+                for og, m, x in zip(ogs, mods, xl):            # the next layer computes behind the last transfers of this one
                     og.run(m, x, local=True, wait=False)
                 for og in ogs:
                     og.finish()
-            for spare in ([args.gather_sms] if args.gather_sms >= 0 else ([0] if args.gather_mode == "push" else [0, 8, 16])):
+            for spare in ([args.gather_sms] if args.gather_sms >= 0 else ([0, 8, 16] if mode == "nccl" else [0])):
                 # NCCL's copy kernels need SMs, which the persistent GEMM otherwise holds for the length of a chunk
                 _lib.set_option("gemm_max_ctas", sms - spare if spare > 0 else 0)
                 ms = timed_steps(gather_step, n_g)
+                tried.append({"mode": mode, "chunks": chunks, "spare_sms": spare, "ms_per_step": ms})
                 if best is None or ms < best[0]:
-                    best = (ms, spare, chunks)
+                    best = (ms, spare, chunks, mode)
             _lib.set_option("gemm_max_ctas", 0)
+            if chunks == 1:
+                # with one block per rank the row layout is the sequential gather's: the results must be the same tensors
+                gather_step()
+                barrier()
+                for og, ref in zip(ogs, seq_out):
+                    assert torch.equal(og.full[:M_TOTAL], ref), f"gathered output differs from the sequential all-gather ({mode})"
             del ogs, xl
             torch.cuda.empty_cache()
-        chunks = best[2]
+        del seq_out
+        chunks, mode = best[2], best[3]
         recv = (world - 1) / world * sum(M_TOTAL * N * 2.0 for _n, _K, N in LAYERS)
+        how = {"push": f"rows dealt out block-cyclically in {chunks} chunks per rank, chunk i pushed into every peer's output buffer by "
+                       f"device-to-device copies (copy engines over NVLink, symmetric-memory buffers) while the next chunk or layer "
+                       f"computes; two one-element all-reduces order the step",
+               "store": "the GEMM epilogue stores every output tile into this GPU's and every peer's output buffer (plain vector stores to "
+                        "peer memory, symmetric-memory buffers): tiles cross NVLink while the tensor cores work on the next ones; two "
+                        "one-element all-reduces order the step",
+               "nccl": f"rows dealt out block-cyclically in {chunks} chunks per rank, chunk i gathered (NCCL, asynchronous) while chunk "
+                       f"i+1 computes, {best[1]} SMs left free for NCCL's kernels"}[mode]
         gather = {"ms_per_step": best[0], "tops": step_ops(M_TOTAL) / (best[0] * 1e-3) / 1e12,
-                  "mode": (f"overlapped: rows dealt out block-cyclically in {chunks} chunks per rank, chunk i pushed into every "
-                           f"peer's output buffer by device-to-device copies (copy engines over NVLink, symmetric-memory buffers) while "
-                           f"the next chunk or layer computes; two one-element all-reduces order the step" if args.gather_mode == "push" else
-                           f"overlapped: rows dealt out block-cyclically in {chunks} chunks per rank, chunk i gathered (NCCL, "
-                           f"asynchronous) while chunk i+1 computes, {best[1]} SMs left free for NCCL's kernels"),
+                  "mode": f"{mode}: {how}", "tried": tried,
                   "bytes_recv_per_gpu": recv, "gbps": recv / (best[0] * 1e-3) / 1e9,
                   "sequential_ms_per_step": seq_ms, "sequential_tops": step_ops(M_TOTAL) / (seq_ms * 1e-3) / 1e12,
                   "compute_only_ms_per_step": ms_step,
@@ -774,8 +795,9 @@ if __name__ == "__main__":
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the measurement of the optional output all-gather")
     ap.add_argument("--gather-chunks", type=int, default=0, help="chunks per rank of the overlapped all-gather (0: try 1 and 2)")
-    ap.add_argument("--gather-mode", choices=("push", "nccl"), default="push",
-                    help="overlapped all-gather by copy-engine pushes into peers' buffers (default) or by NCCL")
+    ap.add_argument("--gather-mode", choices=("auto", "store", "push", "nccl"), default="auto",
+                    help="all-gather hidden behind the compute: stores to peers from the GEMM epilogue, copy-engine pushes into "
+                         "peers' buffers, NCCL per chunk; auto tries the first two and reports the faster")
     ap.add_argument("--gather-sms", type=int, default=-1,
                     help="SMs the GEMM leaves free while NCCL gathers (-1: try 0, 8 and 16 and report the best)")
     ap.add_argument("--no-cpu", action="store_true")

@@ -59,6 +59,10 @@ int pq_last_cuda_error(void);
  *   "gemm_pair"         0 = never use the CTA-pair kernel, 1 = automatic (default), 2 = whenever it is legal;
  *   "gemm_debug_timing" 1 = the CTA-pair kernel runs in its debug instantiation (the production kernel contains no
  *                       counters) and writes per-role cycle counters to workspace + 256 (needs ws_bytes >= 256 + 4096*64).
+ *   "gemm_panel_mb"     CTA-pair kernel with several column rounds: megabytes of activation rows per row panel of the tile
+ *                       schedule (the rows of a panel stay in L2 across the rounds); 0 = one panel over all rows;
+ *   "gemm_l2_hints"     CTA-pair kernel, L2 eviction priorities: bit 0 weights evict-last, bit 1 activations evict-first,
+ *                       bit 2 activations evict-last, bit 3 streaming output stores;
  *   "g32_variant"       group-32 GEMM: bit 0 = eight epilogue warps instead of sixteen; bit 1 = scalar instead of packed
  *                       fp32 operations; bit 3 = data path only (measurements; the output is meaningless).
  * Unknown keys return PQ_ERR_UNSUPPORTED.  Not part of the reference API. */
@@ -141,6 +145,23 @@ int pq_int8_gemm_ex(const int8_t* xq, int64_t ldx, const float* s_row,
                     void* out, int out_dtype, int64_t ldo,
                     int64_t M, int64_t N, int64_t K, int epilogue,
                     void* workspace, size_t ws_bytes, void* stream);
+
+/* pq_int8_gemm_ex whose epilogue stores every output tile to n_out_more further buffers as well (no counterpart in
+ * the reference, which runs on one GPU).  `out_more` is a HOST array of n_out_more (<= PQ_MAX_OUT_MORE) device
+ * pointers; buffer d receives exactly what `out` receives, at the same offsets (same [M,N] extent, row stride ldo,
+ * 16-byte aligned).  Meant for the row-sharded Linear on several GPUs of one node: `out` and out_more[d] are this
+ * rank's row block inside the full output buffers of this GPU and of its peers (peer memory mapped into the process,
+ * written with plain stores), so the all-gather of the outputs happens tile by tile inside the GEMM instead of after
+ * it.  The call only enqueues the kernel: peers may read their buffer once this GPU's stream has passed the kernel and
+ * the ranks have synchronised (the caller's job).  Same shape rules as pq_int8_gemm_ex (CTA-pair kernel, N % 32 == 0,
+ * ldo % 8 == 0, 16-byte-aligned outputs, lb_t given with t); n_out_more == 0 is pq_int8_gemm_ex. */
+#define PQ_MAX_OUT_MORE 7
+int pq_int8_gemm_bcast(const int8_t* xq, int64_t ldx, const float* s_row,
+                       const int8_t* w, int64_t ldw, const float* s_col, const float* bias,
+                       const void* t, int64_t ldt, const void* lb, int64_t ldb, const void* lb_t, int R, int lr_dtype,
+                       void* out, void* const* out_more, int n_out_more, int out_dtype, int64_t ldo,
+                       int64_t M, int64_t N, int64_t K, int epilogue,
+                       void* workspace, size_t ws_bytes, void* stream);
 
 /* Routed two-tier GEMM (the per-leaf precision routing of flux/run_flux.py:117-123 collapsed to a
  * hard choice at the Linear): rows [0, M_hi) use weight set 0 (the INT8 codes), rows [M_hi, M)

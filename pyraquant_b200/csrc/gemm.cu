@@ -520,7 +520,7 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
                 const int8_t* w1, const float* sc1, int64_t ldw, const float* bias, const void* t, int64_t ldt,
                 const void* lb, int64_t ldb, const void* lb_t, int R, int lr_dtype, void* out, int out_dtype,
                 int64_t ldo, int64_t m_split, int64_t M, int64_t N, int64_t K, void* workspace, size_t ws_bytes,
-                int32_t* dbg_acc, void* stream, int epi_flags = 0) {
+                int32_t* dbg_acc, void* stream, int epi_flags = 0, void* const* out_more = nullptr, int n_out_more = 0) {
   if (M < 0 || N <= 0 || K <= 0 || m_split < 0 || m_split > M) return PQ_ERR_SHAPE;
   if (epi_flags & ~(PQ_EPI_ACCUMULATE | PQ_EPI_GELU_TANH)) return PQ_ERR_UNSUPPORTED;
   if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return PQ_ERR_SHAPE;
@@ -560,13 +560,16 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
   p.timing = (options().gemm_debug_timing != 0 && workspace != nullptr && ws_bytes >= 256 + 4096 * 64)
                  ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + 256) : nullptr;
   p.sched_pm = p.sched_pn = p.sched_m_steps = p.sched_n_rounds = 1;
+  p.sched_panel = 0; p.l2_hints = 0; p.tma_store = 0;
+  p.n_out_more = n_out_more;
+  for (int d = 0; d < 7; ++d) p.out_more[d] = d < n_out_more ? out_more[d] : nullptr;
 
   // CTA-pair kernel: 256-column tiles, enough 256-row tiles to occupy the SM pairs, and the K-major low-rank
   // factor when there is a low-rank term
   {
     const int64_t pair_rows = (m_split + 255) / 256 + (M - m_split + 255) / 256;
     const bool pair_legal = (!has_lr || lb_t != nullptr);
-    if (epi_flags != 0) {
+    if (epi_flags != 0 || n_out_more > 0) {
       // the epilogue variants exist in the CTA-pair kernel's vector store path only
       if (!pair_legal || N % 32 != 0 || ldo % 8 != 0 || !aligned_to(out, 16)) return PQ_ERR_UNSUPPORTED;
       return launch_gemm_pair(out_dtype == PQ_DTYPE_BF16, dbg_acc != nullptr || p.timing != nullptr, xq, ldx, w0, w1, ldw, has_lr ? t : nullptr, ldt,
@@ -631,6 +634,21 @@ extern "C" int pq_int8_gemm_ex(const int8_t* xq, int64_t ldx, const float* s_row
                                void* stream) {
   return gemm_common(xq, ldx, s_row, w, s_col, nullptr, nullptr, ldw, bias, t, ldt, lb, ldb, lb_t, R, lr_dtype, out,
                      out_dtype, ldo, M, M, N, K, workspace, ws_bytes, nullptr, stream, epilogue);
+}
+
+extern "C" int pq_int8_gemm_bcast(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t* w, int64_t ldw,
+                                  const float* s_col, const float* bias, const void* t, int64_t ldt, const void* lb,
+                                  int64_t ldb, const void* lb_t, int R, int lr_dtype, void* out, void* const* out_more,
+                                  int n_out_more, int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                                  int epilogue, void* workspace, size_t ws_bytes, void* stream) {
+  if (n_out_more < 0 || n_out_more > PQ_MAX_OUT_MORE) return PQ_ERR_SHAPE;
+  if (n_out_more > 0 && out_more == nullptr) return PQ_ERR_NULL;
+  for (int d = 0; d < n_out_more; ++d) {
+    if (out_more[d] == nullptr) return PQ_ERR_NULL;
+    if (!aligned_to(out_more[d], 16)) return PQ_ERR_ALIGN;
+  }
+  return gemm_common(xq, ldx, s_row, w, s_col, nullptr, nullptr, ldw, bias, t, ldt, lb, ldb, lb_t, R, lr_dtype, out,
+                     out_dtype, ldo, M, M, N, K, workspace, ws_bytes, nullptr, stream, epilogue, out_more, n_out_more);
 }
 
 extern "C" int pq_int8_gemm_grouped(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t* w_hi,

@@ -84,6 +84,24 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
       ::"r"(smem_u32(smem_dst)), "l"(m), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
+// the same with an L2 eviction-priority policy (createpolicy) attached to the copy
+__device__ __forceinline__ void tma_load_2d_pair_hint(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y,
+                                                      uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(smem_dst)), "l"(m), "r"(bar_cluster_addr), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
                : "memory");
@@ -146,15 +164,27 @@ __device__ __noinline__ void dump_acc_pair(int32_t* dbg, int N, int rA, int rB, 
   if (rB < row_end && col + 1 < N) dbg[static_cast<int64_t>(rB) * N + col + 1] = static_cast<int32_t>(v3);
 }
 
-// Walker over pair tiles: the pairs (not the CTAs) form the pm x pn grid.
+// Walker over pair tiles: the pairs (not the CTAs) form the pm x pn grid.  Order of the tiles a pair visits: the row
+// steps are cut into panels of `panel` steps; inside a panel the pair runs down its column (all row steps of the panel)
+// before it moves pn column tiles to the right, and only after the last column round does it enter the next panel.
+// A panel that covers all row steps is the plain column-round-major order.  With several column rounds a short panel
+// keeps the panel's activation rows in L2 across the rounds instead of streaming all M rows once per round.
 struct PairWalker {
-  int mt, ntile, bm, pm, pn, mt_total, nt;
-  __device__ __forceinline__ void init(int pair, int pm_, int pn_, int mt_total_, int nt_) {
+  int mt, ntile, bn, pm, pn, mt_total, nt, panel0, panel_span;
+  __device__ __forceinline__ void init(int pair, int pm_, int pn_, int mt_total_, int nt_, int panel_steps) {
     pm = pm_; pn = pn_; mt_total = mt_total_; nt = nt_;
-    bm = pair / pn; mt = bm; ntile = pair - bm * pn;
+    const int bm = pair / pn; bn = pair - bm * pn;
+    panel_span = (panel_steps > 0 && panel_steps < (1 << 20)) ? panel_steps * pm : (1 << 30);
+    panel0 = bm; mt = bm; ntile = bn;
   }
   __device__ __forceinline__ bool valid() const { return ntile < nt && mt < mt_total; }
-  __device__ __forceinline__ void advance() { mt += pm; if (mt >= mt_total) { mt = bm; ntile += pn; } }
+  __device__ __forceinline__ void advance() {
+    mt += pm;
+    if (mt >= mt_total || mt - panel0 >= panel_span) {
+      ntile += pn; mt = panel0;
+      if (ntile >= nt && panel_span < (1 << 30) && panel0 + panel_span < mt_total) { ntile = bn; panel0 += panel_span; mt = panel0; }
+    }
+  }
 };
 
 // Rows of a pair tile.  Row tiles [0, mt0) cover rows [0, m_split) with weight set 0, the rest cover [m_split, M) with
@@ -242,7 +272,11 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     if (elect_one()) {
       int stage = 0; uint32_t phase = 0; long long issued = 0; bool ok = true;
       int it = 0; int lb_col = -1; uint32_t lb_count = 0;
-      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
+      // L2 priorities of the operand streams (l2_hints bit 0: weights evict-last; bit 1: activations evict-first; bit 2:
+      // activations evict-last)
+      const uint64_t pol_w = l2_policy_evict_last();
+      const uint64_t pol_a = (p.l2_hints & 4) ? l2_policy_evict_last() : l2_policy_evict_first();
+      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt, p.sched_panel);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance(), ++it) {
         const PairCoord c = pair_coord(w.mt, mt0, p, rank);
@@ -274,9 +308,11 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           uint8_t* a_s = smem + stage * L::kStageBytes;
           const uint32_t fb = leader_addr(&full_bar[stage]);
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
-          tma_load_2d_pair(a_s, &tmA, fb, kb * BK, row0);
-          if (c.set == 0) tma_load_2d_pair(a_s + L::kABytes, &tmW, fb, kb * BK, nhalf0);
-          else tma_load_2d_pair(a_s + L::kABytes, &tmW1, fb, kb * BK, nhalf0);
+          if (p.l2_hints & 6) tma_load_2d_pair_hint(a_s, &tmA, fb, kb * BK, row0, pol_a);
+          else tma_load_2d_pair(a_s, &tmA, fb, kb * BK, row0);
+          const CUtensorMap* wm = c.set == 0 ? &tmW : &tmW1;
+          if (p.l2_hints & 1) tma_load_2d_pair_hint(a_s + L::kABytes, wm, fb, kb * BK, nhalf0, pol_w);
+          else tma_load_2d_pair(a_s + L::kABytes, wm, fb, kb * BK, nhalf0);
           ++issued;
           if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
         }
@@ -312,7 +348,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       int stage = 0; uint32_t phase = 0; int it = 0; bool ok = true;
       long long tm_tempty = 0, tm_full = 0;
       auto commit_both = [&](uint64_t* bar) { tc_commit_pair(smem_u32(bar)); tc_commit_pair(peer_addr(bar)); };
-      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
+      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt, p.sched_panel);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance(), ++it) {
         const int buf = it & 1;
@@ -357,7 +393,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       int it = 0, lb_col = -1; uint32_t lb_count = 0; bool ok = true;
       long long tm_det[2] = {0, 0};
       auto commit_both = [&](uint64_t* bar) { tc_commit_pair(smem_u32(bar)); tc_commit_pair(peer_addr(bar)); };
-      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
+      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt, p.sched_panel);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance(), ++it) {
         const int pb = it & 1;
@@ -416,7 +452,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         dst[mb][1] = rA + 8 < pc.row_end ? p.s_row[rA + 8] : 0.0f;
       }
     };
-    PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt);
+    PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt, p.sched_panel);
 #pragma unroll 1
     for (; w.valid(); w.advance(), ++it) {
       const PairCoord c = pair_coord(w.mt, mt0, p, rank);
@@ -535,8 +571,25 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
                 wB[2] = add_word<OutT>(wB[2], o.z); wB[3] = add_word<OutT>(wB[3], o.w);
               }
             }
-            if (rA < row_end) st_v4(pA, make_uint4(wA[0], wA[1], wA[2], wA[3]));
-            if (rB < row_end) st_v4(pB, make_uint4(wB[0], wB[1], wB[2], wB[3]));
+            if (p.n_out_more > 0) {
+              // the same words go to the further output buffers (other GPUs' memory mapped into this process: the
+              // all-gather of a row-sharded layer happens here, tile by tile, while the main loop keeps running)
+              const int64_t offA = static_cast<int64_t>(rA) * p.ldo + col_grp + q * 8;
+              const int64_t offB = static_cast<int64_t>(rB) * p.ldo + col_grp + q * 8;
+#pragma unroll 1
+              for (int d = 0; d < p.n_out_more; ++d) {
+                OutT* o = static_cast<OutT*>(p.out_more[d]);
+                if (rA < row_end) st_v4(o + offA, make_uint4(wA[0], wA[1], wA[2], wA[3]));
+                if (rB < row_end) st_v4(o + offB, make_uint4(wB[0], wB[1], wB[2], wB[3]));
+              }
+            }
+            if (p.l2_hints & 8) {                          // outputs are not read again by this kernel: evict first
+              if (rA < row_end) st_v4_cs(pA, make_uint4(wA[0], wA[1], wA[2], wA[3]));
+              if (rB < row_end) st_v4_cs(pB, make_uint4(wB[0], wB[1], wB[2], wB[3]));
+            } else {
+              if (rA < row_end) st_v4(pA, make_uint4(wA[0], wA[1], wA[2], wA[3]));
+              if (rB < row_end) st_v4(pB, make_uint4(wB[0], wB[1], wB[2], wB[3]));
+            }
           } else {
             store_pairs_slow(p.out, p.ldo, rA, rB, col_grp + 2 * q, row_end, p.N, make_uint4(wA[0], wA[1], wA[2], wA[3]),
                              make_uint4(wB[0], wB[1], wB[2], wB[3]));
@@ -692,7 +745,7 @@ int launch_pair_ew(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtenso
   // sixteen-warp tiles of a plain single-tier call store through shared memory + TMA when the output allows it
   CUtensorMap tmOut = tmA;
   p.tma_store = 0;
-  if (EW == 16 && !HAS_LR && p.m_split == p.M && !(p.epi_flags & PQ_EPI_ACCUMULATE) && options().gemm_tma_store != 0 &&
+  if (EW == 16 && !HAS_LR && p.m_split == p.M && !(p.epi_flags & PQ_EPI_ACCUMULATE) && p.n_out_more == 0 && options().gemm_tma_store != 0 &&
       p.ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
     const int rc = make_out_map16(&tmOut, p.out, p.M, p.N, p.ldo, std::is_same<OutT, __nv_bfloat16>::value);
     if (rc != PQ_OK) return rc;
@@ -723,6 +776,17 @@ int launch_pair_ew(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtenso
   if (options().gemm_max_ctas > 0 && options().gemm_max_ctas / 2 < pairs_cap) pairs_cap = options().gemm_max_ctas / 2;
   if (pairs_cap < 1) pairs_cap = 1;
   choose_cta_grid(mt_pairs, ntl, pairs_cap, &p.sched_pm, &p.sched_pn);
+  // Row panels.  With several column rounds, the activation rows of a panel (panel steps x pm pair tiles x 256 rows x
+  // K bytes) are meant to stay in L2 from one round to the next: the panel is sized to gemm_panel_mb megabytes.
+  p.sched_panel = 0;
+  const int rounds = (ntl + p.sched_pn - 1) / p.sched_pn;
+  if (rounds > 1 && options().gemm_panel_mb > 0) {
+    const double step_bytes = static_cast<double>(p.sched_pm) * 2 * BM * p.K;
+    int steps = static_cast<int>(options().gemm_panel_mb * 1048576.0 / step_bytes);
+    if (steps < 1) steps = 1;
+    if (steps < (mt_pairs + p.sched_pm - 1) / p.sched_pm) p.sched_panel = steps;
+  }
+  p.l2_hints = options().gemm_l2_hints;
   cfg.gridDim = dim3(2 * p.sched_pm * p.sched_pn, 1, 1);
   PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmW1, tmT, tmLbT, tmOut, p));
   return PQ_OK;

@@ -24,7 +24,11 @@ struct GemmParams {
   int sched_n_rounds;       // ceil(column tiles / sched_pn)
   int has_bias;
   int epi_flags;            // PQ_EPI_* bits (CTA-pair kernel only)
+  int sched_panel;          // CTA-pair kernel: row steps per panel (0 = all rows in one panel)
+  int l2_hints;             // CTA-pair kernel: Options::gemm_l2_hints
   int tma_store;            // CTA-pair kernel, sixteen epilogue warps: output tiles leave through shared memory + TMA
+  void* out_more[7];        // CTA-pair kernel: further buffers (same shape and row stride as out) that receive every output store
+  int n_out_more;
   long long* timing;        // experiments: per-CTA cycle counters [grid][8] (NULL in normal use)
 };
 

@@ -416,6 +416,33 @@ class Int8Linear(nn.Module):
             return out
         return y2.reshape(*shape[:-1], N)
 
+    def forward_into(self, x2: torch.Tensor, out: torch.Tensor, out_more: Sequence[torch.Tensor] = ()) -> torch.Tensor:
+        """``out[:] = self(x2)`` for 2-D ``x2``, the same values also stored to every tensor of ``out_more`` (same shape,
+        dtype and row stride as ``out``; up to ``ops.MAX_OUT_MORE``).  When the shapes allow it the GEMM epilogue
+        writes all destinations itself (``pq_int8_gemm_bcast``): with ``out`` / ``out_more`` being this rank's row block
+        inside the full output buffers of this GPU and of its peers, the all-gather of a row-sharded layer happens
+        inside the GEMM.  Otherwise the layer runs as usual and the result is copied."""
+        M, K = x2.shape
+        N = self.out_features
+        assert out.shape == (M, N) and out.dtype == x2.dtype and out.stride(1) == 1, (out.shape, out.dtype)
+        lr = self.lr_A is not None
+        direct = (M > 0 and x2.is_cuda and x2.dtype in ops._DT and K % 16 == 0 and len(out_more) <= ops.MAX_OUT_MORE
+                  and not torch.compiler.is_compiling() and (not lr or self._fusable_lowrank(x2))
+                  and ops.epilogue_supported(N, out.stride(0), out.data_ptr(), lr)
+                  and all(o.stride(0) == out.stride(0) and o.data_ptr() % 16 == 0 for o in out_more))
+        if not direct:
+            y = self.forward(x2)
+            out.copy_(y)
+            for o in out_more:
+                o.copy_(y, non_blocking=True)
+            return out
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        t = self._down(x2) if lr else None
+        xq, sx = quant_rows(x2)
+        return ops._gemm_impl(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B if lr else None, x2.dtype,
+                              lb_t=self._lr_Bt() if lr else None, out=out, out_more=list(out_more))
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])

@@ -8,7 +8,7 @@ CUDA tensors only: a CPU tensor raises AssertionError, as the reference's ``quan
 from __future__ import annotations
 
 import ctypes
-from typing import Dict, Optional, Tuple
+from typing import Dict, Optional, Sequence, Tuple
 
 import torch
 
@@ -22,6 +22,7 @@ LOWRANK_ON_TENSOR_CORES = True
 # epilogue variants of pq_int8_gemm_ex
 EPI_ACCUMULATE = 1      # out += y (both rounded to the output type first)
 EPI_GELU_TANH = 2       # out = gelu_tanh(y rounded to the output type)
+MAX_OUT_MORE = 7        # further output buffers of pq_int8_gemm_bcast
 _status_words: Dict[int, Tensor] = {}
 
 
@@ -262,7 +263,7 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
                t: Optional[Tensor], lb: Optional[Tensor], out_dtype: torch.dtype,
                dbg_acc: Optional[Tensor] = None, w_lo: Optional[Tensor] = None, s_lo: Optional[Tensor] = None,
                m_hi: Optional[int] = None, lb_t: Optional[Tensor] = None, epilogue: int = 0,
-               out: Optional[Tensor] = None) -> Tensor:
+               out: Optional[Tensor] = None, out_more: Optional[Sequence[Tensor]] = None) -> Tensor:
     assert xq.is_cuda and xq.dtype == torch.int8 and xq.dim() == 2 and xq.stride(1) == 1
     assert w_int8.dtype == torch.int8 and w_int8.dim() == 2 and w_int8.stride(1) == 1
     M, K = xq.shape
@@ -304,6 +305,26 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
     lib = _LIB()
     ldx = xq.stride(0) if M > 1 else max(K, xq.stride(0))
     ldo = out.stride(0) if M > 1 else max(N, out.stride(0))
+    if out_more:
+        # further destinations of the output stores (pq_int8_gemm_bcast): same extent, dtype and row stride as `out`;
+        # they may live on other GPUs of the node (peer memory mapped into this process)
+        assert w_lo is None and dbg_acc is None and len(out_more) <= MAX_OUT_MORE, len(out_more)
+        assert epilogue_supported(N, ldo, out.data_ptr(), t is not None, R or 32), "shape needs the CTA-pair kernel"
+        for o in out_more:
+            assert o.shape == (M, N) and o.dtype == out_dtype and o.stride(1) == 1 and o.is_cuda, (o.shape, o.dtype)
+            assert (o.stride(0) if M > 1 else ldo) == ldo and o.data_ptr() % 16 == 0, (o.stride(), ldo)
+        ptrs = (ctypes.c_void_p * len(out_more))(*[o.data_ptr() for o in out_more])
+        with _on_device(xq):
+            rc = lib.pq_int8_gemm_bcast(xq.data_ptr(), ldx, s_row.data_ptr(), w_int8.data_ptr(), w_int8.stride(0),
+                                        w_scale.data_ptr(), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, _ptr(lb_t), R,
+                                        _dt(out_dtype), out.data_ptr(), ptrs, len(out_more), _dt(out_dtype), ldo,
+                                        M, N, K, int(epilogue), ws.data_ptr(), ws.numel() * 4, _stream(xq))
+        if rc:
+            _lib.check(rc, f"pq_int8_gemm_bcast(M={M}, N={N}, K={K}, copies={len(out_more)})")
+        _written_in_place(out)
+        for o in out_more:
+            _written_in_place(o)
+        return out
     with _on_device(xq):
         if epilogue:
             assert w_lo is None and dbg_acc is None

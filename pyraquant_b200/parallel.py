@@ -189,6 +189,40 @@ class PeerPushGather(OverlappedRowGather):
             dist.all_reduce(self._token, group=self.group)           # every rank's copies are behind its all-reduce
 
 
+class PeerStoreGather(PeerPushGather):
+    """Row-sharded layer whose GEMM epilogue performs the all-gather (CUDA, one node).
+
+    The full-size output buffers live in symmetric memory as in `PeerPushGather`; here the GEMM kernel itself stores
+    every output tile to this GPU's buffer and to each peer's (`Int8Linear.forward_into` -> `pq_int8_gemm_bcast`, plain
+    vector stores to peer memory from the epilogue warps), so tiles cross NVLink while the tensor cores work on the next
+    ones and no copy or collective kernel follows the layer.  The kernel waits on nobody: ordering between ranks is the
+    stream-ordered one-element all-reduce before (peers have finished reading the previous result) and after (every
+    rank's kernel, and with it its stores, is complete) the layer.  Rows are dealt out as one contiguous block per rank
+    and chunk (`chunks` = 1 unless a later layer wants to start on early rows)."""
+
+    def __init__(self, M: int, N: int, dtype: torch.dtype, device, chunks: int = 1, group: Optional[dist.ProcessGroup] = None):
+        super().__init__(M, N, dtype, device, chunks, group, copy_streams=1)
+
+    def run(self, linear, x: torch.Tensor, local: bool = False, wait: bool = True) -> torch.Tensor:
+        c, W, r = self.c, self.world, self.rank
+        if W > 1:
+            dist.all_reduce(self._token, group=self.group)
+        for i, (a, b) in enumerate(cyclic_local_blocks(self.M, W, r, self.chunks)):
+            if b <= a:
+                continue
+            xb = x[i * c: i * c + (b - a)] if local else x[a:b]
+            row = (i * W + r) * c
+            more = [self.peers[(r + k) % W][row: row + (b - a)] for k in range(1, W)]
+            linear.forward_into(xb, self.full[row: row + (b - a)], more)
+        if wait:
+            self.finish()
+        return self.full[: self.M]
+
+    def finish(self) -> None:
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)
+
+
 class RowShardedLinear(torch.nn.Module):
     """Runs `linear` on this rank's row block of a full-size input; `gather=True` returns the full output."""
 

@@ -112,6 +112,26 @@ def test_gemm_ex_argument_checks():
     assert ex(K=40) == 3                             # the plain GEMM's checks still come first
 
 
+def test_gemm_bcast_argument_checks():
+    """The broadcast-store GEMM refuses bad destination lists before anything is launched."""
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(4096)
+    p16 = (ctypes.addressof(buf) + 15) & ~15
+
+    def bc(more, n, N=64, ldo=64, M=8):
+        arr = (ctypes.c_void_p * max(1, len(more)))(*more) if more is not None else None
+        return lib.pq_int8_gemm_bcast(p16, 64, p16, p16, 64, p16, None, None, 0, None, 0, None, 0, 0, p16, arr, n, 0, ldo,
+                                      M, N, 64, 0, None, 0, None)
+
+    assert bc([p16], 1, M=0) == 0                    # nothing to do
+    assert bc([p16] * 8, 8) == 2                     # more than PQ_MAX_OUT_MORE destinations
+    assert bc([p16], -1) == 2
+    assert bc(None, 1) == 1                          # no list
+    assert bc([p16, None], 2) == 1                   # a null destination
+    assert bc([p16 + 4], 1) == 3                     # destination not 16-byte aligned
+    assert bc([p16], 1, N=40, ldo=40) == 7           # shape outside the CTA-pair kernel's vector store path
+
+
 def test_scatter_and_gather_argument_checks():
     lib = _lib.load()
     buf = ctypes.create_string_buffer(4096)

@@ -450,6 +450,42 @@ def test_epilogue_variants(cuda_dev, dtype, N, lowrank):
     assert bool((err <= 4 * ulp * (base + ref_act).float().abs() + 4e-3).all()), err.max().item()
 
 
+@pytest.mark.parametrize("M,K,N,lowrank,copies", [(700, 512, 768, True, 3), (1000, 256, 512, False, 7), (513, 3072, 1024, True, 1),
+                                                  (300, 512, 264, True, 2)])
+def test_gemm_stores_to_every_destination(cuda_dev, M, K, N, lowrank, copies):
+    """`forward_into` (pq_int8_gemm_bcast): the epilogue writes each output tile to several buffers -- on several GPUs
+    these are the peers' output buffers, here slices of larger local ones.  Every destination must equal the plain
+    forward bit for bit and rows outside the slice must stay untouched.  N = 264 is a shape the kernel path does not
+    take: same results through the copy path."""
+    g = torch.Generator().manual_seed(M + copies)
+    layer = _toy_layer(cuda_dev, g, K, N, lowrank=lowrank)
+    x = (torch.randn(M, K, generator=g) * 1.5).to(torch.bfloat16).to(cuda_dev)
+    ref = layer(x)
+    pad = 40
+    bufs = [torch.full((M + 2 * pad, N), 7.0, dtype=torch.bfloat16, device=cuda_dev) for _ in range(copies + 1)]
+    views = [b[pad: pad + M] for b in bufs]
+    r = layer.forward_into(x, views[0], views[1:])
+    torch.cuda.synchronize()
+    ops.check_device_status(cuda_dev)
+    assert r.data_ptr() == views[0].data_ptr()
+    for b, v in zip(bufs, views):
+        assert torch.equal(v, ref)
+        assert bool((b[:pad] == 7.0).all()) and bool((b[pad + M:] == 7.0).all())
+
+
+def test_peer_store_gather_on_one_rank(cuda_dev):
+    """`parallel.PeerStoreGather` without a process group: one rank owns all rows, the result is the layer's output."""
+    from pyraquant_b200 import parallel
+    g = torch.Generator().manual_seed(11)
+    M, K, N = 900, 512, 768
+    layer = _toy_layer(cuda_dev, g, K, N, lowrank=True)
+    x = (torch.randn(M, K, generator=g) * 1.5).to(torch.bfloat16).to(cuda_dev)
+    for chunks in (1, 3):
+        og = parallel.PeerStoreGather(M, N, torch.bfloat16, cuda_dev, chunks=chunks)
+        y = og.run(layer, x)
+        assert y.shape == (M, N) and torch.equal(y, layer(x))
+
+
 def test_split_input_linear(cuda_dev):
     """y = L0(x[..., :in0]) + L1(x[..., in0:]) with the sum in the second GEMM's epilogue: identical to the two layers
     and a torch add (pyraquant/external_quant.py:191-192), 3-D input, strided halves."""
