@@ -380,7 +380,7 @@ def main_ours(args):
         # copies in flight (measured: two chunks win on 2 GPUs, one chunk -- only the next layer computes behind the
         # transfers -- on 8); the store mode needs no chunks: tiles leave from the GEMM epilogue as they are finished
         if args.gather_mode == "auto":
-            cands = [("store", 1), ("push", 1), ("push", 2)]
+            cands = [("store", 1), ("push", 1), ("push", 2), ("push", 4)]
         elif args.gather_mode == "store":
             cands = [("store", max(1, args.gather_chunks))]
         else:

@@ -166,17 +166,18 @@ class PeerPushGather(OverlappedRowGather):
             if b <= a:
                 continue
             xb = x[i * c: i * c + (b - a)] if local else x[a:b]
-            y = forward(xb)
-            done = torch.cuda.Event(); done.record(cur)
             row = (i * W + r) * c
-            for k in range(W):                                       # farthest peers first is of no use on a switch: round robin
-                peer = (r + k) % W
+            mine = self.full[row: row + (b - a)]
+            if hasattr(forward, "forward_into"):                     # the layer writes its rows of this rank's buffer itself
+                forward.forward_into(xb, mine)
+            else:
+                mine.copy_(forward(xb))
+            done = torch.cuda.Event(); done.record(cur)
+            for k in range(1, W):                                    # every peer is one hop away on a switch: round robin
                 st = self.streams[k % len(self.streams)]
                 st.wait_event(done)
                 with torch.cuda.stream(st):
-                    self.peers[peer][row: row + (b - a)].copy_(y, non_blocking=True)
-            for st in self.streams:
-                y.record_stream(st)
+                    self.peers[(r + k) % W][row: row + (b - a)].copy_(mine, non_blocking=True)
         if wait:
             self.finish()
         return self.full[: self.M]
