@@ -643,19 +643,43 @@ def main_other(args) -> None:
     def interleaved(items, reps):
         """items: list of (name, fn); fn takes a call counter (to rotate between input copies).  Returns {name: median
         microseconds per call}; the repetitions of the items are interleaved.  Each measurement is a burst of BURST calls
-        back to back between two events: the host enqueues the next launch while the previous one runs, so that the
-        host-side cost of a call (5-15 us) is not mistaken for device time of kernels that take 15-50 us."""
+        back to back between two events.  The burst of every item is captured once into a CUDA graph and replayed, so
+        that the device runs the calls back to back and the host-side cost of a call (10-50 us of Python and launch
+        latency) is not mistaken for device time of kernels that take 15-100 us; an item that cannot be captured is
+        timed as a plain burst (the host enqueues the next launch while the previous one runs)."""
         n = 0
         for _n, fn in items:
             fn(0); fn(1)
-        ev = {name: [] for name, _ in items}
         torch.cuda.synchronize()
+        graphs = {}
+        if not args.no_graph:
+            side = torch.cuda.Stream(dev)
+            for name, fn in items:
+                try:
+                    gr = torch.cuda.CUDAGraph()
+                    side.wait_stream(torch.cuda.current_stream(dev))
+                    with torch.cuda.stream(side):
+                        with torch.cuda.graph(gr, stream=side):
+                            for j in range(BURST):
+                                fn(j)
+                    graphs[name] = gr
+                except Exception as e:                      # noqa: BLE001 - capture is an optimisation of the timing only
+                    print(f"[bench] {name}: not captured ({type(e).__name__}), timed as plain bursts", file=sys.stderr)
+                    torch.cuda.synchronize()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            for gr in graphs.values():
+                gr.replay()
+            torch.cuda.synchronize()
+        ev = {name: [] for name, _ in items}
         for _ in range(reps):
             for name, fn in items:
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
-                for _j in range(BURST):
-                    fn(n); n += 1
+                if name in graphs:
+                    graphs[name].replay()
+                else:
+                    for _j in range(BURST):
+                        fn(n); n += 1
                 b.record()
                 ev[name].append((a, b))
             torch.cuda.synchronize()
@@ -689,7 +713,7 @@ def main_other(args) -> None:
         return args.shape is None or args.shape == f"{M}x{K}x{N}"
 
     out = {"workload": args.workload, "n_gpus": 1,
-           "unit_time": f"us per call (median over interleaved repetitions of bursts of {BURST} back-to-back calls)", "reps": reps,
+           "unit_time": f"us per call (median over interleaved repetitions of bursts of {BURST} back-to-back calls" + (")" if args.no_graph else ", each burst replayed from a CUDA graph)"), "reps": reps,
            "data": "synthetic", "items": []}
     if args.workload == "flux2k":
         M = 16384 + 512
@@ -764,19 +788,32 @@ def main_other(args) -> None:
         hmid = up.forward_gathered(canvas, d["row_idx"], mh)
         y = down.forward_rows(hmid, mh)
         cv = [canvas, canvas.clone()]                       # 2 x 403 MB: rotating defeats L2
-        r = interleaved([("gather_quant", lambda i: routing.gather_quant_rows(cv[i % 2], plan)),
+        # plain device copies that move as many bytes as the two memory-bound kernels (half read, half written): what
+        # the memory system gives a kernel of this size in the same timing loop
+        gq_bytes, sc_bytes = 3.0 * M * C + 8.0 * M, 2.0 * C * (int(plan.src.shape[0]) + int(plan.tokens.shape[0]))
+        cp_src = [torch.empty(int(max(gq_bytes, sc_bytes)) // 2 + 4096, dtype=torch.uint8, device=dev) for _ in range(2)]
+        cp_dst = [torch.empty_like(t) for t in cp_src]
+        r = interleaved([("copy_gq", lambda i: cp_dst[i % 2][: int(gq_bytes) // 2].copy_(cp_src[i % 2][: int(gq_bytes) // 2])),
+                         ("copy_sc", lambda i: cp_dst[i % 2][: int(sc_bytes) // 2].copy_(cp_src[i % 2][: int(sc_bytes) // 2])),
+                         ("gather_quant", lambda i: routing.gather_quant_rows(cv[i % 2], plan)),
                          ("up", lambda i: up.forward_gathered(cv[i % 2], d["row_idx"], mh)),
                          ("down", lambda i: down.forward_rows(hmid, mh)),
                          ("scatter", lambda i: routing.scatter_rows_(y, plan, cv[i % 2]))], reps)
         nt, nnz = int(plan.tokens.shape[0]), int(plan.src.shape[0])
+        # canvas rows the scatter has to read: tokens whose accumulated blend weight stays below one (the others take
+        # nothing from the background)
+        n_bg = int((np.add.reduceat(plan.beta.astype(np.float64), plan.ptr[:-1].astype(np.int64)) < 1.0).sum()) if nnz else nt
         out.update({"rows_gathered": M, "rows_hi": mh, "touched_tokens": nt, "canvas": [H * W, C]})
         out["items"] = [
-            {"item": "gather+quantise", "us": r["gather_quant"], "gbs": (3.0 * M * C + 8.0 * M) / r["gather_quant"] / 1e3},
+            {"item": "gather+quantise", "us": r["gather_quant"], "gbs": (3.0 * M * C + 8.0 * M) / r["gather_quant"] / 1e3,
+             "plain_copy_same_bytes_us": r["copy_gq"]},
             {"item": f"routed Linear {C}->{F} (gather, quantise, down-projection, two-tier GEMM)", "us": r["up"],
              "tops": 2.0 * M * C * F / r["up"] / 1e6},
             {"item": f"routed Linear {F}->{C} (quantise, down-projection, two-tier GEMM)", "us": r["down"],
              "tops": 2.0 * M * C * F / r["down"] / 1e6},
-            {"item": "feathered scatter", "us": r["scatter"], "gbs": 2.0 * C * (nnz + 2 * nt) / r["scatter"] / 1e3}]
+            {"item": "feathered scatter", "us": r["scatter"], "gbs": 2.0 * C * (nnz + nt + n_bg) / r["scatter"] / 1e3,
+             "rows_read": nnz, "canvas_rows_written": nt, "canvas_rows_read": n_bg,
+             "plain_copy_same_bytes_us": r["copy_sc"] * (nnz + nt + n_bg) / (nnz + nt)}]
     ops.check_device_status(dev)
     out["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "int8_proxy_tops": 2.0 * float(peaks["bf16_sustained"]), "source": peaks["source"]}
     print(json.dumps(out))
@@ -793,6 +830,7 @@ if __name__ == "__main__":
     ap.add_argument("--rows", type=int, default=M_TOTAL,
                     help="total token rows (default: the 4K stage's 66048); smaller values are for profiler captures only")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="secondary workloads: time plain bursts instead of CUDA-graph replays")
     ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the measurement of the optional output all-gather")
     ap.add_argument("--gather-chunks", type=int, default=0, help="chunks per rank of the overlapped all-gather (0: try 1 and 2)")
     ap.add_argument("--gather-mode", choices=("auto", "store", "push", "nccl"), default="auto",
