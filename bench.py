@@ -733,6 +733,28 @@ def main_other(args) -> None:
                                  "quant_gbs": (3.0 * M * K + 4 * M) / r["quant"] / 1e3,
                                  "lowrank_down_us": r["down"], "lowrank_down_gbs": 2.0 * M * K / r["down"] / 1e3})
             del m, x, xq, sx, t, xc
+        # adaLN prologue of the feed-forward's first Linear (flux/transformer_flux.py:236-240): LayerNorm, modulation and
+        # quantisation as one kernel, against torch's three kernels followed by the plain quantisation
+        K, N = 3072, 12288
+        m = layer(K, N, torch.bfloat16)
+        hc = copies(act(M, K, torch.bfloat16), 5 * M * K)
+        sc = (torch.randn(1, K, generator=g, device=dev) * 0.3).to(torch.bfloat16)
+        sh = (torch.randn(1, K, generator=g, device=dev) * 0.2).to(torch.bfloat16)
+        F = torch.nn.functional
+
+        def unfused(h):
+            z = F.layer_norm(h, (K,), eps=1e-6) * (1 + sc) + sh
+            return int8_exec.quant_rows(z)
+        r = interleaved([("fused", lambda i: ops.adaln_quant_rows(hc[i % len(hc)], sc, sh, 1e-6)),
+                         ("fused_codes_only", lambda i: ops.adaln_quant_rows(hc[i % len(hc)], sc, sh, 1e-6, want_modulated=False)),
+                         ("unfused", lambda i: unfused(hc[i % len(hc)])),
+                         ("forward_adaln", lambda i: m.forward_adaln(hc[i % len(hc)], sc[0], sh[0])),
+                         ("forward_unfused", lambda i: m(F.layer_norm(hc[i % len(hc)], (K,), eps=1e-6) * (1 + sc) + sh))], reps)
+        out["adaln"] = {"rows": M, "K": K, "N": N, "fused_us": r["fused"], "fused_gbs": 5.0 * M * K / r["fused"] / 1e3,
+                        "fused_codes_only_us": r["fused_codes_only"], "fused_codes_only_gbs": 3.0 * M * K / r["fused_codes_only"] / 1e3,
+                        "torch_layernorm_mul_add_then_quant_us": r["unfused"],
+                        "forward_adaln_us": r["forward_adaln"], "forward_after_torch_modulation_us": r["forward_unfused"]}
+        del m, hc
     elif args.workload == "sdxl_pc":
         # the reference's SDXL deployment arm: per-channel weights, per-token activations, fp16, no low-rank branch
         # (deploy/run_sdxl_latency.py:214-224, shapes :280)

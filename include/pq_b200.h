@@ -95,6 +95,20 @@ int pq_gather_rows(const void* canvas, int dtype, int64_t rows, int64_t K, int64
 int pq_quant_rows_g32(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
                       int8_t* q, float* s, void* stream);
 
+/* adaLN prologue fused into the per-token quantisation (no counterpart kernel in the reference, which runs
+ * LayerNorm, multiply, add and the Linear's quantisation as four kernels):
+ *   z[m,:] = LayerNorm(x[m,:]) * (1 + scale[b,:]) + shift[b,:],  b = m / rows_per_sample (0 when rows_per_sample == 0),
+ *   (q, s) = pq_quant_rows(z),
+ * the input of the feed-forward's first Linear in the FLUX blocks (flux/transformer_flux.py:195 `norm2 =
+ * nn.LayerNorm(dim, elementwise_affine=False, eps=1e-6)`, :236-239).  LayerNorm without affine parameters, row
+ * statistics in fp32; every step rounds to the activation type where the reference's 16-bit tensors round.
+ *   x [M,K] row stride ldx; scale, shift [samples, K] row stride ld_mod, same dtype as x;
+ *   x_mod: NULL, or [M,K] (row stride ldxm) that receives z (the low-rank down-projection reads it);
+ *   K % 8 == 0, K <= 16384, strides % 8 == 0, 16-byte aligned x, scale, shift, x_mod. */
+int pq_adaln_quant_rows(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                        const void* scale, const void* shift, int64_t ld_mod, int64_t rows_per_sample, float eps,
+                        void* x_mod, int64_t ldxm, int8_t* q, float* s, void* stream);
+
 /* Dequantisation of materialised accumulators: out[m,n] = float(acc[m,n]) * (s_row[m] * s_col[n])
  * (+ bias[n]) rounded to out_dtype.  Replaces dequant_epilogue / _dequant_epilogue_kernel
  * (deploy/int8_exec.py:233-243, :104-127); kept for API parity, the fused GEMM never needs it.

@@ -13,10 +13,11 @@ build_patch_buckets, fuse_patch_predictions, inner_split_median) were executed i
 and their outputs are committed under tests/golden/ (made by tests/golden/make_golden.py); the oracle
 is pinned against those fixtures by tests/test_oracle_golden.py.
 
-Parity status: integer codes, scales and int32 accumulators are pinned by the fixtures; the assembled
-forward (quantise -> int32 GEMM -> epilogue) has no CPU-runnable reference and no golden vector in the
-reference repository, so that composition is pinned only through its parts and the reference's own
-self-test formula (deploy/int8_exec.py:506-510), which `selftest_unfused_reference` restates.
+Parity status: integer codes, scales and int32 accumulators are pinned by the CPU-made fixtures; the assembled
+forward (quantise -> int32 GEMM -> epilogue) is pinned by tests/golden/forward_reference_gpu.npz, made by running the
+reference's unmodified Int8Linear.forward on a B200 (tests/golden/make_golden_gpu.py; its "cublas" backend, because
+its Triton GEMM kernels do not compile under the installed Triton), against which tests/test_reference_forward.py
+checks this oracle on the CPU and the CUDA path on the GPU.
 """
 from __future__ import annotations
 
@@ -36,6 +37,14 @@ def quant_rows(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     sc = xf.abs().amax(1, keepdim=True).clamp_min(1e-8) / 127
     xq = torch.round(xf / sc).clamp(-127, 127).to(torch.int8)
     return xq, sc[:, 0].contiguous()
+
+
+def adaln_modulate(h: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """Input of the feed-forward's first Linear in a FLUX block: flux/transformer_flux.py:236-237
+    `norm2(h) * (1 + scale_mlp[:, None]) + shift_mlp[:, None]` with `norm2 = nn.LayerNorm(dim, elementwise_affine=False,
+    eps=1e-6)` (:195), evaluated in the tensors' own 16-bit type like the reference.  h [B, T, K]; scale, shift [B, K]."""
+    y = torch.nn.functional.layer_norm(h, (h.shape[-1],), eps=eps)
+    return y * (1 + scale[:, None]) + shift[:, None]
 
 
 def quant_rows_g32(x: torch.Tensor, group: int = 32) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -17,7 +17,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "csrc" / "build"
 LIB = PKG / "libpq_b200.so"
-SOURCES = ["api.cu", "quant.cu", "gemm.cu", "gemm_lr_tc.cu", "gemm_2cta.cu", "gemm_g32.cu", "scatter.cu", "unpack4.cu", "lowrank.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "quant.cu", "adaln_quant.cu", "gemm.cu", "gemm_lr_tc.cu", "gemm_2cta.cu", "gemm_g32.cu", "scatter.cu", "unpack4.cu", "lowrank.cu", "noalloc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

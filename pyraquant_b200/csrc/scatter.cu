@@ -42,23 +42,6 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   f[4] = lo_f32(v.z, tag); f[5] = hi_f32(v.z, tag); f[6] = lo_f32(v.w, tag); f[7] = hi_f32(v.w, tag);
 }
 
-// Packed 16-bit arithmetic on two values per register, round-to-nearest-even, never contracted into a fused
-// multiply-add.  For operands that are themselves 16-bit values the result is bit-identical to the fp32 operation
-// followed by one rounding (which is how the reference's 16-bit tensors compute): a product of two 8- or 11-bit
-// significands is exact in fp32, and a sum of two such values is either exact in fp32 or dominated by the larger
-// operand far beyond the rounding position.
-__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b, __nv_bfloat16) {
-  uint32_t r; asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r;
-}
-__device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b, __nv_bfloat16) {
-  uint32_t r; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r;
-}
-__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b, __half) {
-  uint32_t r; asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r;
-}
-__device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b, __half) {
-  uint32_t r; asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r;
-}
 template <typename T>
 __device__ __forceinline__ bool fits(float v) { return rnd1<T>(v) == v; }
 

@@ -416,6 +416,34 @@ class Int8Linear(nn.Module):
             return out
         return y2.reshape(*shape[:-1], N)
 
+    def forward_adaln(self, h: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-6,
+                      return_modulated: bool = False):
+        """``self(LayerNorm(h) * (1 + scale[:, None]) + shift[:, None])``: the feed-forward's first Linear behind the
+        adaLN modulation of a FLUX block (flux/transformer_flux.py:236-240; LayerNorm without affine parameters, :195).
+        h [B, T, K] with scale / shift [B, K], or h [M, K] with [K].  On CUDA the normalisation, the modulation and the
+        Linear's per-token quantisation are one pass over h (``ops.adaln_quant_rows``); the modulated activations are
+        written out only when the layer has a low-rank branch or the caller wants them (``return_modulated``: the
+        single-stream blocks feed them to the attention as well).  Values match the separate torch kernels except where
+        LayerNorm's fp32 row statistics, summed in another order, move a normalised value across a rounding boundary."""
+        K = h.shape[-1]
+        x2 = h.reshape(-1, K)
+        lr = self.lr_A is not None
+        fused = (x2.shape[0] > 0 and x2.is_cuda and x2.dtype in ops._DT and K % 16 == 0 and K <= 16384
+                 and scale.dtype == x2.dtype and shift.dtype == x2.dtype and not torch.compiler.is_compiling()
+                 and (not lr or self._fusable_lowrank(x2)))
+        if not fused:
+            y = F.layer_norm(h, (K,), eps=eps)
+            z = y * (1 + scale[:, None]) + shift[:, None] if h.dim() == 3 else y * (1 + scale) + shift
+            out = self.forward(z)
+            return (out, z) if return_modulated else out
+        rows_per_sample = h.shape[-2] if h.dim() == 3 else 0
+        xq, sx, z = ops.adaln_quant_rows(x2, scale, shift, eps, rows_per_sample, want_modulated=lr or return_modulated)
+        t = self._down(z) if lr else None
+        y2 = ops._gemm_impl(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B if lr else None, x2.dtype,
+                            lb_t=self._lr_Bt() if lr else None)
+        out = y2.reshape(*h.shape[:-1], self.out_features)
+        return (out, z.reshape(h.shape)) if return_modulated else out
+
     def forward_into(self, x2: torch.Tensor, out: torch.Tensor, out_more: Sequence[torch.Tensor] = ()) -> torch.Tensor:
         """``out[:] = self(x2)`` for 2-D ``x2``, the same values also stored to every tensor of ``out_more`` (same shape,
         dtype and row stride as ``out``; up to ``ops.MAX_OUT_MORE``).  When the shapes allow it the GEMM epilogue

@@ -144,6 +144,34 @@ def _quant_rows_g32_impl(x2: Tensor) -> Tuple[Tensor, Tensor]:
     return q, s
 
 
+def adaln_quant_rows(x2: Tensor, scale: Tensor, shift: Tensor, eps: float = 1e-6, rows_per_sample: int = 0,
+                     want_modulated: bool = True) -> Tuple[Tensor, Tensor, Optional[Tensor]]:
+    """(q, s, z) with z = LayerNorm(x2) * (1 + scale) + shift and (q, s) = quant_rows(z), in one pass over x2
+    (pq_adaln_quant_rows).  scale / shift: [K] or [samples, K]; row m belongs to sample m // rows_per_sample.
+    z is None unless want_modulated."""
+    x2 = _rows_ok(x2)
+    M, K = x2.shape
+    scale = scale.reshape(-1, K); shift = shift.reshape(-1, K)
+    assert scale.shape == shift.shape and scale.dtype == x2.dtype and shift.dtype == x2.dtype, (scale.shape, shift.shape)
+    assert scale.is_cuda and shift.is_cuda and K % 8 == 0 and K <= 16384, K
+    samples = scale.shape[0]
+    if samples == 1:
+        rows_per_sample = 0
+    else:
+        assert rows_per_sample > 0 and samples * rows_per_sample >= M, (samples, rows_per_sample, M)
+    scale = scale.contiguous(); shift = shift.contiguous()
+    q = torch.empty((M, K), dtype=torch.int8, device=x2.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x2.device)
+    z = torch.empty((M, K), dtype=x2.dtype, device=x2.device) if want_modulated else None
+    ld = x2.stride(0) if M > 1 else max(K, x2.stride(0))
+    with _on_device(x2):
+        rc = _LIB().pq_adaln_quant_rows(x2.data_ptr(), _dt(x2.dtype), M, K, ld, scale.data_ptr(), shift.data_ptr(), K,
+                                        int(rows_per_sample), float(eps), _ptr(z), K, q.data_ptr(), s.data_ptr(), _stream(x2))
+    if rc:
+        _lib.check(rc, f"pq_adaln_quant_rows(M={M}, K={K})")
+    return q, s, z
+
+
 def _gather_quant_rows_impl(canvas: Tensor, row_idx: Tensor) -> Tuple[Tensor, Tensor]:
     canvas = _rows_ok(canvas)
     assert row_idx.is_cuda and row_idx.dtype == torch.int32 and row_idx.dim() == 1 and row_idx.is_contiguous()

@@ -141,6 +141,14 @@ def test_scatter_and_gather_argument_checks():
     assert lib.pq_scatter_rows(p16, 64, 4, None, p16, p16, p16, 2, p16, 64, 16, 64, 0, None) == 1
     assert lib.pq_gather_rows(p16, 0, 16, 64, 64, None, 4, p16, 64, None) == 1
     assert lib.pq_gather_quant_rows(p16, 0, 16, 64, 64, None, 4, p16, p16, None) == 1
+    ada = lambda K=64, ldx=64, x=p16, xm=None, ldxm=0, rps=0, eps=1e-6, M=4: lib.pq_adaln_quant_rows(
+        x, 0, M, K, ldx, p16, p16, K, rps, eps, xm, ldxm, p16, p16, None)
+    assert ada(M=0) == 0
+    assert ada(K=60, ldx=64) == 3                     # K % 8
+    assert ada(x=None) == 1
+    assert ada(xm=p16, ldxm=32) == 2                  # x_mod rows shorter than K
+    assert ada(rps=-1) == 2
+    assert ada(eps=-1.0) == 2
     assert lib.pq_i8_mma_issue_loop(0, 10, p16, None, 0, None) == 2
     assert lib.pq_wait_probe(None, 256, 1000, None) == 1
     assert lib.pq_wait_probe(p16, 8, 1000, None) == 8

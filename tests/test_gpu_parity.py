@@ -486,6 +486,61 @@ def test_peer_store_gather_on_one_rank(cuda_dev):
         assert y.shape == (M, N) and torch.equal(y, layer(x))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,T,K", [(1, 300, 3072), (2, 129, 640), (1, 70, 15360), (3, 50, 200), (1, 1, 1024)])
+def test_adaln_quant_rows(cuda_dev, dtype, B, T, K):
+    """LayerNorm + adaLN modulation + per-token quantisation in one kernel (flux/transformer_flux.py:236-239).  The
+    quantisation of the modulated activations is exact; the modulated activations themselves equal the reference
+    sequence (CPU restatement, and torch's own kernels on the GPU) except where the fp32 row statistics, summed in a
+    different order, move a normalised value across a rounding boundary: a few elements in ten thousand, one unit in
+    the last place of the products involved."""
+    g = torch.Generator().manual_seed(B * 1000 + T + K)
+    h = torch.randn(B, T, K, generator=g) * 2 + 0.3
+    h[..., 5] *= 30.0
+    h = h.to(dtype)
+    scale = (torch.randn(B, K, generator=g) * 0.3).to(dtype)
+    shift = (torch.randn(B, K, generator=g) * 0.2).to(dtype)
+    hd, sc, sh = h.to(cuda_dev), scale.to(cuda_dev), shift.to(cuda_dev)
+    q, s, z = ops.adaln_quant_rows(hd.reshape(-1, K), sc, sh, 1e-6, T)
+    ops.check_device_status(cuda_dev)
+    qo, so = oracle.quant_rows(z.cpu())
+    assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+    q2, s2, none = ops.adaln_quant_rows(hd.reshape(-1, K), sc, sh, 1e-6, T, want_modulated=False)
+    assert none is None and torch.equal(q2, q) and torch.equal(s2, s)
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    refs = [oracle.adaln_modulate(h, scale, shift, 1e-6).reshape(-1, K),
+            (F.layer_norm(hd, (K,), eps=1e-6) * (1 + sc[:, None]) + sh[:, None]).reshape(-1, K).cpu()]
+    for zo in refs:
+        diff = (z.cpu().float() - zo.float()).abs()
+        bound = 4 * ulp * (zo.float().abs() + shift.float().abs().repeat_interleave(T, 0)) + 1e-6
+        assert bool((diff <= bound).all()), (diff - bound).max().item()
+        assert (z.cpu() != zo).float().mean().item() <= 2e-3
+
+
+def test_forward_adaln(cuda_dev):
+    """`Int8Linear.forward_adaln` against the separate sequence: torch's LayerNorm and modulation, then the layer."""
+    g = torch.Generator().manual_seed(21)
+    B, T, K, N = 2, 333, 1024, 768
+    layer = _toy_layer(cuda_dev, g, K, N, lowrank=True)
+    plain = _toy_layer(cuda_dev, g, K, N, lowrank=False)
+    h = (torch.randn(B, T, K, generator=g) * 1.5).to(torch.bfloat16).to(cuda_dev)
+    scale = (torch.randn(B, K, generator=g) * 0.3).to(torch.bfloat16).to(cuda_dev)
+    shift = (torch.randn(B, K, generator=g) * 0.2).to(torch.bfloat16).to(cuda_dev)
+    z_ref = F.layer_norm(h, (K,), eps=1e-6) * (1 + scale[:, None]) + shift[:, None]
+    for m in (layer, plain):
+        y, z = m.forward_adaln(h, scale, shift, return_modulated=True)
+        assert y.shape == (B, T, N) and z.shape == h.shape
+        assert (z != z_ref).float().mean().item() <= 2e-3
+        assert torch.equal(y, m(z))                                  # the layer on the kernel's own modulated rows
+        y_ref = m(z_ref)
+        rel = ((y.float() - y_ref.float()).norm() / y_ref.float().norm()).item()
+        assert rel < 2e-3, rel
+        assert torch.equal(m.forward_adaln(h, scale, shift), y)
+    # 2-D input with one modulation vector
+    y2 = layer.forward_adaln(h[0], scale[0], shift[0])
+    assert torch.equal(y2, layer.forward_adaln(h[:1], scale[:1], shift[:1])[0])
+
+
 def test_split_input_linear(cuda_dev):
     """y = L0(x[..., :in0]) + L1(x[..., in0:]) with the sum in the second GEMM's epilogue: identical to the two layers
     and a torch add (pyraquant/external_quant.py:191-192), 3-D input, strided halves."""

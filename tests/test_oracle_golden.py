@@ -119,3 +119,18 @@ def test_forward_agrees_with_reference_selftest_formula():
     xq, sx = oracle.quant_rows(L["x"])
     ref = oracle.selftest_unfused_reference(xq, sx, wq, ws, L["bias"]).float()
     assert ((y - ref).norm() / ref.norm()).item() < 1e-3
+
+
+def test_adaln_modulate_follows_the_float64_formula():
+    """The restatement of flux/transformer_flux.py:236-237 in the tensors' own type against float64 arithmetic."""
+    g = torch.Generator().manual_seed(3)
+    B, T, K = 2, 40, 256
+    h = (torch.randn(B, T, K, generator=g) * 2 + 0.5).to(torch.bfloat16)
+    scale = (torch.randn(B, K, generator=g) * 0.3).to(torch.bfloat16)
+    shift = (torch.randn(B, K, generator=g) * 0.2).to(torch.bfloat16)
+    z = oracle.adaln_modulate(h, scale, shift, 1e-6)
+    hd = h.double()
+    y = (hd - hd.mean(-1, keepdim=True)) / torch.sqrt(hd.var(-1, unbiased=False, keepdim=True) + 1e-6)
+    want = y * (1 + scale.double()[:, None]) + shift.double()[:, None]
+    assert z.dtype == torch.bfloat16 and z.shape == h.shape
+    assert bool(((z.double() - want).abs() <= 2.0 ** -6 * (want.abs() + shift.double().abs()[:, None]) + 1e-3).all())
