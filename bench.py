@@ -375,12 +375,12 @@ def main_ours(args):
         seq_ms = timed_steps(lambda: [parallel.all_gather_rows(m(x), M_TOTAL) for m, x in zip(mods, xs)], n_g)
         seq_out = [parallel.all_gather_rows(m(x), M_TOTAL) for m, x in zip(mods, xs)]
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        classes = {"push": parallel.PeerPushGather, "nccl": parallel.OverlappedRowGather, "store": parallel.PeerStoreGather}
+        classes = {"push": parallel.PeerPushGather, "pushcopy": parallel.PeerPushGather, "nccl": parallel.OverlappedRowGather, "store": parallel.PeerStoreGather}
         # candidates (mode, chunks per rank): more chunks start the transfers earlier but cost smaller launches and more
         # copies in flight (measured: two chunks win on 2 GPUs, one chunk -- only the next layer computes behind the
         # transfers -- on 8); the store mode needs no chunks: tiles leave from the GEMM epilogue as they are finished
         if args.gather_mode == "auto":
-            cands = [("store", 1), ("push", 1), ("push", 2), ("push", 4)]
+            cands = [("store", 1), ("push", 1), ("push", 2), ("push", 4)] + ([("pushcopy", 1), ("pushcopy", 2)] if args.gather_try_copy else [])
         elif args.gather_mode == "store":
             cands = [("store", max(1, args.gather_chunks))]
         else:
@@ -389,7 +389,8 @@ def main_ours(args):
         tried = []
         for mode, chunks in cands:
             c = parallel.cyclic_block_rows(M_TOTAL, world, chunks)
-            ogs = [classes[mode](M_TOTAL, N, torch.bfloat16, dev, chunks=chunks) for _n, _K, N in LAYERS]
+            kw = {"direct": False} if mode == "pushcopy" else {}
+            ogs = [classes[mode](M_TOTAL, N, torch.bfloat16, dev, chunks=chunks, **kw) for _n, _K, N in LAYERS]
             xl = []
             for x in xs:                               # this rank's rows, block after block (synthetic rows: any will do)
                 xp = x.new_zeros((chunks * c, x.shape[1]))
@@ -420,7 +421,8 @@ def main_ours(args):
         del seq_out
         chunks, mode = best[2], best[3]
         recv = (world - 1) / world * sum(M_TOTAL * N * 2.0 for _n, _K, N in LAYERS)
-        how = {"push": f"rows dealt out block-cyclically in {chunks} chunks per rank, chunk i pushed into every peer's output buffer by "
+        how = {"pushcopy": "as push, through a staging tensor",
+               "push": f"rows dealt out block-cyclically in {chunks} chunks per rank, chunk i pushed into every peer's output buffer by "
                        f"device-to-device copies (copy engines over NVLink, symmetric-memory buffers) while the next chunk or layer "
                        f"computes; two one-element all-reduces order the step",
                "store": "the GEMM epilogue stores every output tile into this GPU's and every peer's output buffer (plain vector stores to "
@@ -858,6 +860,7 @@ if __name__ == "__main__":
     ap.add_argument("--gather-mode", choices=("auto", "store", "push", "nccl"), default="auto",
                     help="all-gather hidden behind the compute: stores to peers from the GEMM epilogue, copy-engine pushes into "
                          "peers' buffers, NCCL per chunk; auto tries the first two and reports the faster")
+    ap.add_argument("--gather-try-copy", action="store_true", help="also try the push mode with a local staging copy")
     ap.add_argument("--gather-sms", type=int, default=-1,
                     help="SMs the GEMM leaves free while NCCL gathers (-1: try 0, 8 and 16 and report the best)")
     ap.add_argument("--no-cpu", action="store_true")

@@ -142,9 +142,10 @@ class PeerPushGather(OverlappedRowGather):
     overwrites a buffer its owner may still be reading from the previous call."""
 
     def __init__(self, M: int, N: int, dtype: torch.dtype, device, chunks: int = 4, group: Optional[dist.ProcessGroup] = None,
-                 copy_streams: int = 2):
+                 copy_streams: int = 0, direct: bool = True):
         super().__init__(M, N, dtype, device, chunks, group)
         self.device = torch.device(device)
+        self.direct = direct           # the layer writes its rows of this rank's buffer itself (no local copy)
         self.peers = [self.full] * self.world
         if self.world > 1:
             import torch.distributed._symmetric_memory as symm_mem
@@ -152,7 +153,10 @@ class PeerPushGather(OverlappedRowGather):
             self.full = symm_mem.empty(shape, dtype=dtype, device=self.device)
             self._handle = symm_mem.rendezvous(self.full, group=group if group is not None else dist.group.WORLD)
             self.peers = [self.full if r == self.rank else self._handle.get_buffer(r, shape, dtype) for r in range(self.world)]
-        self.streams = [torch.cuda.Stream(self.device) for _ in range(max(1, copy_streams))]
+        # one stream per peer (copy_streams = 0): copies on one stream run one after the other, and streams may share
+        # a copy engine, so with few streams the pushes of a rank can end up serialised at half the link rate
+        n_streams = copy_streams if copy_streams > 0 else max(1, self.world - 1)
+        self.streams = [torch.cuda.Stream(self.device) for _ in range(n_streams)]
         self._token = torch.zeros(1, device=self.device)
 
     def run(self, forward, x: torch.Tensor, local: bool = False, wait: bool = True) -> torch.Tensor:
@@ -168,16 +172,21 @@ class PeerPushGather(OverlappedRowGather):
             xb = x[i * c: i * c + (b - a)] if local else x[a:b]
             row = (i * W + r) * c
             mine = self.full[row: row + (b - a)]
-            if hasattr(forward, "forward_into"):                     # the layer writes its rows of this rank's buffer itself
+            if self.direct and hasattr(forward, "forward_into"):
                 forward.forward_into(xb, mine)
+                srcrows = mine
             else:
-                mine.copy_(forward(xb))
+                srcrows = forward(xb)
+                mine.copy_(srcrows)
             done = torch.cuda.Event(); done.record(cur)
             for k in range(1, W):                                    # every peer is one hop away on a switch: round robin
                 st = self.streams[k % len(self.streams)]
                 st.wait_event(done)
                 with torch.cuda.stream(st):
-                    self.peers[(r + k) % W][row: row + (b - a)].copy_(mine, non_blocking=True)
+                    self.peers[(r + k) % W][row: row + (b - a)].copy_(srcrows, non_blocking=True)
+            if srcrows is not mine:
+                for st in self.streams:
+                    srcrows.record_stream(st)
         if wait:
             self.finish()
         return self.full[: self.M]
