@@ -17,7 +17,16 @@
 // the latency of the tensor-memory loads better than eight; within a slot pair the load of the next 16 rows is in flight
 // while the current ones are folded.  Slots are handed over in pairs, so the MMA thread refills one pair while the
 // warps work on the other.
-// Tried and dropped: a row-per-thread arrangement (tcgen05.ld 32x32b: the row scale becomes a register, but the loads
+// Probes of where the time goes (16384 x 1280 -> 10240, cycles per group and SM at 1.9 GHz): the full kernel 715; the
+// same with the arithmetic removed 405; with the tensor-memory loads removed as well, i.e. only the slot hand-shakes
+// between the MMA thread and the sixteen warps, 246 (a slot pair needs about 980 cycles from its release to being
+// complete again, hidden as long as draining and folding the other pair takes longer); requesting all four chunks of a
+// pair at once instead of one ahead does not speed up the loads (405 -> 400): the drain is a throughput limit of about
+// 160-200 bytes per cycle, not a latency one.  Drain (about 320) and arithmetic (about 310: the conversion pipe takes
+// 256 of them) add up instead of overlapping, whatever the warps' arrangement.
+// Tried and dropped: slots handed over one by one with the next chunk always requested across slot and stage boundaries
+// (non-blocking probe of the next slot's barrier): 356 instead of 408 TOPS, spills at 96 registers;
+// a row-per-thread arrangement (tcgen05.ld 32x32b: the row scale becomes a register, but the loads
 // are no faster and the column scales need twice the shared-memory loads); accumulators pre-biased with 0x4B400000 so
 // that the int32 result read as fp32 bits needs only a subtraction (the tcgen05.st that restores the bias costs more
 // tensor-memory bandwidth than the integer additions it saves); keeping a load in flight across slot pairs, stages and
