@@ -229,6 +229,10 @@ int pq_unpack_int4(const uint8_t* packed, int64_t ldp, int8_t* out, int64_t ldo,
  * e in [ptr[j], ptr[j+1]):  local = sum_e beta[e] * y[src[e], :], bsum = sum_e beta[e] (both
  * accumulated in the canvas dtype, in list order, like the reference's bf16 accumulators), then
  *   canvas[j] = (1 - clamp(bsum,0,1)) * canvas[j] + clamp(bsum,0,1) * (local / max(bsum, 1e-8)).
+ * Every intermediate is rounded to the canvas dtype where the reference's 16-bit tensors round (bit-identical
+ * results for finite data).  A token whose factor 1 - clamp(bsum,0,1) rounds to zero takes nothing from the canvas and
+ * its old row is not read (0 * b + u == u for every finite b; an Inf/NaN already on the canvas under such a token does
+ * not propagate, unlike in the reference's formula).
  * Tokens without contributors are left untouched.  `tokens` is the list of canvas rows that have
  * at least one contributor (n_tokens of them); ptr has n_tokens + 1 entries and indexes src/beta.
  * y [M_act, C] row stride ldy; canvas [rows, C] row stride ldc.  C % 8 == 0, 16-byte aligned. */
