@@ -23,7 +23,8 @@
 // complete again, hidden as long as draining and folding the other pair takes longer); requesting all four chunks of a
 // pair at once instead of one ahead does not speed up the loads (405 -> 400): the drain is a throughput limit of about
 // 160-200 bytes per cycle, not a latency one.  Drain (about 320) and arithmetic (about 310: the conversion pipe takes
-// 256 of them) add up instead of overlapping, whatever the warps' arrangement.
+// 256 of them) add up instead of overlapping, whatever the warps' arrangement: requesting the next chunk only after
+// the current one has been folded, i.e. with no overlap by construction, measures the same (415 against 406 TOPS).
 // Tried and dropped: slots handed over one by one with the next chunk always requested across slot and stage boundaries
 // (non-blocking probe of the next slot's barrier): 356 instead of 408 TOPS, spills at 96 registers;
 // a row-per-thread arrangement (tcgen05.ld 32x32b: the row scale becomes a register, but the loads
