@@ -838,6 +838,59 @@ def test_routed_gather_scatter_vs_oracle(cuda_dev, dtype):
     assert torch.equal(got.cpu().reshape(H * W, C)[~touched], bg.reshape(H * W, C)[~touched])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scatter_contributor_lists_of_every_kind(cuda_dev, dtype):
+    """`pq_scatter_rows` on hand-made contributor lists that the routing plans of the other tests do not produce: one
+    full-weight contributor (copied), fractional weights, weights that are not values of the canvas type (fp32
+    arithmetic instead of the packed one), two and five contributors, more than 32 (the list is then walked from global
+    memory), out-of-range row numbers (skipped), an all-invalid list (weight sum 0), signed zeros.  Checked bit for bit
+    against the reference's sequence of roundings evaluated in fp32 with explicit rounding after every step."""
+    g = torch.Generator().manual_seed(77)
+    C, M_act, rows = 264, 64, 40
+    y = (torch.randn(M_act, C, generator=g) * 2).to(dtype)
+    y[3, :20] = -0.0; y[5, 7] = 0.0
+    canvas = torch.randn(rows, C, generator=g).to(dtype)
+    canvas[2, :9] = -0.0
+    q = lambda v: float(torch.tensor(v).to(dtype))                     # a weight representable in the canvas type
+    lists = [
+        [(3, 1.0)],                                                       # copy, with -0 in the row
+        [(7, q(0.37))],                                                   # one fractional weight: background keeps a share
+        [(8, 0.3)],                                                       # 0.3 is not a bf16 / fp16 value
+        [(1, 1.0), (2, q(0.25))],                                         # sum > 1, two contributors
+        [(9, q(0.5)), (10, q(0.5))],                                      # power-of-two divisor
+        [(11, q(0.2)), (12, q(0.3)), (13, q(0.1)), (14, q(0.15)), (15, q(0.05))],
+        [(i % M_act, q(0.02)) for i in range(40)],                        # more than 32 entries
+        [(-1, 1.0), (5, 1.0)],                                            # an invalid row number in front of a valid one
+        [(M_act + 3, q(0.5))],                                            # nothing valid: weight sum 0
+        [(20, 1.0), (-5, q(0.5)), (21, q(0.125))],
+    ]
+    tokens = torch.tensor([0, 2, 5, 6, 9, 17, 18, 30, 31, 39], dtype=torch.int32)
+    ptr, src, beta = [0], [], []
+    for lst in lists:
+        src += [r for r, _ in lst]; beta += [b for _, b in lst]; ptr.append(len(src))
+    rnd = lambda t: t.to(dtype).float()
+    want = canvas.clone()
+    for tok, lst in zip(tokens.tolist(), lists):
+        local = torch.zeros(C); bsum = torch.zeros(())
+        for r, b in lst:
+            if r < 0 or r >= M_act:
+                continue
+            bt = torch.tensor(b, dtype=torch.float32)
+            local = rnd(local + rnd(bt * y[r].float()))
+            bsum = rnd(bsum + bt)
+        bm = bsum.clamp(0.0, 1.0)
+        denom = rnd(bsum.clamp_min(1e-8))
+        om = rnd(1.0 - bm)
+        c = rnd(local / denom) if bsum > 0 else torch.zeros(C)
+        want[tok] = (rnd(om * canvas[tok].float()) + rnd(bm * c)).to(dtype)
+    got = canvas.clone().to(cuda_dev)
+    ops._scatter_rows_impl(y.to(cuda_dev), tokens.to(cuda_dev), torch.tensor(ptr, dtype=torch.int32, device=cuda_dev),
+                           torch.tensor(src, dtype=torch.int32, device=cuda_dev),
+                           torch.tensor(beta, dtype=torch.float32, device=cuda_dev), got)
+    torch.cuda.synchronize()
+    assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16))
+
+
 def test_routed_two_tier_linear(cuda_dev):
     """Config-4 shape in miniature: routed rows -> Linear with per-leaf hi/lo weights -> scatter."""
     H = W = 32; K = 256; N = 512
