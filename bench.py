@@ -789,6 +789,19 @@ def main_other(args) -> None:
                         "torch_layernorm_mul_add_then_quant_us": r["unfused"],
                         "forward_adaln_us": r["forward_adaln"], "forward_after_torch_modulation_us": r["forward_unfused"]}
         del m, hc
+        # tail of a block (flux/transformer_flux.py:145-149): residual + gate * Linear(x), in the GEMM epilogue against
+        # the layer followed by torch's multiply and add
+        K, N = 12288, 3072
+        m = layer(K, N, torch.bfloat16)
+        xc = copies(act(M, K, torch.bfloat16), 3 * M * K)
+        gate = (torch.randn(N, generator=g, device=dev) * 0.5).to(torch.bfloat16)
+        resid = [torch.randn(M, N, generator=g, device=dev).to(torch.bfloat16) for _ in range(3)]
+        r = interleaved([("fused", lambda i: m.forward_gated_residual(xc[i % len(xc)], gate, resid[i % 3])),
+                         ("unfused", lambda i: resid[i % 3].add_(gate * m(xc[i % len(xc)]))),
+                         ("linear", lambda i: m(xc[i % len(xc)]))], reps)
+        out["gated_residual"] = {"rows": M, "K": K, "N": N, "fused_us": r["fused"], "linear_then_torch_mul_add_us": r["unfused"],
+                                 "linear_alone_us": r["linear"]}
+        del m, xc, resid
     elif args.workload == "sdxl_pc":
         # the reference's SDXL deployment arm: per-channel weights, per-token activations, fp16, no low-rank branch
         # (deploy/run_sdxl_latency.py:214-224, shapes :280)

@@ -153,12 +153,29 @@ int pq_int8_gemm(const int8_t* xq, int64_t ldx, const float* s_row,
  * PQ_ERR_UNSUPPORTED and nothing is launched.  epilogue == 0 is pq_int8_gemm. */
 #define PQ_EPI_ACCUMULATE 1
 #define PQ_EPI_GELU_TANH 2
+#define PQ_EPI_GATE 4          /* set by pq_int8_gemm_gated; not accepted by pq_int8_gemm_ex */
 int pq_int8_gemm_ex(const int8_t* xq, int64_t ldx, const float* s_row,
                     const int8_t* w, int64_t ldw, const float* s_col, const float* bias,
                     const void* t, int64_t ldt, const void* lb, int64_t ldb, const void* lb_t, int R, int lr_dtype,
                     void* out, int out_dtype, int64_t ldo,
                     int64_t M, int64_t N, int64_t K, int epilogue,
                     void* workspace, size_t ws_bytes, void* stream);
+
+/* Tail of a FLUX block in the Linear's epilogue (no counterpart kernel in the reference, which runs a multiply and an
+ * add after the Linear): with PQ_EPI_ACCUMULATE,
+ *   out[m,n] = round(out[m,n] + round(gate[b,n] * round(y[m,n]))),   b = m / rows_per_sample (0 when that is 0),
+ * i.e. `residual + gate.unsqueeze(1) * proj_out(x)` with the residual stream in `out`, updated in place
+ * (flux/transformer_flux.py:145-149 for the single-stream blocks; :224-225, :240-242 for attention and feed-forward
+ * outputs of the double-stream blocks).  Every step rounds to out_dtype where the reference's 16-bit tensors round; fp16
+ * sums are clipped to +-65504 as the block does.  Without PQ_EPI_ACCUMULATE the product alone is stored.
+ * gate [samples, N] in out_dtype, row stride ld_gate (% 8 == 0, >= N), 16-byte aligned.  Other rules as pq_int8_gemm_ex. */
+int pq_int8_gemm_gated(const int8_t* xq, int64_t ldx, const float* s_row,
+                       const int8_t* w, int64_t ldw, const float* s_col, const float* bias,
+                       const void* t, int64_t ldt, const void* lb, int64_t ldb, const void* lb_t, int R, int lr_dtype,
+                       const void* gate, int64_t ld_gate, int64_t rows_per_sample,
+                       void* out, int out_dtype, int64_t ldo,
+                       int64_t M, int64_t N, int64_t K, int epilogue,
+                       void* workspace, size_t ws_bytes, void* stream);
 
 /* pq_int8_gemm_ex whose epilogue stores every output tile to n_out_more further buffers as well (no counterpart in
  * the reference, which runs on one GPU).  `out_more` is a HOST array of n_out_more (<= PQ_MAX_OUT_MORE) device

@@ -45,6 +45,10 @@ SIGNATURES = {
                                 c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int,
                                 c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int,
                                 c_void_p, c_size_t, c_void_p]),
+    "pq_int8_gemm_gated": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                   c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int,
+                                   c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int,
+                                   c_void_p, c_size_t, c_void_p]),
     "pq_int8_gemm_bcast": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                    c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int,
                                    c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int,

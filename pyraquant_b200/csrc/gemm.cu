@@ -520,9 +520,12 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
                 const int8_t* w1, const float* sc1, int64_t ldw, const float* bias, const void* t, int64_t ldt,
                 const void* lb, int64_t ldb, const void* lb_t, int R, int lr_dtype, void* out, int out_dtype,
                 int64_t ldo, int64_t m_split, int64_t M, int64_t N, int64_t K, void* workspace, size_t ws_bytes,
-                int32_t* dbg_acc, void* stream, int epi_flags = 0, void* const* out_more = nullptr, int n_out_more = 0) {
+                int32_t* dbg_acc, void* stream, int epi_flags = 0, void* const* out_more = nullptr, int n_out_more = 0,
+                const void* gate = nullptr, int64_t ld_gate = 0, int64_t gate_rows = 0) {
   if (M < 0 || N <= 0 || K <= 0 || m_split < 0 || m_split > M) return PQ_ERR_SHAPE;
-  if (epi_flags & ~(PQ_EPI_ACCUMULATE | PQ_EPI_GELU_TANH)) return PQ_ERR_UNSUPPORTED;
+  if (epi_flags & ~(PQ_EPI_ACCUMULATE | PQ_EPI_GELU_TANH | PQ_EPI_GATE)) return PQ_ERR_UNSUPPORTED;
+  if (((epi_flags & PQ_EPI_GATE) != 0) != (gate != nullptr)) return PQ_ERR_NULL;
+  if (gate != nullptr && (gate_rows < 0 || ld_gate < N || ld_gate % 8 != 0 || !aligned_to(gate, 16))) return PQ_ERR_ALIGN;
   if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return PQ_ERR_SHAPE;
   if (out_dtype != PQ_DTYPE_BF16 && out_dtype != PQ_DTYPE_FP16) return PQ_ERR_DTYPE;
   if (M == 0) return PQ_OK;
@@ -561,6 +564,7 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
                  ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + 256) : nullptr;
   p.sched_pm = p.sched_pn = p.sched_m_steps = p.sched_n_rounds = 1;
   p.sched_panel = 0; p.l2_hints = 0; p.tma_store = 0;
+  p.gate = gate; p.ld_gate = ld_gate; p.gate_rows = gate_rows;
   p.n_out_more = n_out_more;
   for (int d = 0; d < 7; ++d) p.out_more[d] = d < n_out_more ? out_more[d] : nullptr;
 
@@ -634,6 +638,17 @@ extern "C" int pq_int8_gemm_ex(const int8_t* xq, int64_t ldx, const float* s_row
                                void* stream) {
   return gemm_common(xq, ldx, s_row, w, s_col, nullptr, nullptr, ldw, bias, t, ldt, lb, ldb, lb_t, R, lr_dtype, out,
                      out_dtype, ldo, M, M, N, K, workspace, ws_bytes, nullptr, stream, epilogue);
+}
+
+extern "C" int pq_int8_gemm_gated(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t* w, int64_t ldw,
+                                  const float* s_col, const float* bias, const void* t, int64_t ldt, const void* lb,
+                                  int64_t ldb, const void* lb_t, int R, int lr_dtype, const void* gate, int64_t ld_gate,
+                                  int64_t rows_per_sample, void* out, int out_dtype, int64_t ldo, int64_t M, int64_t N,
+                                  int64_t K, int epilogue, void* workspace, size_t ws_bytes, void* stream) {
+  if (gate == nullptr) return PQ_ERR_NULL;
+  return gemm_common(xq, ldx, s_row, w, s_col, nullptr, nullptr, ldw, bias, t, ldt, lb, ldb, lb_t, R, lr_dtype, out,
+                     out_dtype, ldo, M, M, N, K, workspace, ws_bytes, nullptr, stream, epilogue | PQ_EPI_GATE, nullptr, 0,
+                     gate, ld_gate, rows_per_sample);
 }
 
 extern "C" int pq_int8_gemm_bcast(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t* w, int64_t ldw,

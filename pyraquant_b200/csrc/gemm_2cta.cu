@@ -559,16 +559,45 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
             quad_transpose(wB, q);
             OutT* pA = out + static_cast<int64_t>(rA) * p.ldo + col_grp + q * 8;
             OutT* pB = out + static_cast<int64_t>(rB) * p.ldo + col_grp + q * 8;
+            if (p.epi_flags & PQ_EPI_GATE) {
+              // y * gate[sample, column] in the output type (the rounded Linear output times the block's gate vector, as
+              // the reference's 16-bit tensors compute it), then the residual sum below; the eight columns of this lane
+              // are one 16-byte load of the gate row
+              const OutT* gbase = static_cast<const OutT*>(p.gate) + col_grp + q * 8;
+              int64_t sA = 0, sB = 0;
+              if (p.gate_rows > 0) { sA = rA / p.gate_rows; sB = rB / p.gate_rows; }
+              if (rA < row_end) {
+                const uint4 gv = ld_v4(gbase + sA * p.ld_gate);
+                wA[0] = mul2(wA[0], gv.x, OutT{}); wA[1] = mul2(wA[1], gv.y, OutT{});
+                wA[2] = mul2(wA[2], gv.z, OutT{}); wA[3] = mul2(wA[3], gv.w, OutT{});
+              }
+              if (rB < row_end) {
+                const uint4 gv = ld_v4(gbase + sB * p.ld_gate);
+                wB[0] = mul2(wB[0], gv.x, OutT{}); wB[1] = mul2(wB[1], gv.y, OutT{});
+                wB[2] = mul2(wB[2], gv.z, OutT{}); wB[3] = mul2(wB[3], gv.w, OutT{});
+              }
+            }
             if (p.epi_flags & PQ_EPI_ACCUMULATE) {          // out += y: the sum of two rounded tensors, rounded once
+              const bool clip = (p.epi_flags & PQ_EPI_GATE) != 0;      // the block tail clips fp16 sums (no-op for bf16)
               if (rA < row_end) {
                 const uint4 o = ld_v4(pA);
-                wA[0] = add_word<OutT>(wA[0], o.x); wA[1] = add_word<OutT>(wA[1], o.y);
-                wA[2] = add_word<OutT>(wA[2], o.z); wA[3] = add_word<OutT>(wA[3], o.w);
+                if (clip) {
+                  wA[0] = add_word_clipped<OutT>(wA[0], o.x); wA[1] = add_word_clipped<OutT>(wA[1], o.y);
+                  wA[2] = add_word_clipped<OutT>(wA[2], o.z); wA[3] = add_word_clipped<OutT>(wA[3], o.w);
+                } else {
+                  wA[0] = add_word<OutT>(wA[0], o.x); wA[1] = add_word<OutT>(wA[1], o.y);
+                  wA[2] = add_word<OutT>(wA[2], o.z); wA[3] = add_word<OutT>(wA[3], o.w);
+                }
               }
               if (rB < row_end) {
                 const uint4 o = ld_v4(pB);
-                wB[0] = add_word<OutT>(wB[0], o.x); wB[1] = add_word<OutT>(wB[1], o.y);
-                wB[2] = add_word<OutT>(wB[2], o.z); wB[3] = add_word<OutT>(wB[3], o.w);
+                if (clip) {
+                  wB[0] = add_word_clipped<OutT>(wB[0], o.x); wB[1] = add_word_clipped<OutT>(wB[1], o.y);
+                  wB[2] = add_word_clipped<OutT>(wB[2], o.z); wB[3] = add_word_clipped<OutT>(wB[3], o.w);
+                } else {
+                  wB[0] = add_word<OutT>(wB[0], o.x); wB[1] = add_word<OutT>(wB[1], o.y);
+                  wB[2] = add_word<OutT>(wB[2], o.z); wB[3] = add_word<OutT>(wB[3], o.w);
+                }
               }
             }
             if (p.n_out_more > 0) {
@@ -745,7 +774,7 @@ int launch_pair_ew(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtenso
   // sixteen-warp tiles of a plain single-tier call store through shared memory + TMA when the output allows it
   CUtensorMap tmOut = tmA;
   p.tma_store = 0;
-  if (EW == 16 && !HAS_LR && p.m_split == p.M && !(p.epi_flags & PQ_EPI_ACCUMULATE) && p.n_out_more == 0 && options().gemm_tma_store != 0 &&
+  if (EW == 16 && !HAS_LR && p.m_split == p.M && !(p.epi_flags & (PQ_EPI_ACCUMULATE | PQ_EPI_GATE)) && p.n_out_more == 0 && options().gemm_tma_store != 0 &&
       p.ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
     const int rc = make_out_map16(&tmOut, p.out, p.M, p.N, p.ldo, std::is_same<OutT, __nv_bfloat16>::value);
     if (rc != PQ_OK) return rc;

@@ -27,6 +27,9 @@ struct GemmParams {
   int sched_panel;          // CTA-pair kernel: row steps per panel (0 = all rows in one panel)
   int l2_hints;             // CTA-pair kernel: Options::gemm_l2_hints
   int tma_store;            // CTA-pair kernel, sixteen epilogue warps: output tiles leave through shared memory + TMA
+  const void* gate;         // CTA-pair kernel, PQ_EPI_GATE: [samples, N] factors in the output type (row stride ld_gate)
+  int64_t ld_gate;
+  int64_t gate_rows;        // rows per sample (0: one sample)
   void* out_more[7];        // CTA-pair kernel: further buffers (same shape and row stride as out) that receive every output store
   int n_out_more;
   long long* timing;        // experiments: per-CTA cycle counters [grid][8] (NULL in normal use)
@@ -44,6 +47,16 @@ __device__ __forceinline__ float gelu_tanh_f32(float x) {
 template <typename OutT>
 __device__ __forceinline__ uint32_t gelu_word(uint32_t w) {
   return pack2(gelu_tanh_f32(lo_f32(w, OutT{})), gelu_tanh_f32(hi_f32(w, OutT{})), OutT{});
+}
+// The FLUX blocks clip fp16 hidden states to the finite range after the residual sum (flux/transformer_flux.py:148-149);
+// clamping the fp32 sum before the rounding gives the same value (a sum beyond 65520 would round to infinity and be clipped
+// to 65504, anything up to 65520 rounds to at most 65504 by itself).
+__device__ __forceinline__ float clip_like_block(float v, __half) { return fminf(fmaxf(v, -65504.0f), 65504.0f); }
+__device__ __forceinline__ float clip_like_block(float v, __nv_bfloat16) { return v; }
+template <typename OutT>
+__device__ __forceinline__ uint32_t add_word_clipped(uint32_t w, uint32_t prev) {
+  return pack2(clip_like_block(lo_f32(w, OutT{}) + lo_f32(prev, OutT{}), OutT{}),
+               clip_like_block(hi_f32(w, OutT{}) + hi_f32(prev, OutT{}), OutT{}), OutT{});
 }
 template <typename OutT>
 __device__ __forceinline__ uint32_t add_word(uint32_t w, uint32_t prev) {

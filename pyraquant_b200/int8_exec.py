@@ -444,6 +444,37 @@ class Int8Linear(nn.Module):
         out = y2.reshape(*h.shape[:-1], self.out_features)
         return (out, z.reshape(h.shape)) if return_modulated else out
 
+    def forward_gated_residual(self, x: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """``residual += gate.unsqueeze(1) * self(x)``, in place, returns ``residual``: the tail of a FLUX block
+        (flux/transformer_flux.py:145-149: ``hidden_states = residual + gate.unsqueeze(1) * proj_out(...)``, fp16 clipped to
+        the finite range; likewise :224-225 and :240-242 for the attention and feed-forward outputs of the double-stream
+        blocks).  x [B, T, K] with gate [B, N] and residual [B, T, N], or x [M, K] with gate [N].  On CUDA the product
+        and the sum happen in the GEMM epilogue (``pq_int8_gemm_gated``), rounding where the separate torch kernels round:
+        the values are identical to the unfused sequence."""
+        K, N = x.shape[-1], self.out_features
+        x2 = x.reshape(-1, K)
+        M = x2.shape[0]
+        res2 = residual.reshape(-1, N)
+        lr = self.lr_A is not None
+        fused = (M > 0 and x2.is_cuda and x2.dtype in ops._DT and K % 16 == 0 and not torch.compiler.is_compiling()
+                 and gate.dtype == x2.dtype and residual.dtype == x2.dtype and res2.shape[0] == M
+                 and res2.stride(1) == 1 and res2.data_ptr() == residual.data_ptr()
+                 and (not lr or self._fusable_lowrank(x2)) and ops.epilogue_supported(N, res2.stride(0), res2.data_ptr(), lr))
+        if not fused:
+            y = self.forward(x)
+            residual.add_((gate.unsqueeze(1) if x.dim() == 3 else gate) * y)
+            if residual.dtype == torch.float16:
+                residual.clamp_(-65504, 65504)
+            return residual
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        t = self._down(x2) if lr else None
+        xq, sx = quant_rows(x2)
+        ops._gemm_impl(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B if lr else None, x2.dtype,
+                       lb_t=self._lr_Bt() if lr else None, epilogue=ops.EPI_ACCUMULATE, out=res2,
+                       gate=gate, gate_rows=x.shape[-2] if x.dim() == 3 else 0)
+        return residual
+
     def forward_into(self, x2: torch.Tensor, out: torch.Tensor, out_more: Sequence[torch.Tensor] = ()) -> torch.Tensor:
         """``out[:] = self(x2)`` for 2-D ``x2``, the same values also stored to every tensor of ``out_more`` (same shape,
         dtype and row stride as ``out``; up to ``ops.MAX_OUT_MORE``).  When the shapes allow it the GEMM epilogue

@@ -291,7 +291,8 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
                t: Optional[Tensor], lb: Optional[Tensor], out_dtype: torch.dtype,
                dbg_acc: Optional[Tensor] = None, w_lo: Optional[Tensor] = None, s_lo: Optional[Tensor] = None,
                m_hi: Optional[int] = None, lb_t: Optional[Tensor] = None, epilogue: int = 0,
-               out: Optional[Tensor] = None, out_more: Optional[Sequence[Tensor]] = None) -> Tensor:
+               out: Optional[Tensor] = None, out_more: Optional[Sequence[Tensor]] = None,
+               gate: Optional[Tensor] = None, gate_rows: int = 0) -> Tensor:
     assert xq.is_cuda and xq.dtype == torch.int8 and xq.dim() == 2 and xq.stride(1) == 1
     assert w_int8.dtype == torch.int8 and w_int8.dim() == 2 and w_int8.stride(1) == 1
     M, K = xq.shape
@@ -352,6 +353,26 @@ def _gemm_impl(xq: Tensor, s_row: Tensor, w_int8: Tensor, w_scale: Tensor, bias:
         _written_in_place(out)
         for o in out_more:
             _written_in_place(o)
+        return out
+    if gate is not None:
+        # out = out + gate[sample] * y (pq_int8_gemm_gated): gate [samples, N] in the output type; rows of sample b are
+        # [b * gate_rows, (b + 1) * gate_rows)
+        assert w_lo is None and dbg_acc is None and not out_more
+        gate = gate.reshape(-1, N)
+        assert gate.is_cuda and gate.dtype == out_dtype and gate.device == xq.device, (gate.dtype, out_dtype)
+        assert gate.shape[0] == 1 or (gate_rows > 0 and gate.shape[0] * gate_rows >= M), (gate.shape, gate_rows, M)
+        if gate.stride(1) != 1 or gate.stride(0) % 8 != 0 or gate.data_ptr() % 16 != 0:
+            gate = gate.contiguous()
+        assert epilogue_supported(N, ldo, out.data_ptr(), t is not None, R or 32), "shape needs the CTA-pair kernel"
+        with _on_device(xq):
+            rc = lib.pq_int8_gemm_gated(xq.data_ptr(), ldx, s_row.data_ptr(), w_int8.data_ptr(), w_int8.stride(0),
+                                        w_scale.data_ptr(), _ptr(bias), _ptr(t), ldt, _ptr(lb), ldb, _ptr(lb_t), R,
+                                        _dt(out_dtype), gate.data_ptr(), gate.stride(0) if gate.shape[0] > 1 else N,
+                                        int(gate_rows) if gate.shape[0] > 1 else 0, out.data_ptr(), _dt(out_dtype), ldo,
+                                        M, N, K, int(epilogue), ws.data_ptr(), ws.numel() * 4, _stream(xq))
+        if rc:
+            _lib.check(rc, f"pq_int8_gemm_gated(M={M}, N={N}, K={K})")
+        _written_in_place(out)
         return out
     with _on_device(xq):
         if epilogue:

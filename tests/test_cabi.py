@@ -110,6 +110,16 @@ def test_gemm_ex_argument_checks():
     assert ex(ldo=68) == 7                           # ldo % 8
     assert ex(out=p16 + 4) == 7                      # out not 16-byte aligned
     assert ex(K=40) == 3                             # the plain GEMM's checks still come first
+    assert ex(epi=4) == 1                            # the gate flag without a gate vector
+
+    def gated(gate=p16, ld_gate=64, rps=0, N=64, ldo=64):
+        return lib.pq_int8_gemm_gated(p16, 64, p16, p16, 64, p16, None, None, 0, None, 0, None, 0, 0, gate, ld_gate, rps,
+                                      p16, 0, ldo, 8, N, 64, 1, None, 0, None)
+    assert gated(gate=None) == 1
+    assert gated(ld_gate=60) == 3                    # gate row stride
+    assert gated(gate=p16 + 4) == 3                  # gate not 16-byte aligned
+    assert gated(rps=-1) == 3
+    assert gated(N=40, ldo=40, ld_gate=40) == 7      # shape outside the CTA-pair kernel's vector store path
 
 
 def test_gemm_bcast_argument_checks():

@@ -541,6 +541,35 @@ def test_forward_adaln(cuda_dev):
     assert torch.equal(y2, layer.forward_adaln(h[:1], scale[:1], shift[:1])[0])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("lowrank", [True, False])
+def test_gated_residual_epilogue(cuda_dev, dtype, lowrank):
+    """`residual + gate.unsqueeze(1) * Linear(x)` (flux/transformer_flux.py:145-149) in the GEMM epilogue: bit-identical to
+    the layer followed by torch's multiply and add, two samples with their own gate vectors, fp16 sums clipped as the
+    block clips them."""
+    g = torch.Generator().manual_seed(31)
+    B, T, K, N = 2, 333, 512, 768
+    layer = _toy_layer(cuda_dev, g, K, N, lowrank=lowrank, dtype=dtype)
+    x = (torch.randn(B, T, K, generator=g) * 1.5).to(dtype).to(cuda_dev)
+    gate = (torch.randn(B, N, generator=g) * 0.7).to(dtype).to(cuda_dev)
+    residual = (torch.randn(B, T, N, generator=g) * 3).to(dtype).to(cuda_dev)
+    if dtype == torch.float16:
+        residual[0, 0, :8] = 65000.0; residual[1, 5, :8] = -65000.0        # sums that leave the fp16 range
+        gate[:, :8] = gate[:, :8].abs() + 40.0
+    y = layer(x)
+    want = residual + gate.unsqueeze(1) * y
+    if dtype == torch.float16:
+        want = want.clip(-65504, 65504)
+    res = residual.clone()
+    out = layer.forward_gated_residual(x, gate, res)
+    assert out is res and torch.equal(res, want)
+    # 2-D input, one gate vector
+    res2 = residual[1].clone()
+    layer.forward_gated_residual(x[1], gate[1], res2)
+    assert torch.equal(res2, want[1])
+    ops.check_device_status(cuda_dev)
+
+
 def test_split_input_linear(cuda_dev):
     """y = L0(x[..., :in0]) + L1(x[..., in0:]) with the sum in the second GEMM's epilogue: identical to the two layers
     and a torch add (pyraquant/external_quant.py:191-192), 3-D input, strided halves."""
