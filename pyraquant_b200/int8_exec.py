@@ -224,6 +224,26 @@ class SharedInputGroup:
         _x, xq, sx, T = self._val
         return xq, sx, T
 
+    def prime_adaln(self, h: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+        """Returns ``z = LayerNorm(h) * (1 + scale[:, None]) + shift[:, None]`` (the block's adaLN output,
+        flux/transformer_flux.py:133, :206, :236-239) and leaves the group primed for it: normalisation, modulation and the
+        members' shared quantisation are one pass over ``h`` (``ops.adaln_quant_rows``), the shared down-projection
+        reads ``z``, and the members called on ``z`` afterwards go straight to their GEMMs.  h [B, T, K] with scale / shift
+        [B, K], or h [M, K] with [K]; CUDA tensors of the members' activation type."""
+        K = h.shape[-1]
+        x2 = h.reshape(-1, K)
+        xq, sx, z2 = ops.adaln_quant_rows(x2, scale, shift, eps, h.shape[-2] if h.dim() == 3 else 0, want_modulated=True)
+        a_cat = self._a_cat(z2.dtype, z2.device)
+        if a_cat is None:
+            T = None
+        elif a_cat.shape[1] in ops.LOWRANK_DOWN_COLS and ops.lowrank_down_ok(z2):
+            T = ops.lowrank_down(z2, self._A_cat_t)
+        else:
+            T = z2 @ a_cat
+        self._key = (z2.data_ptr(), tuple(z2.shape), tuple(z2.stride()), z2.dtype, z2._version, z2.device, ops._stream(z2))
+        self._val = (z2, xq, sx, T)
+        return z2.reshape(h.shape)
+
     def t_of(self, member: "Int8Linear", T: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         off = self._A_slots.get(id(member))
         if T is None or off is None:

@@ -541,6 +541,32 @@ def test_forward_adaln(cuda_dev):
     assert torch.equal(y2, layer.forward_adaln(h[:1], scale[:1], shift[:1])[0])
 
 
+def test_shared_group_primed_by_adaln(cuda_dev, monkeypatch):
+    """`SharedInputGroup.prime_adaln`: one pass produces the modulated activations and the members' shared codes; the
+    members called on the result skip their own quantisation and give what they give ungrouped on the same tensor."""
+    g = torch.Generator().manual_seed(41)
+    B, T, K = 2, 200, 512
+    layers = [_toy_layer(cuda_dev, g, K, n, lowrank=lr) for n, lr in ((768, True), (512, True), (256, False))]
+    h = (torch.randn(B, T, K, generator=g) * 1.5).to(torch.bfloat16).to(cuda_dev)
+    scale = (torch.randn(B, K, generator=g) * 0.3).to(torch.bfloat16).to(cuda_dev)
+    shift = (torch.randn(B, K, generator=g) * 0.2).to(torch.bfloat16).to(cuda_dev)
+    z_alone = ops.adaln_quant_rows(h.reshape(-1, K), scale, shift, 1e-6, T)[2].reshape(h.shape)
+    want = [m(z_alone) for m in layers]
+    grp = int8_exec.share_input_quantisation(layers)
+    z = grp.prime_adaln(h, scale, shift)
+    assert torch.equal(z, z_alone)
+    calls = []
+    real = ops._quant_rows_impl
+    monkeypatch.setattr(ops, "_quant_rows_impl", lambda x2: (calls.append(1), real(x2))[1])
+    got = [m(z) for m in layers]
+    assert not calls, "members quantised again although the group was primed"
+    for a, b, m in zip(got, want, layers):
+        if m.lr_A is None:
+            assert torch.equal(a, b)
+        else:                                            # the shared down-projection is 64 columns wide: other fp32 summation order
+            assert ((a.float() - b.float()).norm() / b.float().norm()).item() < 2e-3
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("lowrank", [True, False])
 def test_gated_residual_epilogue(cuda_dev, dtype, lowrank):
