@@ -59,6 +59,8 @@ int pq_last_cuda_error(void);
  *   "gemm_pair"         0 = never use the CTA-pair kernel, 1 = automatic (default), 2 = whenever it is legal;
  *   "gemm_debug_timing" 1 = the CTA-pair kernel runs in its debug instantiation (the production kernel contains no
  *                       counters) and writes per-role cycle counters to workspace + 256 (needs ws_bytes >= 256 + 4096*64).
+ *   "gemm_tail_pairs"   1 (default) = SM pairs that the rectangular pair grid leaves over take a tail region of the tile
+ *                       matrix (the last row tiles of the last column round), 0 = they stay idle;
  *   "gemm_panel_mb"     CTA-pair kernel with several column rounds: megabytes of activation rows per row panel of the tile
  *                       schedule (the rows of a panel stay in L2 across the rounds); 0 = one panel over all rows;
  *   "gemm_l2_hints"     CTA-pair kernel, L2 eviction priorities: bit 0 weights evict-last, bit 1 activations evict-first,

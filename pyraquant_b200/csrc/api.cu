@@ -62,6 +62,7 @@ int* option_slot(const char* key) {
   if (std::strcmp(key, "gemm_epi_warps") == 0) return &o.gemm_epi_warps;
   if (std::strcmp(key, "gemm_tma_store") == 0) return &o.gemm_tma_store;
   if (std::strcmp(key, "gemm_debug_timing") == 0) return &o.gemm_debug_timing;
+  if (std::strcmp(key, "gemm_tail_pairs") == 0) return &o.gemm_tail_pairs;
   if (std::strcmp(key, "gemm_panel_mb") == 0) return &o.gemm_panel_mb;
   if (std::strcmp(key, "gemm_l2_hints") == 0) return &o.gemm_l2_hints;
   if (std::strcmp(key, "g32_variant") == 0) return &o.g32_variant;

@@ -45,6 +45,7 @@ struct Options {
   int gemm_epi_warps = 0;  // epilogue warps of the CTA-pair kernel: 0 automatic (16 up to K = 1536 without low-rank term, else 8), 8 or 16
   int gemm_tma_store = 1;  // sixteen-warp pair tiles store through shared memory + TMA (0: register stores)
   int gemm_pair = 1;       // CTA-pair (cta_group::2) kernel: 0 off, 1 when the problem is large enough, 2 whenever it applies
+  int gemm_tail_pairs = 1; // CTA-pair kernel: SM pairs that the pm x pn grid leaves over take a tail region of the tiles (0: they idle)
   int gemm_panel_mb = 0;   // CTA-pair kernel, several column rounds: megabytes of activation rows per row panel (0 = one panel)
   int gemm_l2_hints = 0;   // CTA-pair kernel: bit 0 weights evict-last, bit 1 activations evict-first, bit 2 activations evict-last, bit 3 streaming output stores
   int g32_variant = 0;     // group-32 GEMM: bit 0 eight epilogue warps, bit 1 scalar fp32 operations, bit 3 data path only

@@ -164,23 +164,49 @@ __device__ __noinline__ void dump_acc_pair(int32_t* dbg, int N, int rA, int rB, 
   if (rB < row_end && col + 1 < N) dbg[static_cast<int64_t>(rB) * N + col + 1] = static_cast<int32_t>(v3);
 }
 
-// Walker over pair tiles: the pairs (not the CTAs) form the pm x pn grid.  Order of the tiles a pair visits: the row
-// steps are cut into panels of `panel` steps; inside a panel the pair runs down its column (all row steps of the panel)
-// before it moves pn column tiles to the right, and only after the last column round does it enter the next panel.
-// A panel that covers all row steps is the plain column-round-major order.  With several column rounds a short panel
-// keeps the panel's activation rows in L2 across the rounds instead of streaming all M rows once per round.
+// Walker over pair tiles.  The first pm x pn pairs form a grid laid over (row tile, column tile).  Order of the tiles a
+// grid pair visits: the row steps are cut into panels of `panel` steps; inside a panel the pair runs down its column
+// (all row steps of the panel) before it moves pn column tiles to the right, and only after the last column round does
+// it enter the next panel.  A panel that covers all row steps is the plain column-round-major order.  With several
+// column rounds a short panel keeps the panel's activation rows in L2 across the rounds instead of streaming all M rows
+// once per round.
+// Pairs beyond the grid (the SM pairs a pm x pn rectangle leaves over: 2 of 74 with the 6 x 12 grid of the FLUX layers)
+// take a tail region off the grid's hands: the row tiles from `cut` on in the last column round, walked column by column,
+// a contiguous share of `tail_per` tiles each; the grid pairs stop at `cut` in that round.  The host picks `cut` so that
+// grid pairs and tail pairs finish together.
 struct PairWalker {
   int mt, ntile, bn, pm, pn, mt_total, nt, panel0, panel_span;
-  __device__ __forceinline__ void init(int pair, int pm_, int pn_, int mt_total_, int nt_, int panel_steps) {
-    pm = pm_; pn = pn_; mt_total = mt_total_; nt = nt_;
-    const int bm = pair / pn; bn = pair - bm * pn;
-    panel_span = (panel_steps > 0 && panel_steps < (1 << 20)) ? panel_steps * pm : (1 << 30);
-    panel0 = bm; mt = bm; ntile = bn;
+  int col0, cut;       // first column tile of the last column round; row limit of the grid pairs there
+  int tail_left;       // tiles left for a tail pair; -1 for a grid pair
+  __device__ __forceinline__ void init(int pair, const GemmParams& p, int mt_total_, int nt_) {
+    pm = p.sched_pm; pn = p.sched_pn; mt_total = mt_total_; nt = nt_;
+    col0 = ((nt + pn - 1) / pn - 1) * pn;
+    cut = p.sched_tail_per > 0 ? p.sched_cut : mt_total;
+    panel_span = (p.sched_panel > 0 && p.sched_panel < (1 << 20)) ? p.sched_panel * pm : (1 << 30);
+    if (pair < pm * pn) {
+      const int bm = pair / pn; bn = pair - bm * pn;
+      panel0 = bm; mt = bm; ntile = bn; tail_left = -1;
+    } else {
+      const int nrows = mt_total - cut;
+      const int total = nrows * (nt - col0);
+      const int j = (pair - pm * pn) * p.sched_tail_per;
+      const int j_end = j + p.sched_tail_per < total ? j + p.sched_tail_per : total;
+      tail_left = j_end > j ? j_end - j : 0;
+      bn = 0; panel0 = 0;
+      if (tail_left > 0) { ntile = col0 + j / nrows; mt = cut + j % nrows; }
+      else { ntile = nt; mt = mt_total; }
+    }
   }
-  __device__ __forceinline__ bool valid() const { return ntile < nt && mt < mt_total; }
+  __device__ __forceinline__ int row_limit() const { return ntile >= col0 ? cut : mt_total; }
+  __device__ __forceinline__ bool valid() const { return tail_left >= 0 ? tail_left > 0 : (ntile < nt && mt < row_limit()); }
   __device__ __forceinline__ void advance() {
+    if (tail_left >= 0) {
+      --tail_left;
+      if (++mt >= mt_total) { mt = cut; ++ntile; }
+      return;
+    }
     mt += pm;
-    if (mt >= mt_total || mt - panel0 >= panel_span) {
+    if (mt >= row_limit() || mt - panel0 >= panel_span) {
       ntile += pn; mt = panel0;
       if (ntile >= nt && panel_span < (1 << 30) && panel0 + panel_span < mt_total) { ntile = bn; panel0 += panel_span; mt = panel0; }
     }
@@ -276,7 +302,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       // activations evict-last)
       const uint64_t pol_w = l2_policy_evict_last();
       const uint64_t pol_a = (p.l2_hints & 4) ? l2_policy_evict_last() : l2_policy_evict_first();
-      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt, p.sched_panel);
+      PairWalker w; w.init(pair, p, mt_total, nt);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance(), ++it) {
         const PairCoord c = pair_coord(w.mt, mt0, p, rank);
@@ -348,7 +374,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       int stage = 0; uint32_t phase = 0; int it = 0; bool ok = true;
       long long tm_tempty = 0, tm_full = 0;
       auto commit_both = [&](uint64_t* bar) { tc_commit_pair(smem_u32(bar)); tc_commit_pair(peer_addr(bar)); };
-      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt, p.sched_panel);
+      PairWalker w; w.init(pair, p, mt_total, nt);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance(), ++it) {
         const int buf = it & 1;
@@ -393,7 +419,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       int it = 0, lb_col = -1; uint32_t lb_count = 0; bool ok = true;
       long long tm_det[2] = {0, 0};
       auto commit_both = [&](uint64_t* bar) { tc_commit_pair(smem_u32(bar)); tc_commit_pair(peer_addr(bar)); };
-      PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt, p.sched_panel);
+      PairWalker w; w.init(pair, p, mt_total, nt);
 #pragma unroll 1
       for (; w.valid() && ok; w.advance(), ++it) {
         const int pb = it & 1;
@@ -452,7 +478,7 @@ pq_int8_gemm_fused_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         dst[mb][1] = rA + 8 < pc.row_end ? p.s_row[rA + 8] : 0.0f;
       }
     };
-    PairWalker w; w.init(pair, p.sched_pm, p.sched_pn, mt_total, nt, p.sched_panel);
+    PairWalker w; w.init(pair, p, mt_total, nt);
 #pragma unroll 1
     for (; w.valid(); w.advance(), ++it) {
       const PairCoord c = pair_coord(w.mt, mt0, p, rank);
@@ -816,7 +842,25 @@ int launch_pair_ew(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtenso
     if (steps < (mt_pairs + p.sched_pm - 1) / p.sched_pm) p.sched_panel = steps;
   }
   p.l2_hints = options().gemm_l2_hints;
-  cfg.gridDim = dim3(2 * p.sched_pm * p.sched_pn, 1, 1);
+  // Tail pairs.  The pm x pn grid leaves pairs_cap - pm * pn SM pairs idle; they take the row tiles from `cut` on of the
+  // last column round, and `cut` (a multiple of pm) is chosen for the fewest steps of the slower of the two groups.
+  p.sched_cut = mt_pairs; p.sched_tail_per = 0;
+  int extra = pairs_cap - p.sched_pm * p.sched_pn;
+  if (extra > 0 && p.sched_panel == 0 && options().gemm_tail_pairs != 0) {
+    const int row_steps = (mt_pairs + p.sched_pm - 1) / p.sched_pm;
+    const int col0 = (rounds - 1) * p.sched_pn, wl = ntl - col0;
+    long long best = static_cast<long long>(row_steps) * rounds;
+    for (int k = 0; k < row_steps; ++k) {               // the grid keeps k row steps of the last round
+      const int cut = k * p.sched_pm;
+      const long long tail = static_cast<long long>(mt_pairs - cut) * wl;
+      const long long per = (tail + extra - 1) / extra;
+      const long long grid_steps = static_cast<long long>(row_steps) * (rounds - 1) + k;
+      const long long steps = grid_steps > per ? grid_steps : per;
+      if (steps < best && per <= 0x7fffffffLL) { best = steps; p.sched_cut = cut; p.sched_tail_per = static_cast<int>(per); }
+    }
+  }
+  if (p.sched_tail_per == 0) extra = 0;
+  cfg.gridDim = dim3(2 * (p.sched_pm * p.sched_pn + extra), 1, 1);
   PQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmW1, tmT, tmLbT, tmOut, p));
   return PQ_OK;
 }
