@@ -842,6 +842,45 @@ def main_other(args) -> None:
                                  "gemm_g32_us": r["forward"] - r["quant"],
                                  "gemm_g32_tops": opsn / max(r["forward"] - r["quant"], 1e-3) / 1e6})
             del m, x, lin, xc
+    elif args.workload == "block4k":
+        # The Linear path of one FLUX single-stream block at the 4K stage (flux/transformer_flux.py:126-150), attention
+        # left out (its output is stood in for by the query projection): the reference's call sequence on this
+        # library's drop-in layers against the same block with the block-level fusions (adaLN prologue shared by the four
+        # sibling projections, GELU in the epilogue, gate and residual in the epilogue).
+        M, D, H4 = 65536 + 512, 3072, 12288
+        F = torch.nn.functional
+        proj_mlp, to_q, to_k, to_v = layer(D, H4, torch.bfloat16), layer(D, D, torch.bfloat16), layer(D, D, torch.bfloat16), layer(D, D, torch.bfloat16)
+        proj_out = layer(D + H4, D, torch.bfloat16)
+        h = act(M, D, torch.bfloat16)
+        shift, scale, gate = [(torch.randn(1, D, generator=g, device=dev) * 0.3).to(torch.bfloat16) for _ in range(3)]
+
+        def unfused(_i):
+            z = F.layer_norm(h, (D,), eps=1e-6) * (1 + scale) + shift
+            mlp = F.gelu(proj_mlp(z), approximate="tanh")
+            q_, k_, v_ = to_q(z), to_k(z), to_v(z)
+            cat = torch.cat([q_, mlp], dim=-1)
+            return h + gate * proj_out(cat), k_, v_
+        grp = int8_exec.share_input_quantisation([proj_mlp, to_q, to_k, to_v])
+        res = [h.clone() for _ in range(2)]        # the residual stream is updated in place (the block's input is dead after it)
+
+        def fused(i):
+            z = grp.prime_adaln(h, scale[0], shift[0])
+            mlp = proj_mlp.forward_ex(z, ops.EPI_GELU_TANH)
+            q_, k_, v_ = to_q(z), to_k(z), to_v(z)
+            cat = torch.cat([q_, mlp], dim=-1)
+            return proj_out.forward_gated_residual(cat, gate[0], res[i % 2]), k_, v_
+        a, b = unfused(0), fused(0)
+        torch.cuda.synchronize()
+        rel = ((a[0].float() - b[0].float()).norm() / a[0].float().norm()).item()
+        del a, b
+        res[0].copy_(h)
+        r = interleaved([("unfused", unfused), ("fused", fused)], reps)
+        opsn = 2.0 * M * (D * H4 + 3 * D * D + (D + H4) * D)
+        out["items"] = [{"item": "single-stream block, Linear path, reference call sequence on the drop-in layers", "us": r["unfused"],
+                         "tops": opsn / r["unfused"] / 1e6},
+                        {"item": "same block with the block-level fusions", "us": r["fused"], "tops": opsn / r["fused"] / 1e6,
+                         "rel_l2_vs_unfused": rel}]
+        out.update({"rows": M, "dim": D, "mlp_dim": H4})
     else:
         H = W = 256
         C, F = 3072, 12288
@@ -913,7 +952,7 @@ if __name__ == "__main__":
     ap.add_argument("--no-ceiling", action="store_true", help="skip the tensor-pipe issue-loop ceiling measurement")
     ap.add_argument("--no-gpu-baseline", action="store_true", help="skip the reference's own GPU forward (baseline/_ref)")
     ap.add_argument("--shape", default=None, help="MxKxN: only this layer of the sdxl_pc / sdxl_g32 workloads")
-    ap.add_argument("--workload", choices=("flux4k", "flux2k", "sdxl_pc", "sdxl_g32", "routed4k"), default="flux4k",
+    ap.add_argument("--workload", choices=("flux4k", "flux2k", "sdxl_pc", "sdxl_g32", "routed4k", "block4k"), default="flux4k",
                     help="flux4k (default) is the benchmark contract; the others print one JSON line of per-item "
                          "measurements for the remaining configurations of the path (one GPU)")
     args = ap.parse_args()
