@@ -846,7 +846,8 @@ def main_other(args) -> None:
         # The Linear path of one FLUX single-stream block at the 4K stage (flux/transformer_flux.py:126-150), attention
         # left out (its output is stood in for by the query projection): the reference's call sequence on this
         # library's drop-in layers against the same block with the block-level fusions (adaLN prologue shared by the four
-        # sibling projections, GELU in the epilogue, gate and residual in the epilogue).
+        # sibling projections, GELU in the epilogue, proj_out reading its two sources in place, gate and residual in the
+        # epilogue).
         M, D, H4 = 65536 + 512, 3072, 12288
         F = torch.nn.functional
         proj_mlp, to_q, to_k, to_v = layer(D, H4, torch.bfloat16), layer(D, D, torch.bfloat16), layer(D, D, torch.bfloat16), layer(D, D, torch.bfloat16)
@@ -867,8 +868,7 @@ def main_other(args) -> None:
             z = grp.prime_adaln(h, scale[0], shift[0])
             mlp = proj_mlp.forward_ex(z, ops.EPI_GELU_TANH)
             q_, k_, v_ = to_q(z), to_k(z), to_v(z)
-            cat = torch.cat([q_, mlp], dim=-1)
-            return proj_out.forward_gated_residual(cat, gate[0], res[i % 2]), k_, v_
+            return proj_out.forward_gated_residual(q_, gate[0], res[i % 2], x_more=mlp), k_, v_     # no concatenated tensor
         a, b = unfused(0), fused(0)
         torch.cuda.synchronize()
         rel = ((a[0].float() - b[0].float()).norm() / a[0].float().norm()).item()

@@ -236,6 +236,18 @@ int pq_int8_gemm_g32(const int8_t* xq, int64_t ldx, const float* s_a,
 int pq_lowrank_down(const void* x, int dtype, int64_t ldx, const void* a_t, int64_t lda, int R, void* t, int64_t ldt,
                     int64_t M, int64_t K, void* workspace, size_t ws_bytes, void* stream);
 
+/* pq_quant_rows and pq_lowrank_down on an input that is the concatenation of two tensors along K,
+ *   x[m, :] = [x0[m, 0:K0] | x1[m, 0:K1]],
+ * without materialising it: `proj_out(torch.cat([attn_output, mlp_hidden_states], dim=2))` of the single-stream FLUX
+ * blocks (flux/transformer_flux.py:143-145) reads its two sources in place.  Results are those of the plain entry points on
+ * the concatenated tensor, bit for bit.  K0 % 8 == 0, K1 % 8 == 0, K0 + K1 <= 16384 for the quantisation; K0 % 64 == 0
+ * for the down-projection; row strides % 8 == 0; 16-byte aligned bases.  No counterpart in the reference. */
+int pq_quant_rows_cat(const void* x0, int64_t K0, int64_t ldx0, const void* x1, int64_t K1, int64_t ldx1,
+                      int dtype, int64_t M, int8_t* q, float* s, void* stream);
+int pq_lowrank_down_cat(const void* x0, int64_t K0, int64_t ldx0, const void* x1, int64_t K1, int64_t ldx1,
+                        int dtype, const void* a_t, int64_t lda, int R, void* t, int64_t ldt, int64_t M,
+                        void* workspace, size_t ws_bytes, void* stream);
+
 /* Low-tier weights at rest in 4 bits: expands packed nested-4-bit codes (pyraquant/quantizers_weight.py:182-199;
  * the reference keeps this tier for storage/BOPs accounting only, deploy/run_flux_latency.py:16-18) to the int8
  * operand the GEMMs read.  Byte b of row n holds element 2b in its low nibble and element 2b+1 in its high nibble,

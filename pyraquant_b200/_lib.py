@@ -28,6 +28,10 @@ SIGNATURES = {
     "pq_set_option": (c_int, [c_char_p, c_int]),
     "pq_get_option": (c_int, [c_char_p, POINTER(c_int)]),
     "pq_quant_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "pq_quant_rows_cat": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int64, c_void_p, c_void_p,
+                                  c_void_p]),
+    "pq_lowrank_down_cat": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_void_p, c_int64, c_int,
+                                    c_void_p, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
     "pq_adaln_quant_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                     ctypes.c_float, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "pq_gather_quant_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p,

@@ -47,8 +47,9 @@ __host__ __device__ constexpr uint32_t idesc_f16_f32acc(int M, int N, bool bf16)
 
 template <typename T, int NC>
 __global__ void __launch_bounds__(kLowThreads, 1)
-pq_lowrank_down_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmA, T* __restrict__ t,
-                       int64_t ldt, int M, int K, int32_t* status) {
+pq_lowrank_down_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmX1,
+                       const __grid_constant__ CUtensorMap tmA, T* __restrict__ t,
+                       int64_t ldt, int M, int K, int k0, int32_t* status) {
   using L = LowSmem<NC>;
   constexpr int LSTAGES = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -67,7 +68,7 @@ pq_lowrank_down_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
   constexpr uint32_t kTmemCols = L::kTmemCols;       // two accumulators of NC columns
 
   if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tmX); tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmX); tma_prefetch_desc(&tmX1); tma_prefetch_desc(&tmA);
     for (int s = 0; s < LSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
     *abort_flag = 0;
@@ -96,7 +97,10 @@ pq_lowrank_down_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
           mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
 #pragma unroll
           for (int b = 0; b < LBOX; ++b) {             // boxes past the end of K are zero-filled by TMA
-            tma_load_2d(xs + b * (L::kXBytes + L::kABytes), &tmX, &full_bar[stage], (kb * LBOX + b) * LKE, row0);
+            // x may be the concatenation of two tensors along K: columns from k0 on come from the second one
+            const int col = (kb * LBOX + b) * LKE;
+            if (col < k0) tma_load_2d(xs + b * (L::kXBytes + L::kABytes), &tmX, &full_bar[stage], col, row0);
+            else tma_load_2d(xs + b * (L::kXBytes + L::kABytes), &tmX1, &full_bar[stage], col - k0, row0);
             tma_load_2d(xs + b * (L::kXBytes + L::kABytes) + L::kXBytes, &tmA, &full_bar[stage], (kb * LBOX + b) * LKE, 0);
           }
           ++issued;
@@ -213,8 +217,8 @@ int make_map16(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int6
 }
 
 template <typename T, int NC>
-int launch_low(const CUtensorMap& tmX, const CUtensorMap& tmA, void* t, int64_t ldt, int64_t M, int64_t K, int32_t* status,
-               cudaStream_t st) {
+int launch_low(const CUtensorMap& tmX, const CUtensorMap& tmX1, int k0, const CUtensorMap& tmA, void* t, int64_t ldt, int64_t M,
+               int64_t K, int32_t* status, cudaStream_t st) {
   auto kern = pq_lowrank_down_kernel<T, NC>;
   using LS = LowSmem<NC>;
   static bool attr_set[64] = {false};
@@ -228,20 +232,20 @@ int launch_low(const CUtensorMap& tmX, const CUtensorMap& tmA, void* t, int64_t 
   const int64_t tiles = (M + LM - 1) / LM;
   int64_t grid = sm_count();
   if (grid > tiles) grid = tiles;
-  kern<<<static_cast<unsigned>(grid), kLowThreads, LS::kDynamic, st>>>(tmX, tmA, static_cast<T*>(t), ldt,
-                                                                           static_cast<int>(M), static_cast<int>(K), status);
+  kern<<<static_cast<unsigned>(grid), kLowThreads, LS::kDynamic, st>>>(tmX, tmX1, tmA, static_cast<T*>(t), ldt,
+                                                                           static_cast<int>(M), static_cast<int>(K), k0, status);
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
 }
 
 template <typename T>
-int launch_low_cols(int R, const CUtensorMap& tmX, const CUtensorMap& tmA, void* t, int64_t ldt, int64_t M, int64_t K,
-                    int32_t* status, cudaStream_t st) {
+int launch_low_cols(int R, const CUtensorMap& tmX, const CUtensorMap& tmX1, int k0, const CUtensorMap& tmA, void* t, int64_t ldt,
+                    int64_t M, int64_t K, int32_t* status, cudaStream_t st) {
   switch (R) {
-    case 32: return launch_low<T, 32>(tmX, tmA, t, ldt, M, K, status, st);
-    case 64: return launch_low<T, 64>(tmX, tmA, t, ldt, M, K, status, st);
-    case 96: return launch_low<T, 96>(tmX, tmA, t, ldt, M, K, status, st);
-    case 128: return launch_low<T, 128>(tmX, tmA, t, ldt, M, K, status, st);
+    case 32: return launch_low<T, 32>(tmX, tmX1, k0, tmA, t, ldt, M, K, status, st);
+    case 64: return launch_low<T, 64>(tmX, tmX1, k0, tmA, t, ldt, M, K, status, st);
+    case 96: return launch_low<T, 96>(tmX, tmX1, k0, tmA, t, ldt, M, K, status, st);
+    case 128: return launch_low<T, 128>(tmX, tmX1, k0, tmA, t, ldt, M, K, status, st);
     default: return PQ_ERR_UNSUPPORTED;
   }
 }
@@ -251,25 +255,51 @@ int launch_low_cols(int R, const CUtensorMap& tmX, const CUtensorMap& tmA, void*
 
 using namespace pq;
 
-extern "C" int pq_lowrank_down(const void* x, int dtype, int64_t ldx, const void* a_t, int64_t lda, int R, void* t,
-                               int64_t ldt, int64_t M, int64_t K, void* workspace, size_t ws_bytes, void* stream) {
-  if (M < 0 || K <= 0 || M > 0x7fffff00LL || K > 0x7fffff00LL || ldx < K || lda < K || R <= 0 || ldt < R) return PQ_ERR_SHAPE;
+namespace {
+int lowrank_down_impl(const void* x, int64_t K0, int64_t ldx, const void* x1, int64_t K1, int64_t ldx1, int dtype,
+                      const void* a_t, int64_t lda, int R, void* t, int64_t ldt, int64_t M, void* workspace, size_t ws_bytes,
+                      void* stream) {
+  const int64_t K = K0 + K1;
+  if (M < 0 || K0 <= 0 || K1 < 0 || M > 0x7fffff00LL || K > 0x7fffff00LL || ldx < K0 || lda < K || R <= 0 || ldt < R) return PQ_ERR_SHAPE;
+  if (x1 != nullptr && ldx1 < K1) return PQ_ERR_SHAPE;
   if (R % 32 != 0 || R > kLowMaxCols) return PQ_ERR_UNSUPPORTED;
   if (dtype != PQ_DTYPE_BF16 && dtype != PQ_DTYPE_FP16) return PQ_ERR_DTYPE;
   if (M == 0) return PQ_OK;
-  if (x == nullptr || a_t == nullptr || t == nullptr) return PQ_ERR_NULL;
-  if (K % 8 != 0 || ldx % 8 != 0 || lda % 8 != 0 || ldt % 8 != 0 || !aligned_to(x, 16) || !aligned_to(a_t, 16) ||
+  if (x == nullptr || a_t == nullptr || t == nullptr || (K1 > 0 && x1 == nullptr)) return PQ_ERR_NULL;
+  if (K0 % 8 != 0 || ldx % 8 != 0 || lda % 8 != 0 || ldt % 8 != 0 || !aligned_to(x, 16) || !aligned_to(a_t, 16) ||
       !aligned_to(t, 16))
     return PQ_ERR_ALIGN;
+  if (K1 > 0 && (K1 % 8 != 0 || ldx1 % 8 != 0 || !aligned_to(x1, 16))) return PQ_ERR_ALIGN;
+  if (K1 > 0 && K0 % LKE != 0) return PQ_ERR_UNSUPPORTED;       // the seam has to fall between two 64-element boxes
   if (workspace != nullptr && ws_bytes < PQ_GEMM_WORKSPACE_BYTES) return PQ_ERR_WORKSPACE;
   const bool bf16 = dtype == PQ_DTYPE_BF16;
-  CUtensorMap tmX, tmA;
-  int rc = make_map16(&tmX, x, M, K, ldx, LM, bf16);
+  CUtensorMap tmX, tmX1, tmA;
+  int rc = make_map16(&tmX, x, M, K0, ldx, LM, bf16);
   if (rc != PQ_OK) return rc;
+  if (K1 > 0) {
+    rc = make_map16(&tmX1, x1, M, K1, ldx1, LM, bf16);
+    if (rc != PQ_OK) return rc;
+  } else {
+    tmX1 = tmX;
+  }
   rc = make_map16(&tmA, a_t, R, K, lda, R, bf16);
   if (rc != PQ_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int32_t* status = static_cast<int32_t*>(workspace);
-  if (bf16) return launch_low_cols<__nv_bfloat16>(R, tmX, tmA, t, ldt, M, K, status, st);
-  return launch_low_cols<__half>(R, tmX, tmA, t, ldt, M, K, status, st);
+  const int k0 = static_cast<int>(K1 > 0 ? K0 : K + LKE * LBOX);        // one source: every box comes from it
+  if (bf16) return launch_low_cols<__nv_bfloat16>(R, tmX, tmX1, k0, tmA, t, ldt, M, K, status, st);
+  return launch_low_cols<__half>(R, tmX, tmX1, k0, tmA, t, ldt, M, K, status, st);
+}
+}  // namespace
+
+extern "C" int pq_lowrank_down(const void* x, int dtype, int64_t ldx, const void* a_t, int64_t lda, int R, void* t,
+                               int64_t ldt, int64_t M, int64_t K, void* workspace, size_t ws_bytes, void* stream) {
+  return lowrank_down_impl(x, K, ldx, nullptr, 0, 0, dtype, a_t, lda, R, t, ldt, M, workspace, ws_bytes, stream);
+}
+
+extern "C" int pq_lowrank_down_cat(const void* x0, int64_t K0, int64_t ldx0, const void* x1, int64_t K1, int64_t ldx1,
+                                   int dtype, const void* a_t, int64_t lda, int R, void* t, int64_t ldt, int64_t M,
+                                   void* workspace, size_t ws_bytes, void* stream) {
+  if (x1 == nullptr || K1 <= 0) return x1 == nullptr ? PQ_ERR_NULL : PQ_ERR_SHAPE;
+  return lowrank_down_impl(x0, K0, ldx0, x1, K1, ldx1, dtype, a_t, lda, R, t, ldt, M, workspace, ws_bytes, stream);
 }

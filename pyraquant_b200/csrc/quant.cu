@@ -21,7 +21,8 @@ constexpr int kThreads = 256;
 template <typename T, int TPR, int CPT, bool GATHER, bool GROUP32>
 __global__ void __launch_bounds__(kThreads)
 pq_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, const int32_t* __restrict__ row_idx, int64_t src_rows,
-                     int8_t* __restrict__ q, float* __restrict__ s, int64_t M, int K) {
+                     int8_t* __restrict__ q, float* __restrict__ s, int64_t M, int K,
+                     const T* __restrict__ x1, int64_t ldx1, int nchunk0) {
   constexpr int RPB = kThreads / TPR;                  // rows per block
   constexpr int WPR = (TPR + 31) / 32;                 // warps per row
   __shared__ float s_part[kThreads / 32];
@@ -36,12 +37,15 @@ pq_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, const int32_t* __rest
   if (GATHER && row_ok) src = row_idx[row];
   const bool have_src = row_ok && src >= 0 && (!GATHER || src < src_rows);   // out-of-range indices read nothing
   const uint4* xrow = reinterpret_cast<const uint4*>(x + (have_src ? src : 0) * ldx);
+  // second source: the row continues in another tensor from chunk nchunk0 on (the row is the concatenation of the
+  // two along K; nchunk0 == nchunk when there is no second source)
+  const uint4* xrow1 = x1 != nullptr ? reinterpret_cast<const uint4*>(x1 + (have_src ? src : 0) * ldx1) - nchunk0 : xrow;
 
   uint4 v[CPT];
 #pragma unroll
   for (int j = 0; j < CPT; ++j) {
     const int c = lane_in_row + j * TPR;
-    if (have_src && c < nchunk) v[j] = ld_stream_v4(xrow + c);
+    if (have_src && c < nchunk) v[j] = ld_stream_v4((c < nchunk0 ? xrow : xrow1) + c);
     else v[j] = make_uint4(0u, 0u, 0u, 0u);
   }
 
@@ -174,58 +178,64 @@ pq_dequant_epilogue_kernel(const int32_t* __restrict__ acc, const float* __restr
   }
 }
 
+// Second source of a row that is the concatenation of two tensors along K (x1 == nullptr: none).
+struct SecondSrc { const void* x1 = nullptr; int64_t ldx1 = 0; int k0 = 0; };
+
 template <typename T, bool GATHER, bool GROUP32, int TPR, int CPT>
 int launch_one(const void* x, int64_t ldx, const int32_t* row_idx, int64_t src_rows, int8_t* q, float* s, int64_t M,
-               int K, cudaStream_t st) {
+               int K, cudaStream_t st, const SecondSrc& s2 = SecondSrc()) {
   constexpr int RPB = kThreads / TPR;
   const int64_t blocks = (M + RPB - 1) / RPB;
   if (blocks > 0x7fffffffLL) return PQ_ERR_SHAPE;
   pq_quant_rows_kernel<T, TPR, CPT, GATHER, GROUP32>
-      <<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(static_cast<const T*>(x), ldx, row_idx, src_rows, q, s, M, K);
+      <<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(static_cast<const T*>(x), ldx, row_idx, src_rows, q, s, M, K,
+                                                           static_cast<const T*>(s2.x1), s2.ldx1,
+                                                           s2.x1 != nullptr ? (s2.k0 >> 3) : (K >> 3));
   PQ_CUDA_TRY(cudaGetLastError());
   return PQ_OK;
 }
 
 template <typename T, bool GATHER, bool GROUP32>
 int dispatch(const void* x, int64_t ldx, const int32_t* row_idx, int64_t src_rows, int8_t* q, float* s, int64_t M,
-             int K, cudaStream_t st) {
+             int K, cudaStream_t st, const SecondSrc& s2 = SecondSrc()) {
   const int nchunk = K >> 3;
   // team size (threads per row) and chunks per thread: the row must fit the team's registers
   const int force = options().quant_tpr;
-  if (force == 16 && nchunk <= 16 * 5) return launch_one<T, GATHER, GROUP32, 16, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (force == 16 && nchunk <= 16 * 10) return launch_one<T, GATHER, GROUP32, 16, 10>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (force == 32 && nchunk <= 32 * 8) return launch_one<T, GATHER, GROUP32, 32, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (force == 32 && nchunk <= 32 * 12) return launch_one<T, GATHER, GROUP32, 32, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (force == 64 && nchunk <= 64 * 8) return launch_one<T, GATHER, GROUP32, 64, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (force == 64 && nchunk <= 64 * 12) return launch_one<T, GATHER, GROUP32, 64, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (force == 128 && nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (force == 256 && nchunk <= 256 * 8) return launch_one<T, GATHER, GROUP32, 256, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (force == 16 && nchunk <= 16 * 5) return launch_one<T, GATHER, GROUP32, 16, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (force == 16 && nchunk <= 16 * 10) return launch_one<T, GATHER, GROUP32, 16, 10>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (force == 32 && nchunk <= 32 * 8) return launch_one<T, GATHER, GROUP32, 32, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (force == 32 && nchunk <= 32 * 12) return launch_one<T, GATHER, GROUP32, 32, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (force == 64 && nchunk <= 64 * 8) return launch_one<T, GATHER, GROUP32, 64, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (force == 64 && nchunk <= 64 * 12) return launch_one<T, GATHER, GROUP32, 64, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (force == 128 && nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (force == 256 && nchunk <= 256 * 8) return launch_one<T, GATHER, GROUP32, 256, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
   // short rows: half a warp per row, so that a warp amortises its per-row work over two rows (measured: K = 640
   // 28 -> 21 us at 65536 rows; K = 1280 48 -> 44 us without group scales, no gain with them)
-  if (nchunk <= 16 * 5) return launch_one<T, GATHER, GROUP32, 16, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (nchunk <= 16 * 5) return launch_one<T, GATHER, GROUP32, 16, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
   if constexpr (!GROUP32) {
-    if (nchunk <= 16 * 10) return launch_one<T, GATHER, GROUP32, 16, 10>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+    if (nchunk <= 16 * 10) return launch_one<T, GATHER, GROUP32, 16, 10>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
   }
-  if (nchunk <= 32 * 4) return launch_one<T, GATHER, GROUP32, 32, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (nchunk <= 32 * 4) return launch_one<T, GATHER, GROUP32, 32, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
   if constexpr (!GROUP32) {
     // per-row scales: a single warp per row up to 3072 elements (no shared-memory hop, the per-row work is spread over
     // up to 96 elements per thread: a quarter fewer instructions than four warps per row), measured best per rung
-    if (nchunk <= 32 * 8) return launch_one<T, GATHER, GROUP32, 32, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-    if (nchunk <= 32 * 12) return launch_one<T, GATHER, GROUP32, 32, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-    if (nchunk <= 64 * 8) return launch_one<T, GATHER, GROUP32, 64, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-    if (nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-    if (nchunk <= 64 * 12) return launch_one<T, GATHER, GROUP32, 64, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+    if (nchunk <= 32 * 8) return launch_one<T, GATHER, GROUP32, 32, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+    if (nchunk <= 32 * 12) return launch_one<T, GATHER, GROUP32, 32, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+    if (nchunk <= 64 * 8) return launch_one<T, GATHER, GROUP32, 64, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+    if (nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+    if (nchunk <= 64 * 12) return launch_one<T, GATHER, GROUP32, 64, 12>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
   }
-  if (nchunk <= 64 * 4) return launch_one<T, GATHER, GROUP32, 64, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (nchunk <= 128 * 3) return launch_one<T, GATHER, GROUP32, 128, 3>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (nchunk <= 256 * 4) return launch_one<T, GATHER, GROUP32, 256, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (nchunk <= 256 * 6) return launch_one<T, GATHER, GROUP32, 256, 6>(x, ldx, row_idx, src_rows, q, s, M, K, st);
-  if (nchunk <= 256 * 8) return launch_one<T, GATHER, GROUP32, 256, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st);
+  if (nchunk <= 64 * 4) return launch_one<T, GATHER, GROUP32, 64, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (nchunk <= 128 * 3) return launch_one<T, GATHER, GROUP32, 128, 3>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (nchunk <= 128 * 5) return launch_one<T, GATHER, GROUP32, 128, 5>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (nchunk <= 256 * 4) return launch_one<T, GATHER, GROUP32, 256, 4>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (nchunk <= 256 * 6) return launch_one<T, GATHER, GROUP32, 256, 6>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
+  if (nchunk <= 256 * 8) return launch_one<T, GATHER, GROUP32, 256, 8>(x, ldx, row_idx, src_rows, q, s, M, K, st, s2);
   if constexpr (GROUP32) {
     return PQ_ERR_UNSUPPORTED;   // K > 16384 with group scales: not a shape of the path
   } else {
     if (M > 0x7fffffffLL) return PQ_ERR_SHAPE;
+    if (s2.x1 != nullptr) return PQ_ERR_UNSUPPORTED;         // two sources: rows up to 16384 elements
     pq_quant_rows_kernel_long<T, GATHER>
         <<<static_cast<unsigned>(M), kThreads, 0, st>>>(static_cast<const T*>(x), ldx, row_idx, src_rows, q, s, M, K);
     PQ_CUDA_TRY(cudaGetLastError());
@@ -257,6 +267,21 @@ extern "C" int pq_quant_rows(const void* x, int dtype, int64_t M, int64_t K, int
   if (dtype == PQ_DTYPE_BF16)
     return dispatch<__nv_bfloat16, false, false>(x, ldx, nullptr, M, q, s, M, static_cast<int>(K), st);
   return dispatch<__half, false, false>(x, ldx, nullptr, M, q, s, M, static_cast<int>(K), st);
+}
+
+extern "C" int pq_quant_rows_cat(const void* x0, int64_t K0, int64_t ldx0, const void* x1, int64_t K1, int64_t ldx1,
+                                 int dtype, int64_t M, int8_t* q, float* s, void* stream) {
+  if (K0 <= 0 || K1 <= 0 || ldx1 < K1) return PQ_ERR_SHAPE;
+  int rc = check_common(x0, dtype, M, K0, ldx0, q, s, 8);
+  if (rc != PQ_OK || M == 0) return rc;
+  if (x1 == nullptr) return PQ_ERR_NULL;
+  if (K1 % 8 != 0 || ldx1 % 8 != 0 || !aligned_to(x1, 16)) return PQ_ERR_ALIGN;
+  if (K0 + K1 > 16384) return PQ_ERR_UNSUPPORTED;
+  SecondSrc s2; s2.x1 = x1; s2.ldx1 = ldx1; s2.k0 = static_cast<int>(K0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == PQ_DTYPE_BF16)
+    return dispatch<__nv_bfloat16, false, false>(x0, ldx0, nullptr, M, q, s, M, static_cast<int>(K0 + K1), st, s2);
+  return dispatch<__half, false, false>(x0, ldx0, nullptr, M, q, s, M, static_cast<int>(K0 + K1), st, s2);
 }
 
 extern "C" int pq_gather_quant_rows(const void* canvas, int dtype, int64_t rows, int64_t K, int64_t ld,

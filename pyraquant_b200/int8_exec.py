@@ -464,11 +464,48 @@ class Int8Linear(nn.Module):
         out = y2.reshape(*h.shape[:-1], self.out_features)
         return (out, z.reshape(h.shape)) if return_modulated else out
 
-    def forward_gated_residual(self, x: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    def _prologue(self, x2: torch.Tensor, x_more: Optional[torch.Tensor] = None):
+        """(codes, row scales, t or None) of the layer's input; with ``x_more`` the input is ``[x2 | x_more]`` along the
+        features, read from its two sources where the kernels take them and concatenated otherwise."""
+        lr = self.lr_A is not None
+        if x_more is not None:
+            if (ops.cat_sources_ok(x2, x_more) and not torch.compiler.is_compiling()
+                    and (not lr or (self.lr_A.shape[1] == 32 and self.lr_A.dtype == x2.dtype))):
+                t = ops.lowrank_down_cat(x2, x_more, self._lr_At()) if lr else None
+                xq, sx = ops.quant_rows_cat(x2, x_more)
+                return xq, sx, t
+            x2 = torch.cat([x2, x_more], dim=1)
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        t = self._down(x2) if lr else None
+        xq, sx = quant_rows(x2)
+        return xq, sx, t
+
+    def forward_cat(self, x0: torch.Tensor, x1: torch.Tensor) -> torch.Tensor:
+        """``self(torch.cat([x0, x1], dim=-1))`` without building the concatenated tensor: the single-stream blocks'
+        ``proj_out(torch.cat([attn_output, mlp_hidden_states], dim=2))`` (flux/transformer_flux.py:143-145).  Identical
+        values (one row scale over all the features, as for the concatenated tensor)."""
+        K0, K1, N = x0.shape[-1], x1.shape[-1], self.out_features
+        assert K0 + K1 == self.in_features and x0.shape[:-1] == x1.shape[:-1], (x0.shape, x1.shape, self.in_features)
+        a, b = x0.reshape(-1, K0), x1.reshape(-1, K1)
+        lr = self.lr_A is not None
+        if (a.shape[0] == 0 or not a.is_cuda or a.dtype not in ops._DT or (K0 + K1) % 16 != 0
+                or (lr and not (self.lr_A.shape[1] == 32 and (K0 + K1) % 32 == 0 and self.lr_A.dtype == a.dtype
+                                and self.lr_B.dtype == a.dtype and N % 8 == 0))):
+            return self.forward(torch.cat([x0, x1], dim=-1))
+        xq, sx, t = self._prologue(a, b)
+        y = ops._gemm_impl(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B if lr else None, a.dtype,
+                           lb_t=self._lr_Bt() if lr else None)
+        return y.reshape(*x0.shape[:-1], N)
+
+    def forward_gated_residual(self, x: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor,
+                               x_more: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``residual += gate.unsqueeze(1) * self(x)``, in place, returns ``residual``: the tail of a FLUX block
         (flux/transformer_flux.py:145-149: ``hidden_states = residual + gate.unsqueeze(1) * proj_out(...)``, fp16 clipped to
         the finite range; likewise :224-225 and :240-242 for the attention and feed-forward outputs of the double-stream
-        blocks).  x [B, T, K] with gate [B, N] and residual [B, T, N], or x [M, K] with gate [N].  On CUDA the product
+        blocks).  x [B, T, K] with gate [B, N] and residual [B, T, N], or x [M, K] with gate [N]; with ``x_more`` the layer's
+        input is ``[x | x_more]`` along the features, read from the two tensors in place (``proj_out`` of the single-stream
+        blocks, whose input the reference concatenates first).  On CUDA the product
         and the sum happen in the GEMM epilogue (``pq_int8_gemm_gated``), rounding where the separate torch kernels round:
         the values are identical to the unfused sequence."""
         K, N = x.shape[-1], self.out_features
@@ -476,20 +513,22 @@ class Int8Linear(nn.Module):
         M = x2.shape[0]
         res2 = residual.reshape(-1, N)
         lr = self.lr_A is not None
-        fused = (M > 0 and x2.is_cuda and x2.dtype in ops._DT and K % 16 == 0 and not torch.compiler.is_compiling()
+        if x_more is not None and not (x2.is_cuda and ops.cat_sources_ok(x2, x_more.reshape(-1, x_more.shape[-1]))):
+            x = torch.cat([x, x_more], dim=-1)
+            x_more = None
+            K = x.shape[-1]
+            x2 = x.reshape(-1, K)
+        fused = (M > 0 and x2.is_cuda and x2.dtype in ops._DT and self.in_features % 16 == 0 and not torch.compiler.is_compiling()
                  and gate.dtype == x2.dtype and residual.dtype == x2.dtype and res2.shape[0] == M
                  and res2.stride(1) == 1 and res2.data_ptr() == residual.data_ptr()
                  and (not lr or self._fusable_lowrank(x2)) and ops.epilogue_supported(N, res2.stride(0), res2.data_ptr(), lr))
         if not fused:
-            y = self.forward(x)
+            y = self.forward(x if x_more is None else torch.cat([x, x_more], dim=-1))
             residual.add_((gate.unsqueeze(1) if x.dim() == 3 else gate) * y)
             if residual.dtype == torch.float16:
                 residual.clamp_(-65504, 65504)
             return residual
-        if x2.stride(1) != 1:
-            x2 = x2.contiguous()
-        t = self._down(x2) if lr else None
-        xq, sx = quant_rows(x2)
+        xq, sx, t = self._prologue(x2, None if x_more is None else x_more.reshape(-1, x_more.shape[-1]))
         ops._gemm_impl(xq, sx, self.weight_int8, self.w_scale, self.bias, t, self.lr_B if lr else None, x2.dtype,
                        lb_t=self._lr_Bt() if lr else None, epilogue=ops.EPI_ACCUMULATE, out=res2,
                        gate=gate, gate_rows=x.shape[-2] if x.dim() == 3 else 0)

@@ -144,6 +144,51 @@ def _quant_rows_g32_impl(x2: Tensor) -> Tuple[Tensor, Tensor]:
     return q, s
 
 
+def cat_sources_ok(x0: Tensor, x1: Tensor) -> bool:
+    """Whether the two-source entry points take x0 / x1 as they are (the seam on a 64-element boundary, rows up to
+    16384 elements, aligned row-strided views)."""
+    def ok(t):
+        return (t.dim() == 2 and t.is_cuda and t.stride(1) == 1 and (t.shape[0] <= 1 or t.stride(0) % 8 == 0)
+                and t.data_ptr() % 16 == 0)
+    return (ok(x0) and ok(x1) and x0.dtype == x1.dtype and x0.dtype in _DT and x0.shape[0] == x1.shape[0]
+            and x0.device == x1.device and x0.shape[1] % 64 == 0 and x1.shape[1] % 8 == 0
+            and x0.shape[1] + x1.shape[1] <= 16384)
+
+
+def quant_rows_cat(x0: Tensor, x1: Tensor) -> Tuple[Tensor, Tensor]:
+    """quant_rows(torch.cat([x0, x1], 1)) without the concatenated tensor (pq_quant_rows_cat)."""
+    assert cat_sources_ok(x0, x1)
+    M, K0 = x0.shape
+    K1 = x1.shape[1]
+    q = torch.empty((M, K0 + K1), dtype=torch.int8, device=x0.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x0.device)
+    with _on_device(x0):
+        rc = _LIB().pq_quant_rows_cat(x0.data_ptr(), K0, x0.stride(0) if M > 1 else max(K0, x0.stride(0)), x1.data_ptr(), K1,
+                                      x1.stride(0) if M > 1 else max(K1, x1.stride(0)), _dt(x0.dtype), M, q.data_ptr(),
+                                      s.data_ptr(), _stream(x0))
+    if rc:
+        _lib.check(rc, f"pq_quant_rows_cat(M={M}, K={K0}+{K1})")
+    return q, s
+
+
+def lowrank_down_cat(x0: Tensor, x1: Tensor, a_t: Tensor) -> Tensor:
+    """lowrank_down(torch.cat([x0, x1], 1), a_t) without the concatenated tensor (pq_lowrank_down_cat)."""
+    assert cat_sources_ok(x0, x1)
+    M, K0 = x0.shape
+    K1 = x1.shape[1]
+    R = a_t.shape[0]
+    assert R in LOWRANK_DOWN_COLS and a_t.dtype == x0.dtype and a_t.shape == (R, K0 + K1) and a_t.is_contiguous()
+    t = torch.empty((M, R), dtype=x0.dtype, device=x0.device)
+    ws = status_word(x0.device)
+    with _on_device(x0):
+        rc = _LIB().pq_lowrank_down_cat(x0.data_ptr(), K0, x0.stride(0) if M > 1 else max(K0, x0.stride(0)), x1.data_ptr(), K1,
+                                        x1.stride(0) if M > 1 else max(K1, x1.stride(0)), _dt(x0.dtype), a_t.data_ptr(),
+                                        K0 + K1, R, t.data_ptr(), R, M, ws.data_ptr(), ws.numel() * 4, _stream(x0))
+    if rc:
+        _lib.check(rc, f"pq_lowrank_down_cat(M={M}, K={K0}+{K1})")
+    return t
+
+
 def adaln_quant_rows(x2: Tensor, scale: Tensor, shift: Tensor, eps: float = 1e-6, rows_per_sample: int = 0,
                      want_modulated: bool = True) -> Tuple[Tensor, Tensor, Optional[Tensor]]:
     """(q, s, z) with z = LayerNorm(x2) * (1 + scale) + shift and (q, s) = quant_rows(z), in one pass over x2

@@ -159,6 +159,16 @@ def test_scatter_and_gather_argument_checks():
     assert ada(xm=p16, ldxm=32) == 2                  # x_mod rows shorter than K
     assert ada(rps=-1) == 2
     assert ada(eps=-1.0) == 2
+    qc = lambda K0=64, K1=64, x1=p16, ld1=64: lib.pq_quant_rows_cat(p16, K0, 64, x1, K1, ld1, 0, 4, p16, p16, None)
+    assert lib.pq_quant_rows_cat(p16, 64, 64, p16, 64, 64, 0, 0, p16, p16, None) == 0
+    assert qc(x1=None) == 1
+    assert qc(K1=60) == 3
+    assert qc(K1=128, ld1=64) == 2
+    assert lib.pq_quant_rows_cat(p16, 16384, 16384, p16, 64, 64, 0, 4, p16, p16, None) == 7
+    dc = lambda K0=64, x1=p16, K1=64: lib.pq_lowrank_down_cat(p16, K0, 128, x1, K1, 64, 0, p16, 128, 32, p16, 32, 4, None, 0, None)
+    assert dc(x1=None) == 1
+    assert dc(K0=32) == 7                             # seam off the 64-element grid
+    assert dc(K1=0) == 2
     assert lib.pq_i8_mma_issue_loop(0, 10, p16, None, 0, None) == 2
     assert lib.pq_wait_probe(None, 256, 1000, None) == 1
     assert lib.pq_wait_probe(p16, 8, 1000, None) == 8

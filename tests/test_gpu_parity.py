@@ -541,6 +541,32 @@ def test_forward_adaln(cuda_dev):
     assert torch.equal(y2, layer.forward_adaln(h[:1], scale[:1], shift[:1])[0])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("K0,K1,lowrank", [(128, 160, True), (3072, 1024, True), (64, 16, False), (96, 160, True), (15360, 1024, False)])
+def test_forward_on_two_sources(cuda_dev, dtype, K0, K1, lowrank):
+    """`forward_cat(x0, x1)` == the layer on `torch.cat([x0, x1], -1)` (flux/transformer_flux.py:143-145), bit for bit:
+    quantisation and down-projection read the two tensors in place.  K0 = 96 (seam off the 64-element grid) and
+    K0 + K1 = 16384 (beyond the register-resident rows) take the concatenating route; row-strided views are consumed as
+    they are.  Also through the gate-and-residual epilogue."""
+    g = torch.Generator().manual_seed(K0 + K1)
+    N, B, T = 256, 2, 150
+    layer = _toy_layer(cuda_dev, g, K0 + K1, N, lowrank=lowrank, dtype=dtype)
+    wide = (torch.randn(B, T, K0 + 40, generator=g) * 1.5).to(dtype).to(cuda_dev)
+    x0 = wide[..., :K0]                                       # a view with a row stride of K0 + 40
+    x1 = (torch.randn(B, T, K1, generator=g) * 0.7).to(dtype).to(cuda_dev)
+    x1[..., 3] *= 25.0
+    want = layer(torch.cat([x0, x1], dim=-1))
+    got = layer.forward_cat(x0, x1)
+    assert got.shape == want.shape and torch.equal(got, want)
+    gate = (torch.randn(B, N, generator=g) * 0.5).to(dtype).to(cuda_dev)
+    residual = torch.randn(B, T, N, generator=g).to(dtype).to(cuda_dev)
+    ref = residual + gate.unsqueeze(1) * want
+    res = residual.clone()
+    layer.forward_gated_residual(x0, gate, res, x_more=x1)
+    assert torch.equal(res, ref)
+    ops.check_device_status(cuda_dev)
+
+
 def test_shared_group_primed_by_adaln(cuda_dev, monkeypatch):
     """`SharedInputGroup.prime_adaln`: one pass produces the modulated activations and the members' shared codes; the
     members called on the result skip their own quantisation and give what they give ungrouped on the same tensor."""
