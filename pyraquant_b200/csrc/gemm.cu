@@ -563,7 +563,7 @@ int gemm_common(const int8_t* xq, int64_t ldx, const float* s_row, const int8_t*
   p.timing = (options().gemm_debug_timing != 0 && workspace != nullptr && ws_bytes >= 256 + 4096 * 64)
                  ? reinterpret_cast<long long*>(static_cast<char*>(workspace) + 256) : nullptr;
   p.sched_pm = p.sched_pn = p.sched_m_steps = p.sched_n_rounds = 1;
-  p.sched_panel = 0; p.l2_hints = 0; p.tma_store = 0; p.sched_cut = 0; p.sched_tail_per = 0;
+  p.sched_panel = 0; p.l2_hints = 0; p.tma_store = 0; p.sched_cut = 0; p.sched_tail_per = 0; p.sched_tail_rb = 1;
   p.gate = gate; p.ld_gate = ld_gate; p.gate_rows = gate_rows;
   p.n_out_more = n_out_more;
   for (int d = 0; d < 7; ++d) p.out_more[d] = d < n_out_more ? out_more[d] : nullptr;

@@ -171,30 +171,39 @@ __device__ __noinline__ void dump_acc_pair(int32_t* dbg, int N, int rA, int rB, 
 // column rounds a short panel keeps the panel's activation rows in L2 across the rounds instead of streaming all M rows
 // once per round.
 // Pairs beyond the grid (the SM pairs a pm x pn rectangle leaves over: 2 of 74 with the 6 x 12 grid of the FLUX layers)
-// take a tail region off the grid's hands: the row tiles from `cut` on in the last column round, walked column by column,
-// a contiguous share of `tail_per` tiles each; the grid pairs stop at `cut` in that round.  The host picks `cut` so that
+// take a tail region off the grid's hands: the row tiles from `cut` on in the last column round, in small row blocks, a
+// contiguous share of `tail_per` tiles each; the grid pairs stop at `cut` in that round.  The host picks `cut` so that
 // grid pairs and tail pairs finish together.
 struct PairWalker {
   int mt, ntile, bn, pm, pn, mt_total, nt, panel0, panel_span;
   int col0, cut;       // first column tile of the last column round; row limit of the grid pairs there
   int tail_left;       // tiles left for a tail pair; -1 for a grid pair
+  int t_rb0, t_hb, t_rb;   // tail pair: first row tile and height of its current row block, rows per block
   __device__ __forceinline__ void init(int pair, const GemmParams& p, int mt_total_, int nt_) {
     pm = p.sched_pm; pn = p.sched_pn; mt_total = mt_total_; nt = nt_;
     col0 = ((nt + pn - 1) / pn - 1) * pn;
     cut = p.sched_tail_per > 0 ? p.sched_cut : mt_total;
     panel_span = (p.sched_panel > 0 && p.sched_panel < (1 << 20)) ? p.sched_panel * pm : (1 << 30);
+    t_rb0 = 0; t_hb = 1; t_rb = p.sched_tail_rb > 0 ? p.sched_tail_rb : 1;
     if (pair < pm * pn) {
       const int bm = pair / pn; bn = pair - bm * pn;
       panel0 = bm; mt = bm; ntile = bn; tail_left = -1;
     } else {
-      const int nrows = mt_total - cut;
-      const int total = nrows * (nt - col0);
+      // The tail region in blocks of t_rb row tiles, block after block; inside a block column after column, the rows of
+      // the block innermost: a block's activation rows are used again after t_rb tiles (they stay in L2) and the column
+      // changes every t_rb tiles.
+      const int wl = nt - col0;
+      const int total = (mt_total - cut) * wl;
       const int j = (pair - pm * pn) * p.sched_tail_per;
       const int j_end = j + p.sched_tail_per < total ? j + p.sched_tail_per : total;
       tail_left = j_end > j ? j_end - j : 0;
       bn = 0; panel0 = 0;
-      if (tail_left > 0) { ntile = col0 + j / nrows; mt = cut + j % nrows; }
-      else { ntile = nt; mt = mt_total; }
+      if (tail_left > 0) {
+        const int b = j / (t_rb * wl), rem = j - b * (t_rb * wl);
+        t_rb0 = cut + b * t_rb;
+        t_hb = mt_total - t_rb0 < t_rb ? mt_total - t_rb0 : t_rb;
+        ntile = col0 + rem / t_hb; mt = t_rb0 + rem % t_hb;
+      } else { ntile = nt; mt = mt_total; }
     }
   }
   __device__ __forceinline__ int row_limit() const { return ntile >= col0 ? cut : mt_total; }
@@ -202,7 +211,13 @@ struct PairWalker {
   __device__ __forceinline__ void advance() {
     if (tail_left >= 0) {
       --tail_left;
-      if (++mt >= mt_total) { mt = cut; ++ntile; }
+      if (++mt >= t_rb0 + t_hb) {
+        mt = t_rb0;
+        if (++ntile >= nt) {
+          ntile = col0; t_rb0 += t_rb; mt = t_rb0;
+          t_hb = mt_total - t_rb0 < t_rb ? mt_total - t_rb0 : t_rb;
+        }
+      }
       return;
     }
     mt += pm;
@@ -845,6 +860,9 @@ int launch_pair_ew(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtenso
   // Tail pairs.  The pm x pn grid leaves pairs_cap - pm * pn SM pairs idle; they take the row tiles from `cut` on of the
   // last column round, and `cut` (a multiple of pm) is chosen for the fewest steps of the slower of the two groups.
   p.sched_cut = mt_pairs; p.sched_tail_per = 0;
+  // rows per block of the tail order: the whole region as one block, i.e. column after column (blocks of 1, 2 or 4 row
+  // tiles were measured: the same time, 0.5 GB more DRAM reads per launch at 66 048 rows)
+  p.sched_tail_rb = mt_pairs;
   int extra = pairs_cap - p.sched_pm * p.sched_pn;
   if (extra > 0 && p.sched_panel == 0 && options().gemm_tail_pairs != 0) {
     const int row_steps = (mt_pairs + p.sched_pm - 1) / p.sched_pm;

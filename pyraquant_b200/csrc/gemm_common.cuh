@@ -26,7 +26,8 @@ struct GemmParams {
   int epi_flags;            // PQ_EPI_* bits (CTA-pair kernel only)
   int sched_panel;          // CTA-pair kernel: row steps per panel (0 = all rows in one panel)
   int sched_cut;            // CTA-pair kernel: in the last column round the pair grid takes row tiles below this one only ...
-  int sched_tail_per;       // ... and the pairs beyond the grid take the rest, this many tiles each (0: no such pairs)
+  int sched_tail_per;       // ... and the pairs beyond the grid take the rest, this many tiles each (0: no such pairs),
+  int sched_tail_rb;        // in blocks of this many row tiles
   int l2_hints;             // CTA-pair kernel: Options::gemm_l2_hints
   int tma_store;            // CTA-pair kernel, sixteen epilogue warps: output tiles leave through shared memory + TMA
   const void* gate;         // CTA-pair kernel, PQ_EPI_GATE: [samples, N] factors in the output type (row stride ld_gate)
