@@ -861,7 +861,7 @@ int launch_pair_ew(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtenso
   // last column round, and `cut` (a multiple of pm) is chosen for the fewest steps of the slower of the two groups.
   p.sched_cut = mt_pairs; p.sched_tail_per = 0;
   // rows per block of the tail order: the whole region as one block, i.e. column after column (blocks of 1, 2 or 4 row
-  // tiles were measured: the same time, 0.5 GB more DRAM reads per launch at 66 048 rows)
+  // tiles measured the same time)
   p.sched_tail_rb = mt_pairs;
   int extra = pairs_cap - p.sched_pm * p.sched_pn;
   if (extra > 0 && p.sched_panel == 0 && options().gemm_tail_pairs != 0) {
